@@ -1,0 +1,117 @@
+/*
+ * jvpfa.h -- C ABI of the B200 (sm_100a) JVP flash-attention library (libjvpfa.so).
+ *
+ * The entry points below are what a binding of the reference's attention path would call in
+ * place of its Triton launches. All tensors are caller-owned device memory; (B,H,N,D) tensors are
+ * contiguous row-major exactly as the reference requires (jvp_flash_attention/jvp_attention.py:2950,
+ * 3007, 3107-3127). Every call is asynchronous on the given CUDA stream and returns a status code;
+ * nothing here allocates device memory unless a comment on the entry point says otherwise.
+ */
+#ifndef JVPFA_H_
+#define JVPFA_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element types */
+enum { JVPFA_F16 = 0, JVPFA_BF16 = 1, JVPFA_F32 = 2 };
+/* mask kinds: the reference's MASK_TYPE values (jvp_attention.py:2623-2656) */
+enum { JVPFA_MASK_NONE = 0, JVPFA_MASK_BOOL = 1, JVPFA_MASK_ADDITIVE = 2 };
+
+/* status codes */
+enum {
+  JVPFA_OK = 0,
+  JVPFA_ERR_BAD_ARG = 1,       /* null pointer, non-positive size, misaligned pointer            */
+  JVPFA_ERR_UNSUPPORTED = 2,   /* shape / dtype combination this library has no kernel for       */
+  JVPFA_ERR_CAUSAL_MASK = 3,   /* causal together with a mask (ValueError in the reference)      */
+  JVPFA_ERR_WORKSPACE = 4,     /* workspace missing or too small                                 */
+  JVPFA_ERR_LAUNCH = 5,        /* CUDA reported an error at launch or tensor-map encoding        */
+  JVPFA_ERR_DEVICE_TIMEOUT = 6,/* a bounded device-side wait gave up (see jvpfa_read_status)     */
+  JVPFA_ERR_NO_ALLOC_LIMIT = 7 /* problem exceeds the fixed scratch of an allocation-free entry  */
+};
+
+/* A mask of logical shape (B,H,N,N) given by element strides; a stride of 0 broadcasts.
+ * kind BOOL: one byte per element, non-zero = take part in attention.
+ * kind ADDITIVE: `dtype` elements added to the scaled scores; -inf excludes an element. */
+typedef struct jvpfa_mask {
+  const void* ptr;
+  int32_t kind;
+  int32_t dtype;
+  int64_t stride[4];
+} jvpfa_mask;
+
+/* Dual forward. Replaces the launch of _attn_fwd_tma / _attn_fwd in JVPAttn.forward
+ * (jvp_attention.py:2773, 2807). Outputs: o, to (same dtype as q), lse2 and mu ((B,H,N) fp32:
+ * base-2 log-sum-exp of the scaled, masked scores -- the reference's M, jvp_attention.py:2594 --
+ * and mu = rowsum(P o tS), which the dual backward needs). tq/tk/tv/to may all be NULL for the
+ * primal-only call (JVPAttn.fwd, jvp_attention.py:2915-2970). */
+typedef struct jvpfa_fwd_args {
+  int32_t B, H, N, D;
+  int32_t dtype;
+  int32_t causal;
+  float sm_scale;
+  jvpfa_mask mask;
+  const uint8_t* mask_summary; /* optional output of jvpfa_mask_summary, else NULL */
+  const void *q, *k, *v, *tq, *tk, *tv;
+  void *o, *to;
+  float *lse2, *mu;
+  void* workspace;
+  size_t workspace_bytes;
+} jvpfa_fwd_args;
+
+/* Dual backward: gradients of sum(o*go)+sum(to*gto) for all six inputs. Replaces
+ * _attn_bwd_preprocess + _attn_bwd / _attn_bwd_causal in JVPAttn.backward
+ * (jvp_attention.py:3171, 3189), and adds what the reference leaves out: the gradient through
+ * the tangent output and the tangent-input gradients (jvp_attention.py:3081, 3226).
+ * gto == NULL means a zero upstream gradient for the tangent output. */
+typedef struct jvpfa_bwd_args {
+  int32_t B, H, N, D;
+  int32_t dtype;
+  int32_t causal;
+  float sm_scale;
+  jvpfa_mask mask;
+  const uint8_t* mask_summary;
+  const void *q, *k, *v, *tq, *tk, *tv;
+  const void *o, *to;
+  const float *lse2, *mu;
+  const void *go, *gto;
+  void *dq, *dk, *dv, *dtq, *dtk, *dtv;
+  void* workspace;
+  size_t workspace_bytes;
+} jvpfa_bwd_args;
+
+/* Library version (major*10000 + minor*100 + patch). */
+int jvpfa_version(void);
+/* Text for a status code. */
+const char* jvpfa_error_string(int status);
+
+/* Bytes of caller-provided scratch the calls below need (always >= 256: the first 4 bytes hold
+ * the device status word that bounded waits write to). */
+size_t jvpfa_fwd_workspace_bytes(const jvpfa_fwd_args* args);
+size_t jvpfa_bwd_workspace_bytes(const jvpfa_bwd_args* args);
+
+/* Bytes of the per-tile mask summary for a mask over sequences of length N with Bm x Hm
+ * distinct (batch, head) planes, and the kernel that fills it: per 64x64 tile, bit 0 = some
+ * element kept, bit 1 = some element excluded. Lets the kernels skip fully excluded tiles and
+ * skip mask loads on fully kept ones. No reference counterpart (the reference reads the mask in
+ * every tile, jvp_attention.py:250-262). */
+size_t jvpfa_mask_summary_bytes(int32_t Bm, int32_t Hm, int32_t N);
+int jvpfa_mask_summary(const jvpfa_mask* mask, int32_t B, int32_t H, int32_t N, uint8_t* summary, void* stream);
+
+/* The two launches. `stream` is a cudaStream_t. */
+int jvpfa_fwd(const jvpfa_fwd_args* args, void* stream);
+int jvpfa_bwd(const jvpfa_bwd_args* args, void* stream);
+
+/* Synchronises the stream, reads the status word at the start of `workspace`, clears it, and
+ * returns JVPFA_OK or JVPFA_ERR_DEVICE_TIMEOUT (`detail`, if not NULL, receives the raw word:
+ * 100 + the id of the wait that gave up). */
+int jvpfa_read_status(void* workspace, void* stream, int32_t* detail);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* JVPFA_H_ */

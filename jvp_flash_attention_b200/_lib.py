@@ -1,0 +1,231 @@
+"""ctypes binding of libjvpfa.so (the C ABI declared in include/jvpfa.h).
+
+The library is loaded lazily; there is no fallback of any kind: if the shared object is missing
+or a call returns a non-zero status, an exception is raised.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import threading
+from pathlib import Path
+
+import torch
+
+F16, BF16, F32 = 0, 1, 2
+MASK_NONE, MASK_BOOL, MASK_ADDITIVE = 0, 1, 2
+
+OK = 0
+ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_CAUSAL_MASK, ERR_WORKSPACE, ERR_LAUNCH, ERR_DEVICE_TIMEOUT, ERR_NO_ALLOC_LIMIT = range(1, 8)
+
+_DTYPE_CODE = {torch.float16: F16, torch.bfloat16: BF16, torch.float32: F32}
+
+EXPORTED_SYMBOLS = (
+    "jvpfa_version",
+    "jvpfa_error_string",
+    "jvpfa_fwd_workspace_bytes",
+    "jvpfa_bwd_workspace_bytes",
+    "jvpfa_mask_summary_bytes",
+    "jvpfa_mask_summary",
+    "jvpfa_fwd",
+    "jvpfa_bwd",
+    "jvpfa_read_status",
+)
+
+
+class Mask(C.Structure):
+    _fields_ = [("ptr", C.c_void_p), ("kind", C.c_int32), ("dtype", C.c_int32), ("stride", C.c_int64 * 4)]
+
+
+class FwdArgs(C.Structure):
+    _fields_ = [
+        ("B", C.c_int32), ("H", C.c_int32), ("N", C.c_int32), ("D", C.c_int32),
+        ("dtype", C.c_int32), ("causal", C.c_int32), ("sm_scale", C.c_float),
+        ("mask", Mask), ("mask_summary", C.c_void_p),
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p),
+        ("tq", C.c_void_p), ("tk", C.c_void_p), ("tv", C.c_void_p),
+        ("o", C.c_void_p), ("to", C.c_void_p), ("lse2", C.c_void_p), ("mu", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+    ]
+
+
+class BwdArgs(C.Structure):
+    _fields_ = [
+        ("B", C.c_int32), ("H", C.c_int32), ("N", C.c_int32), ("D", C.c_int32),
+        ("dtype", C.c_int32), ("causal", C.c_int32), ("sm_scale", C.c_float),
+        ("mask", Mask), ("mask_summary", C.c_void_p),
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p),
+        ("tq", C.c_void_p), ("tk", C.c_void_p), ("tv", C.c_void_p),
+        ("o", C.c_void_p), ("to", C.c_void_p), ("lse2", C.c_void_p), ("mu", C.c_void_p),
+        ("go", C.c_void_p), ("gto", C.c_void_p),
+        ("dq", C.c_void_p), ("dk", C.c_void_p), ("dv", C.c_void_p),
+        ("dtq", C.c_void_p), ("dtk", C.c_void_p), ("dtv", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+    ]
+
+
+class JvpfaError(RuntimeError):
+    def __init__(self, status: int, text: str):
+        super().__init__(f"libjvpfa status {status}: {text}")
+        self.status = status
+
+
+_lock = threading.Lock()
+_lib = None
+
+
+def library_path() -> Path:
+    env = os.environ.get("JVPFA_LIBRARY")
+    return Path(env) if env else Path(__file__).resolve().parent / "libjvpfa.so"
+
+
+def lib():
+    """Returns the loaded CDLL; raises if the shared object has not been built."""
+    global _lib
+    if _lib is None:
+        with _lock:
+            if _lib is None:
+                path = library_path()
+                if not path.exists():
+                    raise RuntimeError(
+                        f"{path} not found: build it with `python -m jvp_flash_attention_b200.build` "
+                        "(there is no non-CUDA fallback)")
+                L = C.CDLL(str(path))
+                L.jvpfa_version.restype = C.c_int
+                L.jvpfa_error_string.restype = C.c_char_p
+                L.jvpfa_error_string.argtypes = [C.c_int]
+                L.jvpfa_fwd_workspace_bytes.restype = C.c_size_t
+                L.jvpfa_fwd_workspace_bytes.argtypes = [C.POINTER(FwdArgs)]
+                L.jvpfa_bwd_workspace_bytes.restype = C.c_size_t
+                L.jvpfa_bwd_workspace_bytes.argtypes = [C.POINTER(BwdArgs)]
+                L.jvpfa_mask_summary_bytes.restype = C.c_size_t
+                L.jvpfa_mask_summary_bytes.argtypes = [C.c_int32, C.c_int32, C.c_int32]
+                L.jvpfa_mask_summary.restype = C.c_int
+                L.jvpfa_mask_summary.argtypes = [C.POINTER(Mask), C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]
+                L.jvpfa_fwd.restype = C.c_int
+                L.jvpfa_fwd.argtypes = [C.POINTER(FwdArgs), C.c_void_p]
+                L.jvpfa_bwd.restype = C.c_int
+                L.jvpfa_bwd.argtypes = [C.POINTER(BwdArgs), C.c_void_p]
+                L.jvpfa_read_status.restype = C.c_int
+                L.jvpfa_read_status.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_int32)]
+                _lib = L
+    return _lib
+
+
+def check(status: int) -> None:
+    if status != OK:
+        raise JvpfaError(status, lib().jvpfa_error_string(status).decode())
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    try:
+        return _DTYPE_CODE[dt]
+    except KeyError:
+        raise AssertionError(f"unsupported dtype {dt}; expected float16, bfloat16 or float32") from None
+
+
+def _ptr(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def make_mask(mask, B, H, N) -> Mask:
+    """Builds the C mask view of a tensor broadcastable to (B,H,N,N); None -> kind NONE."""
+    m = Mask()
+    if mask is None:
+        m.ptr, m.kind, m.dtype = None, MASK_NONE, 0
+        return m
+    assert mask.dim() == 4, "The provided attention mask must have 4 dimensions (Z, H, N_CTX, N_CTX)."
+    view = mask.expand(B, H, N, N)
+    m.ptr = view.data_ptr()
+    if mask.dtype == torch.bool:
+        m.kind, m.dtype = MASK_BOOL, 0
+    else:
+        m.kind, m.dtype = MASK_ADDITIVE, dtype_code(mask.dtype)
+    for i in range(4):
+        m.stride[i] = view.stride(i)
+    return m
+
+
+def stream_ptr(device) -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+# Per-device workspace (status word + scratch), grown on demand. Reusing one buffer per device keeps
+# the status word at a stable address; kernels of consecutive calls on one stream are ordered.
+_workspaces: dict = {}
+
+
+def workspace(device, nbytes: int) -> torch.Tensor:
+    key = (device.index if device.index is not None else torch.cuda.current_device())
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def read_status(device=None) -> None:
+    """Synchronises the current stream and raises if a device-side wait gave up since the last read."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+    ws = workspace(device, 256)
+    detail = C.c_int32(0)
+    rc = lib().jvpfa_read_status(C.c_void_p(ws.data_ptr()), stream_ptr(device), C.byref(detail))
+    if rc != OK:
+        raise JvpfaError(rc, lib().jvpfa_error_string(rc).decode() + f" (wait id {detail.value})")
+
+
+def mask_summary(mask_c: Mask, mask_tensor, B, H, N):
+    """Runs the tile-summary pre-pass; returns the uint8 tensor (kept alive by the caller)."""
+    if mask_c.kind == MASK_NONE:
+        return None
+    Bm = 1 if mask_c.stride[0] == 0 else B
+    Hm = 1 if mask_c.stride[1] == 0 else H
+    n = lib().jvpfa_mask_summary_bytes(Bm, Hm, N)
+    out = torch.empty(n, dtype=torch.uint8, device=mask_tensor.device)
+    check(lib().jvpfa_mask_summary(C.byref(mask_c), B, H, N, C.c_void_p(out.data_ptr()), stream_ptr(mask_tensor.device)))
+    return out
+
+
+def fwd(q, k, v, tq, tk, tv, mask_c: Mask, summary, causal: bool, sm_scale: float):
+    """Launches the dual forward; returns (o, to, lse2, mu). tq/tk/tv None -> primal only (to None)."""
+    B, H, N, D = q.shape
+    dual = tq is not None
+    o = torch.empty_like(q)
+    to = torch.empty_like(q) if dual else None
+    lse2 = torch.empty((B, H, N), dtype=torch.float32, device=q.device)
+    mu = torch.empty((B, H, N), dtype=torch.float32, device=q.device)
+    a = FwdArgs()
+    a.B, a.H, a.N, a.D = B, H, N, D
+    a.dtype, a.causal, a.sm_scale = dtype_code(q.dtype), int(bool(causal)), float(sm_scale)
+    a.mask = mask_c
+    a.mask_summary = None if summary is None else summary.data_ptr()
+    a.q, a.k, a.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
+    a.tq, a.tk, a.tv = (tq.data_ptr(), tk.data_ptr(), tv.data_ptr()) if dual else (None, None, None)
+    a.o, a.to = o.data_ptr(), (to.data_ptr() if dual else None)
+    a.lse2, a.mu = lse2.data_ptr(), mu.data_ptr()
+    need = lib().jvpfa_fwd_workspace_bytes(C.byref(a))
+    ws = workspace(q.device, need)
+    a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+    check(lib().jvpfa_fwd(C.byref(a), stream_ptr(q.device)))
+    return o, to, lse2, mu
+
+
+def bwd(q, k, v, tq, tk, tv, o, to, lse2, mu, go, gto, mask_c: Mask, summary, causal: bool, sm_scale: float):
+    """Launches the dual backward; returns (dq, dk, dv, dtq, dtk, dtv)."""
+    B, H, N, D = q.shape
+    outs = [torch.empty_like(q) for _ in range(6)]
+    a = BwdArgs()
+    a.B, a.H, a.N, a.D = B, H, N, D
+    a.dtype, a.causal, a.sm_scale = dtype_code(q.dtype), int(bool(causal)), float(sm_scale)
+    a.mask = mask_c
+    a.mask_summary = None if summary is None else summary.data_ptr()
+    a.q, a.k, a.v, a.tq, a.tk, a.tv = (t.data_ptr() for t in (q, k, v, tq, tk, tv))
+    a.o, a.to, a.lse2, a.mu = o.data_ptr(), to.data_ptr(), lse2.data_ptr(), mu.data_ptr()
+    a.go = go.data_ptr()
+    a.gto = None if gto is None else gto.data_ptr()
+    a.dq, a.dk, a.dv, a.dtq, a.dtk, a.dtv = (t.data_ptr() for t in outs)
+    need = lib().jvpfa_bwd_workspace_bytes(C.byref(a))
+    ws = workspace(q.device, need)
+    a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+    check(lib().jvpfa_bwd(C.byref(a), stream_ptr(q.device)))
+    return tuple(outs)

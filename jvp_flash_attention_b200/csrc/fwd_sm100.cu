@@ -1,0 +1,458 @@
+// Dual (JVP) attention forward for sm_100a: O = softmax(s QK^T + mask) V and its tangent tO in one
+// pass, with tcgen05 MMAs accumulating in TMEM and K/tK/V/tV tiles staged by TMA.
+//
+// Replaces the reference's _attn_fwd_tma / _attn_fwd_inner_tma (jvp_flash_attention/jvp_attention.py:
+// 1100-1392, 350-559). Per (128-row query tile, batch*head) one CTA of 6 warps:
+//   warps 0-3  softmax: thread r owns score row r (TMEM lane r); keeps m, l, mu in registers, turns the
+//              score tile S and tangent-score tile tS into 16-bit P and W = P o (s tS) written back to TMEM
+//   warp 4     TMA producer (one lane)
+//   warp 5     MMA issuer (one lane); owns the TMEM allocation
+// Per 64-column key tile: S = Q K^T, tS = tQ K^T + Q tK^T (operands in shared memory), then
+// O += P V, T += W V + P tV (P, W read from TMEM; V, tV as MN-major shared-memory operands).
+// Epilogue: O/l, tO = T/l - (mu/l) O/l, lse2 = m + log2 l, mu/l.
+// TMEM columns: O [0,D), T [D,2D), then two score buffers of (S 64 | tS 64) columns; P and W
+// overwrite the first 32 columns of S and tS of their buffer.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include "host_common.h"
+#include "mask_common.cuh"
+#include "sm100_prims.cuh"
+
+namespace jvpfa {
+using namespace sm100;
+
+namespace {
+
+struct FwdKParams {
+  int H, N;
+  int causal;
+  float c1;      // sm_scale * log2(e)
+  float s;       // sm_scale
+  float thresh;  // lazy-rescale threshold in the log2 domain
+  MaskView mv;
+  void* o;
+  void* to;
+  float* lse2;
+  float* mu;
+  int* status;
+  uint64_t budget_ns;
+};
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+  if constexpr (BF16) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  } else {
+    __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+}
+
+template <int D>
+struct FwdCfg {
+  static constexpr int BM = 128;
+  static constexpr int BN = 64;
+  static constexpr int STAGES = (D == 64) ? 4 : 2;
+  static constexpr int TILE_Q = BM * D * 2;
+  static constexpr int TILE_K = BN * D * 2;
+  static constexpr int TMEM_O = 0;
+  static constexpr int TMEM_T = D;
+  static constexpr int TMEM_S = 2 * D;  // buffer b at TMEM_S + 128*b; tS 64 columns further
+  static constexpr int TMEM_COLS = 512;
+  static constexpr size_t smem_bytes(bool dual) {
+    return 1024 + (dual ? 2 : 1) * TILE_Q + STAGES * (dual ? 4 : 2) * TILE_K;
+  }
+};
+
+template <int D, bool DUAL, bool BF16>
+__global__ void __launch_bounds__(192, 1)
+fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmTQ,
+                 const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmTK,
+                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmTV,
+                 const FwdKParams p) {
+  using C = FwdCfg<D>;
+  constexpr int ST = C::STAGES;
+  constexpr int NT = DUAL ? 2 : 1;  // tensors per operand family
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sTQ = sQ + C::TILE_Q;  // only with DUAL
+  uint8_t* sKV = smem + NT * C::TILE_Q;
+  auto sK = [&](int st) { return sKV + st * (2 * NT) * C::TILE_K; };
+  auto sTK = [&](int st) { return sK(st) + C::TILE_K; };  // only with DUAL
+  auto sV = [&](int st) { return sK(st) + NT * C::TILE_K; };
+  auto sTV = [&](int st) { return sV(st) + C::TILE_K; };  // only with DUAL
+
+  __shared__ uint64_t q_full, k_full[ST], v_full[ST], k_empty[ST], v_empty[ST], s_full[2], p_full[2], o_done, o_final;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int poisoned;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int qt = p.causal ? (static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x)) : blockIdx.x;
+  const int bh = blockIdx.y;
+  const int b = bh / p.H, h = bh % p.H;
+  const int q0 = qt * C::BM;
+  const int N = p.N;
+  const int row_base = bh * N;
+  int n_kt = (N + C::BN - 1) / C::BN;
+  if (p.causal) n_kt = min(n_kt, (q0 + C::BM - 1) / C::BN + 1);
+
+  const WaitCtx w{p.status, &poisoned, p.budget_ns};
+
+  if (tid == 0) {
+    poisoned = 0;
+    mbar_init(&q_full, 1);
+    for (int i = 0; i < ST; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+      mbar_init(&v_empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s_full[i], 1);
+      mbar_init(&p_full[i], 128);
+    }
+    mbar_init(&o_done, 1);
+    mbar_init(&o_final, 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
+  if (warp == 5) {
+    tmem_alloc(&tmem_base_s, C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = tmem_base_s;
+
+  // Key tile j takes part unless the mask summary says that nothing in it is kept.
+  auto tile_bits = [&](int j) -> uint8_t {
+    if (p.mv.kind == JVPFA_MASK_NONE) return kTileAnyKept;
+    uint8_t bits = mask_tile_bits(p.mv, b, h, 2 * qt, j);
+    if (2 * qt + 1 < p.mv.n64) bits |= mask_tile_bits(p.mv, b, h, 2 * qt + 1, j);
+    return bits;
+  };
+
+  if (warp == 4) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tmQ);
+      tma_prefetch_desc(&tmK);
+      tma_prefetch_desc(&tmV);
+      mbar_arrive_expect_tx(&q_full, NT * C::TILE_Q);
+      tma_load_3d(sQ, &tmQ, &q_full, 0, row_base + q0, 0);
+      if constexpr (DUAL) tma_load_3d(sTQ, &tmTQ, &q_full, 0, row_base + q0, 0);
+      int it = 0;
+      for (int j = 0; j < n_kt; ++j) {
+        if (!(tile_bits(j) & kTileAnyKept)) continue;
+        const int st = it % ST;
+        const uint32_t ph = (it / ST) & 1;
+        const int krow = row_base + j * C::BN;
+        mbar_wait(&k_empty[st], ph ^ 1, w, 10);
+        mbar_arrive_expect_tx(&k_full[st], NT * C::TILE_K);
+        tma_load_3d(sK(st), &tmK, &k_full[st], 0, krow, 0);
+        if constexpr (DUAL) tma_load_3d(sTK(st), &tmTK, &k_full[st], 0, krow, 0);
+        mbar_wait(&v_empty[st], ph ^ 1, w, 11);
+        mbar_arrive_expect_tx(&v_full[st], NT * C::TILE_K);
+        tma_load_3d(sV(st), &tmV, &v_full[st], 0, krow, 0);
+        if constexpr (DUAL) tma_load_3d(sTV(st), &tmTV, &v_full[st], 0, krow, 0);
+        ++it;
+      }
+    }
+    __syncwarp();
+  } else if (warp == 5) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t FMT = BF16 ? FMT_BF16 : FMT_F16;
+      const uint32_t idesc_qk = make_idesc(FMT, 128, C::BN, 0, 0);
+      const uint32_t idesc_pv = make_idesc(FMT, 128, D, 0, 1);
+      const uint32_t aQ = smem_u32(sQ), aTQ = smem_u32(sTQ);
+
+      auto issue_qk = [&](int it) {
+        const int st = it % ST;
+        const uint32_t ph = (it / ST) & 1;
+        const uint32_t S_t = tmem + C::TMEM_S + (it & 1) * 128;
+        const uint32_t tS_t = S_t + 64;
+        mbar_wait(&k_full[st], ph, w, 20);
+        tc_fence_after_sync();
+        const uint32_t bK = smem_u32(sK(st)), bTK = smem_u32(sTK(st));
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t oa = (k >> 2) * (C::BM * 128) + (k & 3) * 32;
+          const uint32_t ob = (k >> 2) * (C::BN * 128) + (k & 3) * 32;
+          umma_ss(S_t, desc_kmajor_sw128(aQ + oa), desc_kmajor_sw128(bK + ob), idesc_qk, k > 0);
+        }
+        if constexpr (DUAL) {
+#pragma unroll
+          for (int k = 0; k < D / 16; ++k) {
+            const uint32_t oa = (k >> 2) * (C::BM * 128) + (k & 3) * 32;
+            const uint32_t ob = (k >> 2) * (C::BN * 128) + (k & 3) * 32;
+            umma_ss(tS_t, desc_kmajor_sw128(aTQ + oa), desc_kmajor_sw128(bK + ob), idesc_qk, k > 0);
+          }
+#pragma unroll
+          for (int k = 0; k < D / 16; ++k) {
+            const uint32_t oa = (k >> 2) * (C::BM * 128) + (k & 3) * 32;
+            const uint32_t ob = (k >> 2) * (C::BN * 128) + (k & 3) * 32;
+            umma_ss(tS_t, desc_kmajor_sw128(aQ + oa), desc_kmajor_sw128(bTK + ob), idesc_qk, 1);
+          }
+        }
+        umma_commit(&s_full[it & 1]);
+        umma_commit(&k_empty[st]);
+      };
+      auto issue_pv = [&](int it, bool last) {
+        const int st = it % ST;
+        const uint32_t ph = (it / ST) & 1;
+        const uint32_t P_t = tmem + C::TMEM_S + (it & 1) * 128;
+        const uint32_t W_t = P_t + 64;
+        mbar_wait(&p_full[it & 1], (it >> 1) & 1, w, 21);
+        mbar_wait(&v_full[st], ph, w, 22);
+        tc_fence_after_sync();
+        const uint32_t bV = smem_u32(sV(st)), bTV = smem_u32(sTV(st));
+        const uint32_t acc0 = it > 0;
+#pragma unroll
+        for (int k = 0; k < C::BN / 16; ++k) {
+          const uint64_t dV = desc_mnmajor_sw128(bV + k * 2048, C::BN * 128);
+          umma_ts(tmem + C::TMEM_O, P_t + k * 8, dV, idesc_pv, acc0 | (k > 0));
+          if constexpr (DUAL) {
+            const uint64_t dTV = desc_mnmajor_sw128(bTV + k * 2048, C::BN * 128);
+            umma_ts(tmem + C::TMEM_T, W_t + k * 8, dV, idesc_pv, acc0 | (k > 0));
+            umma_ts(tmem + C::TMEM_T, P_t + k * 8, dTV, idesc_pv, 1);
+          }
+        }
+        umma_commit(&v_empty[st]);
+        umma_commit(&o_done);
+        if (last) umma_commit(&o_final);
+      };
+
+      mbar_wait(&q_full, 0, w, 23);
+      int it = 0;
+      for (int j = 0; j < n_kt; ++j) {
+        if (!(tile_bits(j) & kTileAnyKept)) continue;
+        issue_qk(it);
+        if (it > 0) issue_pv(it - 1, false);
+        ++it;
+      }
+      if (it > 0) issue_pv(it - 1, true);
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ softmax, correction, epilogue
+    const int r = warp * 32 + lane;
+    const int qi = q0 + r;
+    const int qi_c = min(qi, N - 1);
+    const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
+    float m_used = -INFINITY, l = 0.f, mu = 0.f;
+    int it = 0;
+    for (int j = 0; j < n_kt; ++j) {
+      const uint8_t bits = tile_bits(j);
+      if (!(bits & kTileAnyKept)) continue;
+      const uint32_t S_t = tmem + C::TMEM_S + (it & 1) * 128 + lane_off;
+      const uint32_t tS_t = S_t + 64;
+      mbar_wait(&s_full[it & 1], (it >> 1) & 1, w, 30);
+      tc_fence_after_sync();
+      float x[64];
+      {
+        uint32_t r0[32], r1[32];
+        tmem_ld_x32(S_t, r0);
+        tmem_ld_x32(S_t + 32, r1);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          x[i] = __uint_as_float(r0[i]) * p.c1;
+          x[32 + i] = __uint_as_float(r1[i]) * p.c1;
+        }
+      }
+      const int k0 = j * C::BN;
+      if (p.causal && k0 + C::BN - 1 > q0) {
+#pragma unroll
+        for (int i = 0; i < 64; ++i)
+          if (k0 + i > qi) x[i] = -INFINITY;
+      }
+      if (k0 + C::BN > N) {
+#pragma unroll
+        for (int i = 0; i < 64; ++i)
+          if (k0 + i >= N) x[i] = -INFINITY;
+      }
+      if (p.mv.kind != JVPFA_MASK_NONE && (bits & kTileAnyMasked)) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          float bias[16];
+          mask_bias_run<16>(bias, p.mv, b, h, qi_c, k0 + 16 * c, N, true);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) x[16 * c + i] += bias[i];
+        }
+      }
+      float m_tile = x[0];
+#pragma unroll
+      for (int i = 1; i < 64; ++i) m_tile = fmaxf(m_tile, x[i]);
+      const float m_new = fmaxf(m_used, m_tile);
+      const bool need = m_new > m_used + p.thresh;
+      if (__any_sync(0xFFFFFFFFu, need)) {
+        const float alpha = (m_used == -INFINITY) ? 1.0f : fast_exp2(m_used - m_new);
+        if (it > 0) {
+          mbar_wait(&o_done, (it - 1) & 1, w, 31);
+          tc_fence_after_sync();
+#pragma unroll
+          for (int c = 0; c < (DUAL ? 2 : 1) * D / 32; ++c) {
+            uint32_t a[32];
+            tmem_ld_x32(tmem + lane_off + c * 32, a);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) a[i] = __float_as_uint(__uint_as_float(a[i]) * alpha);
+            tmem_st_x32(tmem + lane_off + c * 32, a);
+          }
+        }
+        l *= alpha;
+        mu *= alpha;
+        m_used = m_new;
+      }
+      const float m_eff = (m_used == -INFINITY) ? 0.f : m_used;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t ts[32];
+        if constexpr (DUAL) {
+          tmem_ld_x32(tS_t + 32 * c, ts);
+          tmem_wait_ld();
+        }
+        uint32_t pk[16], wk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float p0 = fast_exp2(x[32 * c + 2 * i] - m_eff);
+          const float p1 = fast_exp2(x[32 * c + 2 * i + 1] - m_eff);
+          l += p0 + p1;
+          pk[i] = pack2<BF16>(p0, p1);
+          if constexpr (DUAL) {
+            const float w0 = p0 * (__uint_as_float(ts[2 * i]) * p.s);
+            const float w1 = p1 * (__uint_as_float(ts[2 * i + 1]) * p.s);
+            mu += w0 + w1;
+            wk[i] = pack2<BF16>(w0, w1);
+          }
+        }
+        tmem_st_x16(S_t + 16 * c, pk);
+        if constexpr (DUAL) tmem_st_x16(tS_t + 16 * c, wk);
+      }
+      tmem_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive(&p_full[it & 1]);
+      ++it;
+    }
+    // epilogue
+    // o_done flips once per key tile and a parity wait is only meaningful within one phase of the
+    // barrier, so the end of the last accumulation has a barrier of its own.
+    if (it > 0) {
+      mbar_wait(&o_final, 0, w, 32);
+      tc_fence_after_sync();
+    }
+    const float linv = (l > 0.f) ? 1.0f / l : 0.f;
+    const float mul = mu * linv;
+    const size_t orow = (static_cast<size_t>(row_base) + qi) * D;
+#pragma unroll
+    for (int c = 0; c < D / 32; ++c) {
+      uint32_t ov[32], tv[32];
+      if (it > 0) {
+        tmem_ld_x32(tmem + lane_off + C::TMEM_O + c * 32, ov);
+        if constexpr (DUAL) tmem_ld_x32(tmem + lane_off + C::TMEM_T + c * 32, tv);
+        tmem_wait_ld();
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) { ov[i] = 0u; tv[i] = 0u; }
+      }
+      uint32_t po[16], pt[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float o0 = __uint_as_float(ov[2 * i]) * linv, o1 = __uint_as_float(ov[2 * i + 1]) * linv;
+        po[i] = pack2<BF16>(o0, o1);
+        if constexpr (DUAL) {
+          const float t0 = __uint_as_float(tv[2 * i]) * linv - mul * o0;
+          const float t1 = __uint_as_float(tv[2 * i + 1]) * linv - mul * o1;
+          pt[i] = pack2<BF16>(t0, t1);
+        }
+      }
+      if (qi < N) {
+        uint4* op = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.o) + orow + c * 32);
+#pragma unroll
+        for (int v4 = 0; v4 < 4; ++v4) op[v4] = make_uint4(po[4 * v4], po[4 * v4 + 1], po[4 * v4 + 2], po[4 * v4 + 3]);
+        if constexpr (DUAL) {
+          uint4* tp = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.to) + orow + c * 32);
+#pragma unroll
+          for (int v4 = 0; v4 < 4; ++v4) tp[v4] = make_uint4(pt[4 * v4], pt[4 * v4 + 1], pt[4 * v4 + 2], pt[4 * v4 + 3]);
+        }
+      }
+    }
+    if (qi < N) {
+      p.lse2[static_cast<size_t>(row_base) + qi] = (l > 0.f) ? m_used + log2f(l) : -INFINITY;
+      p.mu[static_cast<size_t>(row_base) + qi] = mul;
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 5) tmem_dealloc(tmem, C::TMEM_COLS);
+}
+
+template <int D, bool DUAL, bool BF16>
+int launch_one(const jvpfa_fwd_args& a, cudaStream_t stream) {
+  using C = FwdCfg<D>;
+  const uint64_t rows = static_cast<uint64_t>(a.B) * a.H * a.N;
+  CUtensorMap mQ, mTQ, mK, mTK, mV, mTV;
+  bool ok = make_tile_map(&mQ, a.q, rows, D, C::BM, a.dtype) && make_tile_map(&mK, a.k, rows, D, C::BN, a.dtype) &&
+            make_tile_map(&mV, a.v, rows, D, C::BN, a.dtype);
+  if (DUAL) {
+    ok = ok && make_tile_map(&mTQ, a.tq, rows, D, C::BM, a.dtype) && make_tile_map(&mTK, a.tk, rows, D, C::BN, a.dtype) &&
+         make_tile_map(&mTV, a.tv, rows, D, C::BN, a.dtype);
+  } else {
+    mTQ = mQ; mTK = mK; mTV = mV;
+  }
+  if (!ok) return JVPFA_ERR_LAUNCH;
+  FwdKParams p{};
+  p.H = a.H; p.N = a.N; p.causal = a.causal;
+  p.s = a.sm_scale;
+  p.c1 = a.sm_scale * 1.4426950408889634f;
+  p.thresh = BF16 ? 8.0f : 6.0f;
+  p.mv.ptr = a.mask.ptr; p.mv.summary = a.mask_summary;
+  p.mv.s0 = a.mask.stride[0]; p.mv.s1 = a.mask.stride[1]; p.mv.s2 = a.mask.stride[2]; p.mv.s3 = a.mask.stride[3];
+  p.mv.kind = a.mask.kind; p.mv.dtype = a.mask.dtype;
+  p.mv.n64 = (a.N + 63) / 64;
+  p.mv.Hm = a.mask.stride[1] == 0 ? 1 : a.H;
+  p.o = a.o; p.to = a.to; p.lse2 = a.lse2; p.mu = a.mu;
+  p.status = static_cast<int*>(a.workspace);
+  p.budget_ns = wait_budget_ns();
+  auto kern = fwd_sm100_kernel<D, DUAL, BF16>;
+  const size_t smem = C::smem_bytes(DUAL);
+  static bool attr_set = false;  // per template instance
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
+      return JVPFA_ERR_LAUNCH;
+    attr_set = true;
+  }
+  dim3 grid((a.N + C::BM - 1) / C::BM, a.B * a.H);
+  kern<<<grid, 192, smem, stream>>>(mQ, mTQ, mK, mTK, mV, mTV, p);
+  return cudaGetLastError() == cudaSuccess ? JVPFA_OK : JVPFA_ERR_LAUNCH;
+}
+
+}  // namespace
+
+bool sm100_path_supported(int dtype, int D, int N) {
+  return (dtype == JVPFA_BF16 || dtype == JVPFA_F16) && (D == 64 || D == 128) && N >= 1;
+}
+
+int launch_fwd_sm100(const jvpfa_fwd_args& a, cudaStream_t stream) {
+  const bool dual = a.tq != nullptr;
+  const bool bf = a.dtype == JVPFA_BF16;
+  if (a.D == 64) {
+    if (dual) return bf ? launch_one<64, true, true>(a, stream) : launch_one<64, true, false>(a, stream);
+    return bf ? launch_one<64, false, true>(a, stream) : launch_one<64, false, false>(a, stream);
+  }
+  if (dual) return bf ? launch_one<128, true, true>(a, stream) : launch_one<128, true, false>(a, stream);
+  return bf ? launch_one<128, false, true>(a, stream) : launch_one<128, false, false>(a, stream);
+}
+
+}  // namespace jvpfa

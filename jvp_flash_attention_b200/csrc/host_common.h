@@ -1,0 +1,41 @@
+// Host-side helpers shared by the launchers: TMA tensor-map encoding through the driver entry
+// point (the library does not link libcuda), the device status word, small utilities.
+#pragma once
+#include <cstdint>
+#include <cstdio>
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include "../../include/jvpfa.h"
+
+namespace jvpfa {
+
+typedef CUresult (*TensorMapEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                      const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                      CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+TensorMapEncodeFn tensor_map_encoder();
+
+// A (rows x D) matrix of 16-bit elements, D a multiple of 64, viewed as (64, rows, D/64) so that
+// one TMA copy of box (64, box_rows, D/64) lands in shared memory as D/64 slabs of
+// [box_rows][64 elements], each slab in the 128-byte-swizzled layout the MMA descriptors expect.
+// Returns false if the driver rejects the encoding.
+bool make_tile_map(CUtensorMap* out, const void* base, uint64_t rows, int D, int box_rows, int dtype);
+
+// Wait budget of a single device-side mbarrier wait, in nanoseconds (JVPFA_WAIT_BUDGET_MS, default 4000 ms).
+uint64_t wait_budget_ns();
+
+inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// Workspace layout shared by forward and backward: [0,256) status word + padding, then per-call scratch.
+constexpr size_t kStatusBytes = 256;
+
+int launch_fwd_sm100(const jvpfa_fwd_args& a, cudaStream_t stream);
+int launch_bwd_sm100(const jvpfa_bwd_args& a, cudaStream_t stream);
+size_t bwd_sm100_workspace_bytes(const jvpfa_bwd_args& a);
+bool sm100_path_supported(int dtype, int D, int N);
+
+int launch_fwd_generic(const jvpfa_fwd_args& a, cudaStream_t stream);
+int launch_bwd_generic(const jvpfa_bwd_args& a, cudaStream_t stream);
+size_t bwd_generic_workspace_bytes(const jvpfa_bwd_args& a);
+
+}  // namespace jvpfa

@@ -1,0 +1,206 @@
+// C ABI of libjvpfa.so: argument validation, kernel-family selection by shape, the mask-summary
+// pre-pass, status read-back. See include/jvpfa.h for the contract of each entry point.
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include "host_common.h"
+#include "mask_common.cuh"
+
+namespace jvpfa {
+
+TensorMapEncodeFn tensor_map_encoder() {
+  static TensorMapEncodeFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &p, 12000, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<TensorMapEncodeFn>(p);
+  });
+  return fn;
+}
+
+bool make_tile_map(CUtensorMap* out, const void* base, uint64_t rows, int D, int box_rows, int dtype) {
+  TensorMapEncodeFn enc = tensor_map_encoder();
+  if (enc == nullptr || base == nullptr) return false;
+  const cuuint64_t dims[3] = {64, rows, static_cast<cuuint64_t>(D / 64)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(D) * 2, 128};
+  const cuuint32_t box[3] = {64, static_cast<cuuint32_t>(box_rows), static_cast<cuuint32_t>(D / 64)};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUtensorMapDataType dt = dtype == JVPFA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  return enc(out, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+uint64_t wait_budget_ns() {
+  static uint64_t ns = [] {
+    const char* e = std::getenv("JVPFA_WAIT_BUDGET_MS");
+    const long ms = e ? std::atol(e) : 4000;
+    return static_cast<uint64_t>(ms > 0 ? ms : 4000) * 1000000ull;
+  }();
+  return ns;
+}
+
+namespace {
+
+// One CTA per (plane, 64-row band): thread t scans mask rows and ORs per-64-column-tile bits.
+__global__ void mask_summary_kernel(MaskView mv, int N, int Bm, uint8_t* out) {
+  const int qt = blockIdx.x;
+  const int plane = blockIdx.y;
+  const int bm = plane / mv.Hm, hm = plane % mv.Hm;
+  extern __shared__ uint32_t bits[];  // n64 words
+  for (int i = threadIdx.x; i < mv.n64; i += blockDim.x) bits[i] = 0;
+  __syncthreads();
+  const int64_t plane_off = bm * mv.s0 + hm * mv.s1;
+  // each warp takes rows, lanes stride over columns
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  for (int r = warp; r < 64; r += nwarps) {
+    const int q = qt * 64 + r;
+    if (q >= N) break;
+    for (int kt = 0; kt < mv.n64; ++kt) {
+      uint32_t local = 0;
+      for (int c = lane; c < 64; c += 32) {
+        const int k = kt * 64 + c;
+        if (k >= N) continue;
+        const int64_t idx = plane_off + static_cast<int64_t>(q) * mv.s2 + static_cast<int64_t>(k) * mv.s3;
+        bool kept;
+        if (mv.kind == JVPFA_MASK_BOOL) kept = static_cast<const uint8_t*>(mv.ptr)[idx] != 0;
+        else kept = mask_elem_as_float(mv.ptr, idx, mv.dtype) != -INFINITY;
+        local |= kept ? kTileAnyKept : kTileAnyMasked;
+      }
+      local |= __shfl_xor_sync(0xFFFFFFFFu, local, 16);
+      local |= __shfl_xor_sync(0xFFFFFFFFu, local, 8);
+      local |= __shfl_xor_sync(0xFFFFFFFFu, local, 4);
+      local |= __shfl_xor_sync(0xFFFFFFFFu, local, 2);
+      local |= __shfl_xor_sync(0xFFFFFFFFu, local, 1);
+      if (lane == 0 && local) atomicOr(&bits[kt], local);
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < mv.n64; i += blockDim.x)
+    out[(static_cast<int64_t>(plane) * mv.n64 + qt) * mv.n64 + i] = static_cast<uint8_t>(bits[i]);
+  (void)Bm;
+}
+
+int check_common(int B, int H, int N, int D, int dtype, int causal, const jvpfa_mask& mask, const void* ws, size_t ws_bytes,
+                 size_t ws_need) {
+  if (B <= 0 || H <= 0 || N <= 0 || D <= 0) return JVPFA_ERR_BAD_ARG;
+  if (dtype != JVPFA_F16 && dtype != JVPFA_BF16 && dtype != JVPFA_F32) return JVPFA_ERR_UNSUPPORTED;
+  if (causal && mask.kind != JVPFA_MASK_NONE) return JVPFA_ERR_CAUSAL_MASK;
+  if (mask.kind != JVPFA_MASK_NONE) {
+    if (mask.ptr == nullptr) return JVPFA_ERR_BAD_ARG;
+    if (mask.kind != JVPFA_MASK_BOOL && mask.kind != JVPFA_MASK_ADDITIVE) return JVPFA_ERR_BAD_ARG;
+    if (mask.kind == JVPFA_MASK_ADDITIVE && mask.dtype != JVPFA_F16 && mask.dtype != JVPFA_BF16 && mask.dtype != JVPFA_F32)
+      return JVPFA_ERR_UNSUPPORTED;
+  }
+  if (ws == nullptr || ws_bytes < ws_need) return JVPFA_ERR_WORKSPACE;
+  if (static_cast<uint64_t>(B) * H * N >= (1ull << 31)) return JVPFA_ERR_UNSUPPORTED;
+  return JVPFA_OK;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace
+}  // namespace jvpfa
+
+using namespace jvpfa;
+
+extern "C" {
+
+int jvpfa_version(void) { return 100; }
+
+const char* jvpfa_error_string(int status) {
+  switch (status) {
+    case JVPFA_OK: return "ok";
+    case JVPFA_ERR_BAD_ARG: return "bad argument (null pointer, non-positive size or misaligned pointer)";
+    case JVPFA_ERR_UNSUPPORTED: return "unsupported shape or dtype";
+    case JVPFA_ERR_CAUSAL_MASK: return "causal attention does not support an attention mask";
+    case JVPFA_ERR_WORKSPACE: return "workspace missing or too small";
+    case JVPFA_ERR_LAUNCH: return "CUDA launch or tensor-map encoding failed";
+    case JVPFA_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait gave up";
+    case JVPFA_ERR_NO_ALLOC_LIMIT: return "problem exceeds the fixed scratch of the allocation-free entry point";
+    default: return "unknown status";
+  }
+}
+
+size_t jvpfa_fwd_workspace_bytes(const jvpfa_fwd_args* args) {
+  (void)args;
+  return kStatusBytes;
+}
+
+size_t jvpfa_bwd_workspace_bytes(const jvpfa_bwd_args* a) {
+  if (a == nullptr) return kStatusBytes;
+  if (sm100_path_supported(a->dtype, a->D, a->N)) return bwd_sm100_workspace_bytes(*a);
+  return bwd_generic_workspace_bytes(*a);
+}
+
+size_t jvpfa_mask_summary_bytes(int32_t Bm, int32_t Hm, int32_t N) {
+  const size_t n64 = (static_cast<size_t>(N) + 63) / 64;
+  return static_cast<size_t>(Bm) * Hm * n64 * n64;
+}
+
+int jvpfa_mask_summary(const jvpfa_mask* mask, int32_t B, int32_t H, int32_t N, uint8_t* summary, void* stream) {
+  if (mask == nullptr || summary == nullptr || mask->ptr == nullptr || B <= 0 || H <= 0 || N <= 0) return JVPFA_ERR_BAD_ARG;
+  if (mask->kind != JVPFA_MASK_BOOL && mask->kind != JVPFA_MASK_ADDITIVE) return JVPFA_ERR_BAD_ARG;
+  MaskView mv{};
+  mv.ptr = mask->ptr; mv.summary = nullptr;
+  mv.s0 = mask->stride[0]; mv.s1 = mask->stride[1]; mv.s2 = mask->stride[2]; mv.s3 = mask->stride[3];
+  mv.kind = mask->kind; mv.dtype = mask->dtype;
+  mv.n64 = (N + 63) / 64;
+  mv.Hm = mask->stride[1] == 0 ? 1 : H;
+  const int Bm = mask->stride[0] == 0 ? 1 : B;
+  dim3 grid(mv.n64, Bm * mv.Hm);
+  mask_summary_kernel<<<grid, 256, mv.n64 * sizeof(uint32_t), static_cast<cudaStream_t>(stream)>>>(mv, N, Bm, summary);
+  return cudaGetLastError() == cudaSuccess ? JVPFA_OK : JVPFA_ERR_LAUNCH;
+}
+
+int jvpfa_fwd(const jvpfa_fwd_args* a, void* stream) {
+  if (a == nullptr) return JVPFA_ERR_BAD_ARG;
+  int rc = check_common(a->B, a->H, a->N, a->D, a->dtype, a->causal, a->mask, a->workspace, a->workspace_bytes,
+                        jvpfa_fwd_workspace_bytes(a));
+  if (rc != JVPFA_OK) return rc;
+  if (!a->q || !a->k || !a->v || !a->o || !a->lse2 || !a->mu) return JVPFA_ERR_BAD_ARG;
+  const bool dual = a->tq != nullptr;
+  if (dual && (!a->tk || !a->tv || !a->to)) return JVPFA_ERR_BAD_ARG;
+  if (!dual && (a->tk || a->tv)) return JVPFA_ERR_BAD_ARG;
+  if (!aligned16(a->q) || !aligned16(a->k) || !aligned16(a->v) || !aligned16(a->o) ||
+      (dual && (!aligned16(a->tq) || !aligned16(a->tk) || !aligned16(a->tv) || !aligned16(a->to))))
+    return JVPFA_ERR_BAD_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (sm100_path_supported(a->dtype, a->D, a->N)) return launch_fwd_sm100(*a, s);
+  return launch_fwd_generic(*a, s);
+}
+
+int jvpfa_bwd(const jvpfa_bwd_args* a, void* stream) {
+  if (a == nullptr) return JVPFA_ERR_BAD_ARG;
+  int rc = check_common(a->B, a->H, a->N, a->D, a->dtype, a->causal, a->mask, a->workspace, a->workspace_bytes,
+                        jvpfa_bwd_workspace_bytes(a));
+  if (rc != JVPFA_OK) return rc;
+  if (!a->q || !a->k || !a->v || !a->tq || !a->tk || !a->tv || !a->o || !a->to || !a->lse2 || !a->mu || !a->go ||
+      !a->dq || !a->dk || !a->dv || !a->dtq || !a->dtk || !a->dtv)
+    return JVPFA_ERR_BAD_ARG;
+  const void* ptrs[] = {a->q, a->k, a->v, a->tq, a->tk, a->tv, a->o, a->to, a->go, a->gto, a->dq, a->dk, a->dv, a->dtq, a->dtk, a->dtv};
+  for (const void* p : ptrs)
+    if (!aligned16(p)) return JVPFA_ERR_BAD_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (sm100_path_supported(a->dtype, a->D, a->N)) return launch_bwd_sm100(*a, s);
+  return launch_bwd_generic(*a, s);
+}
+
+int jvpfa_read_status(void* workspace, void* stream, int32_t* detail) {
+  if (workspace == nullptr) return JVPFA_ERR_BAD_ARG;
+  int32_t word = 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (cudaMemcpyAsync(&word, workspace, 4, cudaMemcpyDeviceToHost, s) != cudaSuccess) return JVPFA_ERR_LAUNCH;
+  if (cudaStreamSynchronize(s) != cudaSuccess) return JVPFA_ERR_LAUNCH;
+  if (detail) *detail = word;
+  if (word != 0) {
+    cudaMemsetAsync(workspace, 0, 4, s);
+    return JVPFA_ERR_DEVICE_TIMEOUT;
+  }
+  return JVPFA_OK;
+}
+
+}  // extern "C"
