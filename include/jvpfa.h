@@ -67,7 +67,7 @@ typedef struct jvpfa_fwd_args {
  * _attn_bwd_preprocess + _attn_bwd / _attn_bwd_causal in JVPAttn.backward
  * (jvp_attention.py:3171, 3189), and adds what the reference leaves out: the gradient through
  * the tangent output and the tangent-input gradients (jvp_attention.py:3081, 3226).
- * gto == NULL means a zero upstream gradient for the tangent output. */
+ * All pointers are required; pass a zero tensor as gto when only the primal output has a gradient. */
 typedef struct jvpfa_bwd_args {
   int32_t B, H, N, D;
   int32_t dtype;

@@ -178,7 +178,7 @@ int jvpfa_bwd(const jvpfa_bwd_args* a, void* stream) {
   int rc = check_common(a->B, a->H, a->N, a->D, a->dtype, a->causal, a->mask, a->workspace, a->workspace_bytes,
                         jvpfa_bwd_workspace_bytes(a));
   if (rc != JVPFA_OK) return rc;
-  if (!a->q || !a->k || !a->v || !a->tq || !a->tk || !a->tv || !a->o || !a->to || !a->lse2 || !a->mu || !a->go ||
+  if (!a->q || !a->k || !a->v || !a->tq || !a->tk || !a->tv || !a->o || !a->to || !a->lse2 || !a->mu || !a->go || !a->gto ||
       !a->dq || !a->dk || !a->dv || !a->dtq || !a->dtk || !a->dtv)
     return JVPFA_ERR_BAD_ARG;
   const void* ptrs[] = {a->q, a->k, a->v, a->tq, a->tk, a->tv, a->o, a->to, a->go, a->gto, a->dq, a->dk, a->dv, a->dtq, a->dtk, a->dtv};

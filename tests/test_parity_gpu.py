@@ -1,0 +1,278 @@
+"""GPU parity tests: the CUDA path, called through the Python mirror of the reference API and the
+C ABI underneath it, against the CPU oracle on the same seeded inputs.
+
+Tolerances (max abs error against the fp64 oracle fed the rounded inputs): 2e-2 for fp16 / bf16,
+1e-4 for fp32 -- for O, tO and all six gradients.
+"""
+import math
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+import torch.autograd.forward_ad as fwAD
+
+from oracle.jvp_attention_oracle import (GRAD_NAMES, closed_form_oracle, make_additive_mask, make_block_sparse_mask,
+                                         make_bool_mask, make_inputs, sdpa_jvp_oracle)
+
+pytestmark = pytest.mark.gpu
+GOLDEN = Path(__file__).resolve().parent / "golden"
+TOL = {torch.float16: 2e-2, torch.bfloat16: 2e-2, torch.float32: 1e-4}
+
+
+@pytest.fixture(scope="module")
+def dev():
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    return torch.device("cuda:0")
+
+
+def _api():
+    from jvp_flash_attention_b200.jvp_attention import JVPAttn, attention
+    return JVPAttn, attention
+
+
+def _run_cuda(ts, dev, attn_mask=None, causal=False, sm_scale=None, how="dual_level"):
+    """Runs the dual forward + backward through the public API; returns dict of CPU fp64 tensors."""
+    from jvp_flash_attention_b200 import _lib
+    JVPAttn, _ = _api()
+    q, k, v, tq, tk, tv, gO, gtO = [t.to(dev) for t in ts]
+    mask = None if attn_mask is None else attn_mask.to(dev)
+    leaves = [t.clone().requires_grad_(True) for t in (q, k, v, tq, tk, tv)]
+    kw = dict(attn_mask=mask, causal=causal, sm_scale=sm_scale)
+    if how == "dual_level":
+        with fwAD.dual_level():
+            duals = [fwAD.make_dual(leaves[i], leaves[i + 3]) for i in range(3)]
+            out = JVPAttn.fwd_dual(*duals, **kw)
+            O, tO = fwAD.unpack_dual(out)
+            grads = torch.autograd.grad((O * gO).sum() + (tO * gtO).sum(), leaves)
+    elif how == "func_jvp":
+        O, tO = torch.func.jvp(lambda a, b, c: JVPAttn.fwd_dual(a, b, c, **kw), tuple(leaves[:3]), tuple(leaves[3:]))
+        grads = torch.autograd.grad((O * gO).sum() + (tO * gtO).sum(), leaves)
+    else:
+        O, tO = JVPAttn.dual(*leaves, **kw)
+        grads = torch.autograd.grad((O * gO).sum() + (tO * gtO).sum(), leaves)
+    torch.cuda.synchronize()
+    _lib.read_status(dev)
+    out = {"O": O.detach(), "tO": tO.detach()}
+    out.update({n: g for n, g in zip(GRAD_NAMES, grads)})
+    return {n: t.double().cpu() for n, t in out.items()}
+
+
+def _compare(got, ref, tol, slices=None, names=("O", "tO") + GRAD_NAMES):
+    worst = {}
+    for n in names:
+        r = ref[n]
+        r = torch.from_numpy(r) if isinstance(r, np.ndarray) else r
+        g = got[n]
+        if slices is not None:
+            g = torch.stack([g[b, h] for b, h in slices])
+        assert torch.isfinite(g).all(), f"{n} has non-finite values"
+        worst[n] = float((g - r).abs().max())
+    bad = {n: e for n, e in worst.items() if not e <= tol}
+    assert not bad, f"max abs error over tolerance {tol}: {bad} (all: {worst})"
+    return worst
+
+
+# ------------------------------------------------------------------ the benchmark configurations
+def test_cfg1_fp32_cpu_reference_config(dev):
+    """fp32 B=2 H=4 N=128 D=64, no mask: against the SDPA oracle and against the stored golden outputs."""
+    ts = make_inputs(2, 4, 128, 64, dtype=torch.float32, seed=42)
+    got = _run_cuda(ts, dev)
+    ref = sdpa_jvp_oracle(*ts)
+    _compare(got, ref, TOL[torch.float32])
+    g = np.load(GOLDEN / "sdpa_cfg1.npz")
+    for n in ("O", "tO") + GRAD_NAMES:
+        assert float((got[n][:, :, ::5, :] - torch.from_numpy(g[n]).double()).abs().max()) <= 1e-4, n
+
+
+@pytest.mark.parametrize("how", ["dual_level", "func_jvp", "explicit"])
+def test_cfg2_bf16_dense(dev, how):
+    """bf16 B=4 H=16 N=2048 D=64 dense, inputs scaled by D^-1/4; a seeded subset of (b,h) slices."""
+    B, H, N, D = 4, 16, 2048, 64
+    ts = make_inputs(B, H, N, D, dtype=torch.bfloat16, seed=42, scale=D ** -0.25)
+    got = _run_cuda(ts, dev, how=how)
+    slices = [(0, 0), (3, 15), (1, 7)]
+    ref = closed_form_oracle(*ts, slices=slices)
+    _compare(got, ref, TOL[torch.bfloat16], slices)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_cfg3_causal_headline_shape(dev, dtype):
+    """B=8 H=16 N=4096 D=128 causal; first and last (b,h) slice against the oracle."""
+    B, H, N, D = 8, 16, 4096, 128
+    scale = 1.0
+    ts = make_inputs(B, H, N, D, dtype=dtype, seed=42, scale=scale)
+    got = _run_cuda(ts, dev, causal=True)
+    slices = [(0, 0), (7, 15)]
+    ref = closed_form_oracle(*ts, causal=True, slices=slices)
+    _compare(got, ref, TOL[dtype], slices)
+
+
+@pytest.mark.parametrize("kind", ["bool", "block_sparse", "additive"])
+def test_cfg4_masks_bf16(dev, kind):
+    B, H, N, D = 2, 8, 1024, 64
+    ts = make_inputs(B, H, N, D, dtype=torch.bfloat16, seed=42, scale=0.7)
+    mask = {"bool": make_bool_mask(B, N), "block_sparse": make_block_sparse_mask(B, N),
+            "additive": make_additive_mask(B, N, dtype=torch.bfloat16)}[kind]
+    got = _run_cuda(ts, dev, attn_mask=mask)
+    slices = [(0, 0), (1, 7), (0, 3)]
+    ref = closed_form_oracle(*ts, attn_mask=mask, slices=slices)
+    _compare(got, ref, TOL[torch.bfloat16], slices)
+
+
+@pytest.mark.parametrize("kind", ["bool", "additive"])
+def test_cfg4_masks_fp32(dev, kind):
+    B, H, N, D = 2, 8, 512, 64
+    ts = make_inputs(B, H, N, D, dtype=torch.float32, seed=42)
+    mask = make_bool_mask(B, N) if kind == "bool" else make_additive_mask(B, N, dtype=torch.float32)
+    got = _run_cuda(ts, dev, attn_mask=mask)
+    slices = [(0, 0), (1, 7)]
+    ref = closed_form_oracle(*ts, attn_mask=mask, slices=slices)
+    _compare(got, ref, TOL[torch.float32], slices)
+
+
+# ------------------------------------------------------------------ golden vectors of the reference's own kernels
+@pytest.mark.parametrize("case", ["none", "causal", "bool"])
+def test_golden_reference_interpreter(dev, case):
+    g = np.load(GOLDEN / f"reference_interp_{case}.npz")
+    ts = [torch.from_numpy(g[n]) for n in ("q", "k", "v", "tq", "tk", "tv", "gO")]
+    ts.append(torch.zeros_like(ts[0]))
+    kw = {"causal": True} if case == "causal" else {}
+    if case == "bool":
+        kw["attn_mask"] = torch.from_numpy(g["mask"])
+    got = _run_cuda(ts, dev, **kw)
+    for n in ("O", "tO", "dq", "dk", "dv"):
+        assert float((got[n] - torch.from_numpy(g[n]).double()).abs().max()) <= 1e-4, n
+
+
+# ------------------------------------------------------------------ shapes and edge cases
+@pytest.mark.parametrize("dtype,B,H,N,D,causal", [
+    (torch.bfloat16, 1, 2, 32, 64, False),     # MIN_SEQUENCE_LENGTH
+    (torch.float16, 1, 2, 32, 128, True),
+    (torch.bfloat16, 2, 3, 100, 64, True),     # ragged: N not a multiple of any tile
+    (torch.float16, 1, 2, 333, 128, False),
+    (torch.float32, 1, 2, 50, 32, True),
+    (torch.float32, 2, 2, 96, 128, False),
+    (torch.bfloat16, 1, 2, 256, 32, False),    # head dims off the tensor-core path
+    (torch.float16, 1, 2, 64, 16, True),
+    (torch.bfloat16, 1, 1, 256, 72, False),
+])
+def test_shapes(dev, dtype, B, H, N, D, causal):
+    # bf16 keeps 8 bits of mantissa: a gradient of magnitude >= 8 cannot be stored to within 2e-2, and short
+    # causal rows give such gradients for N(0,1) inputs, so the bf16 cases use inputs of half the scale.
+    ts = make_inputs(B, H, N, D, dtype=dtype, seed=N + D, scale=0.5 if dtype == torch.bfloat16 else 1.0)
+    got = _run_cuda(ts, dev, causal=causal)
+    ref = closed_form_oracle(*ts, causal=causal)
+    _compare(got, ref, TOL[dtype])
+
+
+def test_sm_scale_and_head_broadcast_mask(dev):
+    B, H, N, D = 2, 4, 192, 64
+    ts = make_inputs(B, H, N, D, dtype=torch.float16, seed=11)
+    mask = make_bool_mask(1, N).expand(B, H, N, N)          # broadcast over batch and heads, strides 0
+    got = _run_cuda(ts, dev, attn_mask=mask, sm_scale=0.2)
+    ref = closed_form_oracle(*ts, attn_mask=mask, sm_scale=0.2)
+    _compare(got, ref, TOL[torch.float16])
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_fully_masked_rows_and_tiles(dev, dtype):
+    """Rows with nothing to attend to give zero outputs and zero gradients (the reference sets l := 1)."""
+    B, H, N, D = 1, 2, 256, 64
+    ts = make_inputs(B, H, N, D, dtype=dtype, seed=5)
+    mask = make_bool_mask(B, N, keep=0.8)
+    mask[0, 0, 7, :] = False            # one dead row
+    mask[0, 0, 128:, :64] = False       # dead 64x64 tiles
+    got = _run_cuda(ts, dev, attn_mask=mask)
+    ref = closed_form_oracle(*ts, attn_mask=mask)
+    _compare(got, ref, TOL[dtype])
+    assert float(got["O"][0, :, 7].abs().max()) == 0.0 and float(got["dq"][0, :, 7].abs().max()) == 0.0
+
+
+def test_primal_only_attention_and_backward(dev):
+    """``attention`` (JVPAttn.fwd): output and dq, dk, dv against SDPA in fp64."""
+    _, attention = _api()
+    for dtype, D in ((torch.bfloat16, 128), (torch.float32, 64)):
+        q, k, v, _, _, _, gO, _ = make_inputs(2, 2, 256, D, dtype=dtype, seed=21)
+        leaves = [t.to(dev).requires_grad_(True) for t in (q, k, v)]
+        o = attention(*leaves, causal=True)
+        grads = torch.autograd.grad((o * gO.to(dev)).sum(), leaves)
+        ref = closed_form_oracle(q, k, v, torch.zeros_like(q), torch.zeros_like(q), torch.zeros_like(q), gO,
+                                 torch.zeros_like(q), causal=True)
+        got = {"O": o.detach().double().cpu(), "dq": grads[0].double().cpu(), "dk": grads[1].double().cpu(),
+               "dv": grads[2].double().cpu()}
+        _compare(got, ref, TOL[dtype], names=("O", "dq", "dk", "dv"))
+
+
+def test_partial_tangents_and_no_tangents(dev):
+    """Only q carries a tangent: k, v tangents default to zero; no dual input at all -> primal path."""
+    JVPAttn, _ = _api()
+    q, k, v, tq, _, _, _, _ = make_inputs(1, 2, 128, 64, dtype=torch.float16, seed=2)
+    z = torch.zeros_like(q)
+    with fwAD.dual_level():
+        out = JVPAttn.fwd_dual(fwAD.make_dual(q.to(dev), tq.to(dev)), k.to(dev), v.to(dev))
+        O, tO = fwAD.unpack_dual(out)
+        plain = JVPAttn.fwd_dual(q.to(dev), k.to(dev), v.to(dev))
+        assert fwAD.unpack_dual(plain).tangent is None
+    ref = closed_form_oracle(q, k, v, tq, z, z)
+    _compare({"O": O.double().cpu(), "tO": tO.double().cpu()}, ref, 2e-2, names=("O", "tO"))
+    assert float((plain.double().cpu() - torch.from_numpy(ref["O"])).abs().max()) <= 2e-2
+
+
+def test_error_behaviour_on_gpu(dev):
+    JVPAttn, attention = _api()
+    q = torch.randn(1, 2, 64, 64, device=dev, dtype=torch.bfloat16)
+    m = torch.ones(1, 2, 64, 64, dtype=torch.bool, device=dev)
+    with pytest.raises(ValueError):
+        attention(q, q, q, attn_mask=m, causal=True)
+    with pytest.raises(NotImplementedError):
+        JVPAttn.fwd_dual(q, q, q, dropout_p=0.5)
+    with pytest.raises(AssertionError):
+        attention(q, q, q, attn_mask=torch.zeros_like(m))       # all-False head
+    with pytest.raises(AssertionError):
+        attention(q, q, q, attn_mask=m[:, :, :32])              # wrong shape
+    from jvp_flash_attention_b200 import _lib
+    big = torch.randn(1, 1, 64, 256, device=dev, dtype=torch.bfloat16)
+    with pytest.raises(_lib.JvpfaError):
+        attention(big, big, big)                                 # head dim 256: no kernel
+
+
+# ------------------------------------------------------------------ size-independent properties at full size
+def test_properties_at_headline_size(dev):
+    """B=8 H=16 N=4096 D=128 fp16 causal: determinism, causality, head independence, tangent linearity."""
+    JVPAttn, _ = _api()
+    B, H, N, D = 8, 16, 4096, 128
+    g = torch.Generator(device=dev).manual_seed(0)
+    q, k, v, tq, tk, tv = [torch.randn(B, H, N, D, device=dev, dtype=torch.float16, generator=g) for _ in range(6)]
+    O1, T1 = JVPAttn.dual(q, k, v, tq, tk, tv, causal=True)
+    O2, T2 = JVPAttn.dual(q, k, v, tq, tk, tv, causal=True)
+    assert torch.equal(O1, O2) and torch.equal(T1, T2)                       # run twice: bit-equal
+    k2, v2 = k.clone(), v.clone()
+    k2[:, :, 3000:] = 0
+    v2[:, :, 3000:] += 1
+    O3, T3 = JVPAttn.dual(q, k2, v2, tq, tk, tv, causal=True)
+    assert torch.equal(O1[:, :, :3000], O3[:, :, :3000]) and torch.equal(T1[:, :, :3000], T3[:, :, :3000])  # causality
+    perm = torch.randperm(B * H, device=dev)
+    f = lambda t: t.reshape(B * H, N, D)[perm].reshape(B, H, N, D).contiguous()
+    O4, T4 = JVPAttn.dual(f(q), f(k), f(v), f(tq), f(tk), f(tv), causal=True)
+    assert torch.equal(f(O1), O4) and torch.equal(f(T1), T4)                  # (b,h) units are independent
+    O5, T5 = JVPAttn.dual(q, k, v, 2 * tq, 2 * tk, 2 * tv, causal=True)
+    assert torch.equal(O1, O5)
+    assert float((T5.float() - 2 * T1.float()).abs().max()) <= 2e-2          # tangent is linear in the tangents
+    Oz, Tz = JVPAttn.dual(q, k, v, torch.zeros_like(q), torch.zeros_like(q), torch.zeros_like(q), causal=True)
+    assert float(Tz.abs().max()) == 0.0 and torch.equal(Oz, O1)
+    from jvp_flash_attention_b200 import _lib
+    torch.cuda.synchronize()
+    _lib.read_status(dev)
+
+
+def test_backward_determinism_and_zero_upstream(dev):
+    JVPAttn, _ = _api()
+    ts = [t.to(dev) for t in make_inputs(2, 4, 512, 128, dtype=torch.bfloat16, seed=8)]
+    leaves = [t.clone().requires_grad_(True) for t in ts[:6]]
+    O, tO = JVPAttn.dual(*leaves, causal=True)
+    g1 = torch.autograd.grad((O * ts[6]).sum() + (tO * ts[7]).sum(), leaves, retain_graph=True)
+    g2 = torch.autograd.grad((O * ts[6]).sum() + (tO * ts[7]).sum(), leaves, retain_graph=True)
+    assert all(torch.equal(a, b) for a, b in zip(g1, g2))
+    g0 = torch.autograd.grad((O * 0).sum() + (tO * 0).sum(), leaves)
+    assert all(float(x.abs().max()) == 0.0 for x in g0)
