@@ -111,6 +111,14 @@ int jvpfa_bwd(const jvpfa_bwd_args* args, void* stream);
  * 100 + the id of the wait that gave up). */
 int jvpfa_read_status(void* workspace, void* stream, int32_t* detail);
 
+/* Per-kernel timing for benchmarks. Collects what was measured since the last call -- summed
+ * milliseconds and launch counts for the five kernel kinds, in the order forward, backward
+ * preprocess, backward family Q, K, V (either pointer may be NULL) -- waits for those launches
+ * to finish, and then switches measurement on (enable != 0) or off. While on, each launch is
+ * bracketed by CUDA events on its stream. Off by default. No reference counterpart (the reference
+ * times whole calls with perf_counter, tests/test_jvp_attention.py:116-143). */
+int jvpfa_kernel_timing(int enable, float* ms_out, int32_t* launches_out);
+
 #ifdef __cplusplus
 }
 #endif

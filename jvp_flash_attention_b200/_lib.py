@@ -30,6 +30,7 @@ EXPORTED_SYMBOLS = (
     "jvpfa_fwd",
     "jvpfa_bwd",
     "jvpfa_read_status",
+    "jvpfa_kernel_timing",
 )
 
 
@@ -108,6 +109,8 @@ def lib():
                 L.jvpfa_bwd.argtypes = [C.POINTER(BwdArgs), C.c_void_p]
                 L.jvpfa_read_status.restype = C.c_int
                 L.jvpfa_read_status.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_int32)]
+                L.jvpfa_kernel_timing.restype = C.c_int
+                L.jvpfa_kernel_timing.argtypes = [C.c_int, C.POINTER(C.c_float), C.POINTER(C.c_int32)]
                 _lib = L
     return _lib
 
@@ -229,3 +232,15 @@ def bwd(q, k, v, tq, tk, tv, o, to, lse2, mu, go, gto, mask_c: Mask, summary, ca
     a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
     check(lib().jvpfa_bwd(C.byref(a), stream_ptr(q.device)))
     return tuple(outs)
+
+
+KERNEL_NAMES = ("fwd", "bwd_preprocess", "bwd_q", "bwd_k", "bwd_v")
+
+
+def kernel_timing(enable: bool):
+    """Collects per-kernel milliseconds and launch counts measured since the last call, then switches
+    the measurement on or off. Returns {name: (total_ms, launches)}."""
+    ms = (C.c_float * 5)()
+    n = (C.c_int32 * 5)()
+    check(lib().jvpfa_kernel_timing(int(enable), ms, n))
+    return {name: (float(ms[i]), int(n[i])) for i, name in enumerate(KERNEL_NAMES)}

@@ -508,6 +508,7 @@ int launch_family(const jvpfa_bwd_args& a, const float4* stats, cudaStream_t str
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
     return JVPFA_ERR_LAUNCH;
   dim3 grid((a.N + C::BR - 1) / C::BR, a.B * a.H);
+  ScopedKernelTimer timer(FAM == FAM_Q ? KERNEL_BWD_Q : (FAM == FAM_K ? KERNEL_BWD_K : KERNEL_BWD_V), stream);
   kern<<<grid, 192, smem, stream>>>(rm[0], rm[1], rm[2], rm[3], cm[0], cm[1], cm[2], cm[3], p);
   return cudaGetLastError() == cudaSuccess ? JVPFA_OK : JVPFA_ERR_LAUNCH;
 }
@@ -518,9 +519,12 @@ int launch_all(const jvpfa_bwd_args& a, cudaStream_t stream) {
   float4* stats = reinterpret_cast<float4*>(static_cast<uint8_t*>(a.workspace) + kStatusBytes);
   const int warps_per_block = 8;
   const unsigned blocks = static_cast<unsigned>((rows + warps_per_block - 1) / warps_per_block);
+  {
+  ScopedKernelTimer timer(KERNEL_BWD_PREPROCESS, stream);
   bwd_preprocess_kernel<BF16><<<blocks, warps_per_block * 32, 0, stream>>>(
       static_cast<const uint16_t*>(a.o), static_cast<const uint16_t*>(a.to), static_cast<const uint16_t*>(a.go),
       static_cast<const uint16_t*>(a.gto), a.lse2, a.mu, stats, rows, D);
+  }
   if (cudaGetLastError() != cudaSuccess) return JVPFA_ERR_LAUNCH;
   int rc = launch_family<D, FAM_Q, BF16>(a, stats, stream);
   if (rc != JVPFA_OK) return rc;

@@ -427,13 +427,10 @@ int launch_one(const jvpfa_fwd_args& a, cudaStream_t stream) {
   p.budget_ns = wait_budget_ns();
   auto kern = fwd_sm100_kernel<D, DUAL, BF16>;
   const size_t smem = C::smem_bytes(DUAL);
-  static bool attr_set = false;  // per template instance
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
-      return JVPFA_ERR_LAUNCH;
-    attr_set = true;
-  }
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
+    return JVPFA_ERR_LAUNCH;
   dim3 grid((a.N + C::BM - 1) / C::BM, a.B * a.H);
+  ScopedKernelTimer timer(KERNEL_FWD, stream);
   kern<<<grid, 192, smem, stream>>>(mQ, mTQ, mK, mTK, mV, mTV, p);
   return cudaGetLastError() == cudaSuccess ? JVPFA_OK : JVPFA_ERR_LAUNCH;
 }

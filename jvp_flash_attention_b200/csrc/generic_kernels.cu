@@ -395,6 +395,7 @@ int fwd_typed(const jvpfa_fwd_args& a, cudaStream_t stream) {
   auto launch = [&](auto kern) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
       return JVPFA_ERR_LAUNCH;
+    ScopedKernelTimer timer(KERNEL_FWD, stream);
     kern<<<grid, NTHREADS, smem, stream>>>(static_cast<const T*>(a.q), static_cast<const T*>(a.k),
                                            static_cast<const T*>(a.v), static_cast<const T*>(a.tq),
                                            static_cast<const T*>(a.tk), static_cast<const T*>(a.tv),
@@ -436,6 +437,7 @@ int bwd_family(const jvpfa_bwd_args& a, const float4* stats, cudaStream_t stream
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
     return JVPFA_ERR_LAUNCH;
   dim3 grid((a.N + TB - 1) / TB, a.B * a.H);
+  ScopedKernelTimer timer(FAM == FAM_Q ? KERNEL_BWD_Q : (FAM == FAM_K ? KERNEL_BWD_K : KERNEL_BWD_V), stream);
   kern<<<grid, NTHREADS, smem, stream>>>(r[0], r[1], r[2], r[3], c[0], c[1], c[2], c[3], o0, o1, p);
   return cudaGetLastError() == cudaSuccess ? JVPFA_OK : JVPFA_ERR_LAUNCH;
 }
@@ -445,9 +447,12 @@ int bwd_typed(const jvpfa_bwd_args& a, cudaStream_t stream) {
   const int64_t rows = static_cast<int64_t>(a.B) * a.H * a.N;
   float4* stats = reinterpret_cast<float4*>(static_cast<uint8_t*>(a.workspace) + kStatusBytes);
   const unsigned blocks = static_cast<unsigned>((rows + 7) / 8);
+  {
+  ScopedKernelTimer timer(KERNEL_BWD_PREPROCESS, stream);
   generic_preprocess_kernel<T><<<blocks, 256, 0, stream>>>(static_cast<const T*>(a.o), static_cast<const T*>(a.to),
                                                          static_cast<const T*>(a.go), static_cast<const T*>(a.gto),
                                                          a.lse2, a.mu, stats, rows, a.D);
+  }
   if (cudaGetLastError() != cudaSuccess) return JVPFA_ERR_LAUNCH;
   int rc = bwd_family<T, NJ, FAM_Q>(a, stats, stream);
   if (rc != JVPFA_OK) return rc;

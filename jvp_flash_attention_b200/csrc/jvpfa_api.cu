@@ -3,6 +3,8 @@
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
+#include <utility>
+#include <vector>
 #include "host_common.h"
 #include "mask_common.cuh"
 
@@ -41,6 +43,34 @@ uint64_t wait_budget_ns() {
     return static_cast<uint64_t>(ms > 0 ? ms : 4000) * 1000000ull;
   }();
   return ns;
+}
+
+namespace {
+struct TimingState {
+  std::mutex mu;
+  bool enabled = false;
+  std::vector<std::pair<cudaEvent_t, cudaEvent_t>> pending[KERNEL_KINDS];
+};
+TimingState& timing() {
+  static TimingState t;
+  return t;
+}
+}  // namespace
+
+ScopedKernelTimer::ScopedKernelTimer(KernelKind kind, cudaStream_t stream) : kind_(kind), stream_(stream) {
+  TimingState& t = timing();
+  if (!t.enabled) return;
+  if (cudaEventCreate(&start_) != cudaSuccess) { start_ = nullptr; return; }
+  cudaEventRecord(start_, stream_);
+}
+ScopedKernelTimer::~ScopedKernelTimer() {
+  if (start_ == nullptr) return;
+  cudaEvent_t stop = nullptr;
+  if (cudaEventCreate(&stop) != cudaSuccess) { cudaEventDestroy(start_); return; }
+  cudaEventRecord(stop, stream_);
+  TimingState& t = timing();
+  std::lock_guard<std::mutex> g(t.mu);
+  t.pending[kind_].emplace_back(start_, stop);
 }
 
 namespace {
@@ -187,6 +217,29 @@ int jvpfa_bwd(const jvpfa_bwd_args* a, void* stream) {
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (sm100_path_supported(a->dtype, a->D, a->N)) return launch_bwd_sm100(*a, s);
   return launch_bwd_generic(*a, s);
+}
+
+int jvpfa_kernel_timing(int enable, float* ms_out, int32_t* launches_out) {
+  TimingState& t = timing();
+  std::lock_guard<std::mutex> g(t.mu);
+  for (int k = 0; k < KERNEL_KINDS; ++k) {
+    float total = 0.f;
+    int n = 0;
+    for (auto& ev : t.pending[k]) {
+      float ms = 0.f;
+      if (cudaEventSynchronize(ev.second) == cudaSuccess && cudaEventElapsedTime(&ms, ev.first, ev.second) == cudaSuccess) {
+        total += ms;
+        ++n;
+      }
+      cudaEventDestroy(ev.first);
+      cudaEventDestroy(ev.second);
+    }
+    t.pending[k].clear();
+    if (ms_out) ms_out[k] = total;
+    if (launches_out) launches_out[k] = n;
+  }
+  t.enabled = enable != 0;
+  return JVPFA_OK;
 }
 
 int jvpfa_read_status(void* workspace, void* stream, int32_t* detail) {
