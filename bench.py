@@ -161,7 +161,9 @@ def run_cuda(args, rank, world, local_rank):
     torch.cuda.set_device(dev)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    w = WORKLOAD
+    w = dict(WORKLOAD)
+    if args.batch:
+        w["B"] = args.batch
     B, H, N, D, causal = w["B"], w["H"], w["N"], w["D"], w["causal"]
     dtype = torch.bfloat16 if args.dtype == "bf16" else torch.float16
     s = D ** -0.5
@@ -307,6 +309,7 @@ def main():
     ap.add_argument("--dtype", choices=("bf16", "fp16"), default="bf16")
     ap.add_argument("--impl", choices=("cuda", "reference"), default="cuda")
     ap.add_argument("--ref-slices", type=int, default=2, help="(batch, head) slices per step of the reference arm")
+    ap.add_argument("--batch", type=int, default=None, help="override B of the workload (small profiler captures only)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
