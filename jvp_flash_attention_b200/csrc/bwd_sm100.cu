@@ -20,8 +20,8 @@
 // preprocess kernel. Family Q reads them per thread (thread = query row); families K and V stage
 // the 64 statistics of the current query tile in shared memory and read them as broadcasts.
 //
-// Roles as in the forward kernel: warps 0-3 element-wise (thread r = TMEM lane r), warp 4 TMA
-// producer, warp 5 MMA issuer. Column-side tiles flow through a ring of shared-memory slots in the
+// Roles: warps 0-7 element-wise as two warpgroups that split the 64 columns of every score tile
+// (thread = TMEM lane = one score row, 32 columns), warp 8 TMA producer, warp 9 MMA issuer. Column-side tiles flow through a ring of shared-memory slots in the
 // order in which the MMA issuer releases them (tiles only the score MMAs read come first).
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -35,6 +35,18 @@ using namespace sm100;
 namespace {
 
 enum { FAM_Q = 0, FAM_K = 1, FAM_V = 2 };
+
+// Optional cycle trace of CTA (0,0) for kernel tuning (compile with -DJVPFA_TRACE): role 0 = MMA issuer,
+// 1 / 2 = first lane of element-wise warpgroup 0 / 1; 8 time stamps per tile for the first 64 tiles.
+#ifdef JVPFA_TRACE
+__device__ long long g_bwd_trace[3 * 64 * 8];
+#define JVPFA_TR(role, it, k)                                                                        \
+  do {                                                                                               \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && (it) < 64) g_bwd_trace[((role)*64 + (it)) * 8 + (k)] = clock64(); \
+  } while (0)
+#else
+#define JVPFA_TR(role, it, k) do { } while (0)
+#endif
 
 struct BwdKParams {
   int H, N;
@@ -72,46 +84,64 @@ struct BwdCfg {
   static constexpr int BR = 128;                         // rows per CTA
   static constexpr int BC = 64;                          // columns per streamed tile
   static constexpr int NR = (FAM == FAM_V) ? 2 : 4;      // resident row-side operand tiles
-  static constexpr int NSLOT = (D == 128 && FAM != FAM_V) ? 6 : 8;
+  static constexpr int NA = 2;                           // buffers of the first column-side pair
+  static constexpr int NB = (FAM == FAM_V) ? 2 : 1;      // buffers of the second column-side pair
   static constexpr int TILE_R = BR * D * 2;
-  static constexpr int TILE_C = BC * D * 2;
+  static constexpr int PAIR = 2 * BC * D * 2;            // two stacked 64-row tiles = one 128-row operand
+  static constexpr int SLAB = 128 * 128;                 // bytes of one 64-column slab of a 128-row tile
+  static constexpr int HALF = BC * 128;                  // byte offset of the second tile inside a slab
   static constexpr int TMEM_ACC0 = 0;
   static constexpr int TMEM_ACC1 = D;
-  static constexpr int TMEM_T = 2 * D;                   // score tiles T0..T3, 64 columns each
+  static constexpr int TMEM_T = 2 * D;                   // score tiles, 64 columns each
   static constexpr int TMEM_COLS = 512;
-  static constexpr size_t smem_bytes() { return NR * TILE_R + NSLOT * TILE_C + 2 * BC * 16 + (6 + 2 * NSLOT) * 8; }
+  static constexpr int NBAR = 8 + 2 * NA + 2 * NB;
+  static constexpr size_t smem_bytes() { return NR * TILE_R + (NA + NB) * PAIR + 2 * BC * 16 + (NBAR + 2) * 8; }
 };
 
-// rmK: row-side tensor maps (box 128 rows); cmK: column-side tensor maps in ring (load) order.
-//  family Q: rm = Q, tQ, gO, gtO;  cm = V, tV, K, tK
-//  family K: rm = K, tK, V, tV;    cm = gO, gtO, Q, tQ
-//  family V: rm = K, tK, (unused); cm = Q, tQ, gO, gtO
+// Tensor maps: rmK = row-side operands (box of 128 rows, all slabs); cmK = column-side operands (box of
+// 64 rows, one 64-column slab), cm0/cm1 the first pair, cm2/cm3 the second pair:
+//  family Q: rm = Q, tQ, gO, gtO;  first pair (K, tK),  second pair (V, tV)
+//  family K: rm = K, tK, V, tV;    first pair (Q, tQ),  second pair (gO, gtO)
+//  family V: rm = K, tK;           first pair (Q, tQ),  second pair (gO, gtO)
+// The two tiles of a pair are stacked in shared memory as one 128-row operand, so that the score
+// products against it run as N = 128 MMAs:
+//  [S | R0 c1^T] = R0 [c0; c1]^T, then tS += R1 c0^T; and for families Q, K
+//  Q: [A | gtO tV^T] = gtO [V; tV]^T, X += gO V^T;    K: [V gO^T | A^T] = V [gO; gtO]^T, X^T += tV gtO^T.
+// Families Q and K keep one set of score tiles and overlap in two phases per tile: phase 1 reads S, tS
+// (which frees them for the next tile's products), phase 2 reads X, A and writes the 16-bit dS, dtS operands;
+// family V double-buffers S, tS.
 template <int D, int FAM, bool BF16>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant__ CUtensorMap rm1,
                  const __grid_constant__ CUtensorMap rm2, const __grid_constant__ CUtensorMap rm3,
                  const __grid_constant__ CUtensorMap cm0, const __grid_constant__ CUtensorMap cm1,
                  const __grid_constant__ CUtensorMap cm2, const __grid_constant__ CUtensorMap cm3,
                  const BwdKParams p) {
   using C = BwdCfg<D, FAM>;
-  constexpr int NS = C::NSLOT;
+  constexpr int NA = C::NA, NB = C::NB;
+  constexpr int SLABS = D / 64;
 
   // Everything lives in dynamic shared memory so that the 128-byte-swizzled tiles can start at its
   // 1024-byte-aligned base without alignment slack: tiles, then statistics, then barriers.
   extern __shared__ __align__(1024) uint8_t smem[];
   auto sR = [&](int i) { return smem + i * C::TILE_R; };
-  auto sSlot = [&](int k) { return smem + C::NR * C::TILE_R + k * C::TILE_C; };
-  uint8_t* tail = smem + C::NR * C::TILE_R + NS * C::TILE_C;
+  auto sA = [&](int k) { return smem + C::NR * C::TILE_R + k * C::PAIR; };
+  auto sB = [&](int k) { return smem + C::NR * C::TILE_R + (NA + k) * C::PAIR; };
+  uint8_t* tail = smem + C::NR * C::TILE_R + (NA + NB) * C::PAIR;
   float4(*stats_s)[C::BC] = reinterpret_cast<float4(*)[C::BC]>(tail);
   uint64_t* bars = reinterpret_cast<uint64_t*>(tail + 2 * C::BC * sizeof(float4));
   uint64_t& r_full = bars[0];
-  uint64_t& s_full = bars[1];
-  uint64_t& p_full = bars[2];
-  uint64_t& acc_final = bars[3];
-  uint64_t* c_full = bars + 4;
-  uint64_t* c_empty = bars + 4 + NS;
-  uint32_t& tmem_base_s = *reinterpret_cast<uint32_t*>(bars + 4 + 2 * NS);
-  int& poisoned = *reinterpret_cast<int*>(bars + 5 + 2 * NS);
+  uint64_t* st_full = bars + 1;   // [2] (family V uses both, Q/K only [0])
+  uint64_t* p_full = bars + 3;    // [2]
+  uint64_t& ph1_done = bars[5];
+  uint64_t& xa_full = bars[6];
+  uint64_t& acc_final = bars[7];
+  uint64_t* a_full = bars + 8;
+  uint64_t* a_empty = a_full + NA;
+  uint64_t* b_full = a_empty + NA;
+  uint64_t* b_empty = b_full + NB;
+  uint32_t& tmem_base_s = *reinterpret_cast<uint32_t*>(bars + C::NBAR);
+  int& poisoned = *reinterpret_cast<int*>(bars + C::NBAR + 1);
   if ((smem_u32(smem) & 1023u) != 0u) {  // the swizzled layouts need this; never observed otherwise
     if (threadIdx.x == 0) atomicCAS(p.status, 0, WAIT_TIMEOUT_BASE + 99);
     return;
@@ -138,17 +168,25 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
   if (tid == 0) {
     poisoned = 0;
     mbar_init(&r_full, 1);
-    for (int i = 0; i < NS; ++i) {
-      mbar_init(&c_full[i], 1);
-      mbar_init(&c_empty[i], 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&st_full[i], 1);
+      mbar_init(&p_full[i], 256);
     }
-    mbar_init(&s_full, 1);
-    mbar_init(&p_full, 128);
+    mbar_init(&ph1_done, 256);
+    mbar_init(&xa_full, 1);
     mbar_init(&acc_final, 1);
+    for (int i = 0; i < NA; ++i) {
+      mbar_init(&a_full[i], 1);
+      mbar_init(&a_empty[i], 1);
+    }
+    for (int i = 0; i < NB; ++i) {
+      mbar_init(&b_full[i], 1);
+      mbar_init(&b_empty[i], 1);
+    }
     fence_mbar_init();
   }
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 9) {
     tmem_alloc(&tmem_base_s, C::TMEM_COLS);
     tmem_relinquish();
   }
@@ -170,8 +208,13 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
     }
     return bits;
   };
+  // next column tile at or after j that takes part, or j_end
+  auto next_active = [&](int j) {
+    while (j < j_end && !(tile_bits(j) & kTileAnyKept)) ++j;
+    return j;
+  };
 
-  if (warp == 4) {
+  if (warp == 8) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       mbar_arrive_expect_tx(&r_full, C::NR * C::TILE_R);
@@ -181,105 +224,133 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
         tma_load_3d(sR(2), &rm2, &r_full, 0, row_base + r0, 0);
         tma_load_3d(sR(3), &rm3, &r_full, 0, row_base + r0, 0);
       }
-      const CUtensorMap* cms[4] = {&cm0, &cm1, &cm2, &cm3};
-      int g = 0;
-      for (int j = j_begin; j < j_end; ++j) {
-        if (!(tile_bits(j) & kTileAnyKept)) continue;
+      int it = 0;
+      for (int j = next_active(j_begin); j < j_end; j = next_active(j + 1), ++it) {
         const int crow = row_base + j * C::BC;
+        {
+          const int buf = it % NA;
+          mbar_wait(&a_empty[buf], ((it / NA) & 1) ^ 1, w, 10);
+          mbar_arrive_expect_tx(&a_full[buf], C::PAIR);
 #pragma unroll
-        for (int e = 0; e < 4; ++e, ++g) {
-          const int slot = g % NS;
-          const uint32_t ph = (g / NS) & 1;
-          mbar_wait(&c_empty[slot], ph ^ 1, w, 10 + e);
-          mbar_arrive_expect_tx(&c_full[slot], C::TILE_C);
-          tma_load_3d(sSlot(slot), cms[e], &c_full[slot], 0, crow, 0);
+          for (int sl = 0; sl < SLABS; ++sl) {
+            tma_load_3d(sA(buf) + sl * C::SLAB, &cm0, &a_full[buf], 0, crow, sl);
+            tma_load_3d(sA(buf) + sl * C::SLAB + C::HALF, &cm1, &a_full[buf], 0, crow, sl);
+          }
+        }
+        {
+          const int buf = it % NB;
+          mbar_wait(&b_empty[buf], ((it / NB) & 1) ^ 1, w, 11);
+          mbar_arrive_expect_tx(&b_full[buf], C::PAIR);
+#pragma unroll
+          for (int sl = 0; sl < SLABS; ++sl) {
+            tma_load_3d(sB(buf) + sl * C::SLAB, &cm2, &b_full[buf], 0, crow, sl);
+            tma_load_3d(sB(buf) + sl * C::SLAB + C::HALF, &cm3, &b_full[buf], 0, crow, sl);
+          }
         }
       }
     }
     __syncwarp();
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t FMT = BF16 ? FMT_BF16 : FMT_F16;
-      const uint32_t idesc_sc = make_idesc(FMT, 128, C::BC, 0, 0);
+      const uint32_t idesc_64 = make_idesc(FMT, 128, 64, 0, 0);
+      const uint32_t idesc_128 = make_idesc(FMT, 128, 128, 0, 0);
       const uint32_t idesc_out = make_idesc(FMT, 128, D, 0, 1);
-      const uint32_t T0 = tmem + C::TMEM_T, T1 = T0 + 64, T2 = T0 + 128, T3 = T0 + 192;
-      const uint32_t E0 = (FAM == FAM_V) ? T0 : T2, E1 = (FAM == FAM_V) ? T1 : T3;
+      const uint32_t TS0 = tmem + C::TMEM_T;
 
-      // dst[128 x 64] (+)= R[128 x D] * Cc[64 x D]^T
-      auto mma_nt = [&](uint32_t dst, const uint8_t* rtile, const uint8_t* ctile, uint32_t acc) {
+      // dst[128 x n] (+)= R[128 x D] * Cc[n x D]^T, Cc = n rows starting at `ctile` inside a pair buffer
+      auto mma_nt = [&](uint32_t dst, const uint8_t* rtile, const uint8_t* ctile, uint32_t idesc, uint32_t acc) {
         const uint32_t a = smem_u32(rtile), bb = smem_u32(ctile);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
-          const uint32_t oa = (k >> 2) * (C::BR * 128) + (k & 3) * 32;
-          const uint32_t ob = (k >> 2) * (C::BC * 128) + (k & 3) * 32;
-          umma_ss(dst, desc_kmajor_sw128(a + oa), desc_kmajor_sw128(bb + ob), idesc_sc, acc | (k > 0));
+          const uint32_t o = (k >> 2) * C::SLAB + (k & 3) * 32;
+          umma_ss(dst, desc_kmajor_sw128(a + o), desc_kmajor_sw128(bb + o), idesc, acc | (k > 0));
         }
       };
-      // acc[128 x D] (+)= E[128 x 64] (TMEM, 16-bit) * Cc[64 x D]
+      // acc[128 x D] (+)= E[128 x 64] (TMEM, 16-bit, two column groups of 16) * Cc[64 x D]
       auto mma_out = [&](uint32_t accum, uint32_t e, const uint8_t* ctile, uint32_t acc) {
         const uint32_t bb = smem_u32(ctile);
 #pragma unroll
         for (int k = 0; k < C::BC / 16; ++k)
-          umma_ts(accum, e + k * 8, desc_mnmajor_sw128(bb + k * 2048, C::BC * 128), idesc_out, acc | (k > 0));
+          umma_ts(accum, e + (k & 1) * 8 + (k >> 1) * 32, desc_mnmajor_sw128(bb + k * 2048, C::SLAB), idesc_out,
+                  acc | (k > 0));
+      };
+      // S, tS of tile i into score buffer sb
+      auto issue_st = [&](int i, int sb) {
+        const int buf = i % NA;
+        mbar_wait(&a_full[buf], (i / NA) & 1, w, 20);
+        tc_fence_after_sync();
+        const uint32_t T0 = TS0 + sb * 128;
+        mma_nt(T0, sR(0), sA(buf), idesc_128, 0);        // [S | R0 c1^T]
+        mma_nt(T0 + 64, sR(1), sA(buf), idesc_64, 1);    // tS += R1 c0^T
+        umma_commit(&st_full[sb]);
+        if constexpr (FAM == FAM_V) umma_commit(&a_empty[buf]);
+      };
+      // X, A of tile i (families Q, K)
+      auto issue_xa = [&](int i) {
+        const int buf = i % NB;
+        mbar_wait(&b_full[buf], (i / NB) & 1, w, 21);
+        tc_fence_after_sync();
+        const uint32_t T2 = TS0 + 128;
+        if constexpr (FAM == FAM_Q) {
+          mma_nt(T2, sR(3), sB(buf), idesc_128, 0);               // [A | gtO tV^T]
+          mma_nt(T2 + 64, sR(2), sB(buf), idesc_64, 1);           // X += gO V^T
+        } else {
+          mma_nt(T2, sR(2), sB(buf), idesc_128, 0);               // [V gO^T | A^T]
+          mma_nt(T2, sR(3), sB(buf) + C::HALF, idesc_64, 1);      // X^T += tV gtO^T
+        }
+        umma_commit(&xa_full);
+        umma_commit(&b_empty[buf]);
       };
 
-      mbar_wait(&r_full, 0, w, 20);
+      mbar_wait(&r_full, 0, w, 22);
+      int j = next_active(j_begin);
       int it = 0;
-      for (int j = j_begin; j < j_end; ++j) {
-        if (!(tile_bits(j) & kTileAnyKept)) continue;
-        int slot[4];
-        uint32_t ph[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int g = 4 * it + e;
-          slot[e] = g % NS;
-          ph[e] = (g / NS) & 1;
-        }
-        const uint32_t acc0 = it > 0;
+      if (j < j_end) {
+        issue_st(0, 0);
+        if constexpr (FAM != FAM_V) issue_xa(0);
+      }
+      for (; j < j_end; ++it) {
+        const int jn = next_active(j + 1);
+        const bool has_next = jn < j_end;
+        JVPFA_TR(0, it, 0);
         if constexpr (FAM == FAM_V) {
-          mbar_wait(&c_full[slot[0]], ph[0], w, 21);
-          mbar_wait(&c_full[slot[1]], ph[1], w, 22);
+          if (has_next) issue_st(it + 1, (it + 1) & 1);
+          JVPFA_TR(0, it, 1);
+          const int buf = it % NB;
+          mbar_wait(&p_full[it & 1], (it >> 1) & 1, w, 23);
+          mbar_wait(&b_full[buf], (it / NB) & 1, w, 24);
           tc_fence_after_sync();
-          mma_nt(T0, sR(0), sSlot(slot[0]), 0);  // S^T  = K Q^T
-          mma_nt(T1, sR(1), sSlot(slot[0]), 0);  // tS^T = tK Q^T + K tQ^T
-          mma_nt(T1, sR(0), sSlot(slot[1]), 1);
-          umma_commit(&s_full);
-          umma_commit(&c_empty[slot[0]]);
-          umma_commit(&c_empty[slot[1]]);
-          mbar_wait(&p_full, it & 1, w, 23);
-          mbar_wait(&c_full[slot[2]], ph[2], w, 24);
-          mbar_wait(&c_full[slot[3]], ph[3], w, 25);
-          tc_fence_after_sync();
-          mma_out(tmem + C::TMEM_ACC0, E0, sSlot(slot[2]), acc0);  // dV  += P^T gO + tP^T gtO
-          mma_out(tmem + C::TMEM_ACC0, E1, sSlot(slot[3]), 1);
-          mma_out(tmem + C::TMEM_ACC1, E0, sSlot(slot[3]), acc0);  // dtV += P^T gtO
-          umma_commit(&c_empty[slot[2]]);
-          umma_commit(&c_empty[slot[3]]);
+          JVPFA_TR(0, it, 2);
+          const uint32_t E0 = TS0 + (it & 1) * 128, E1 = E0 + 64;
+          mma_out(tmem + C::TMEM_ACC0, E0, sB(buf), it > 0);               // dV  += P^T gO + tP^T gtO
+          mma_out(tmem + C::TMEM_ACC0, E1, sB(buf) + C::HALF, 1);
+          mma_out(tmem + C::TMEM_ACC1, E0, sB(buf) + C::HALF, it > 0);     // dtV += P^T gtO
+          umma_commit(&b_empty[buf]);
+          JVPFA_TR(0, it, 3);
         } else {
-#pragma unroll
-          for (int e = 0; e < 4; ++e) mbar_wait(&c_full[slot[e]], ph[e], w, 21 + e);
+          if (has_next) {
+            mbar_wait(&ph1_done, it & 1, w, 25);
+            issue_st(it + 1, 0);
+          }
+          JVPFA_TR(0, it, 1);
+          const int buf = it % NA;
+          mbar_wait(&p_full[0], it & 1, w, 26);
           tc_fence_after_sync();
-          // ring positions: 0,1 = second operand pair (V,tV | gO,gtO), 2,3 = first pair (K,tK | Q,tQ)
-          mma_nt(T0, sR(0), sSlot(slot[2]), 0);
-          mma_nt(T1, sR(1), sSlot(slot[2]), 0);
-          mma_nt(T1, sR(0), sSlot(slot[3]), 1);
-          mma_nt(T2, sR(2), sSlot(slot[0]), 0);
-          mma_nt(T2, sR(3), sSlot(slot[1]), 1);
-          if constexpr (FAM == FAM_Q) mma_nt(T3, sR(3), sSlot(slot[0]), 0);  // A   = gtO V^T
-          else mma_nt(T3, sR(2), sSlot(slot[1]), 0);                         // A^T = V gtO^T
-          umma_commit(&s_full);
-          umma_commit(&c_empty[slot[0]]);
-          umma_commit(&c_empty[slot[1]]);
-          mbar_wait(&p_full, it & 1, w, 26);
-          tc_fence_after_sync();
-          mma_out(tmem + C::TMEM_ACC0, E0, sSlot(slot[2]), acc0);
-          mma_out(tmem + C::TMEM_ACC0, E1, sSlot(slot[3]), 1);
-          mma_out(tmem + C::TMEM_ACC1, E1, sSlot(slot[2]), acc0);
-          umma_commit(&c_empty[slot[2]]);
-          umma_commit(&c_empty[slot[3]]);
+          JVPFA_TR(0, it, 2);
+          // dS in the first score tile of the second group, dtS in the second; for family K the
+          // pair product leaves X first and A second, the element-wise code writes them the same way
+          const uint32_t E0 = TS0 + 128, E1 = TS0 + 192;
+          mma_out(tmem + C::TMEM_ACC0, E0, sA(buf), it > 0);               // dS c0 + dtS c1
+          mma_out(tmem + C::TMEM_ACC0, E1, sA(buf) + C::HALF, 1);
+          mma_out(tmem + C::TMEM_ACC1, E1, sA(buf), it > 0);               // dtS c0
+          umma_commit(&a_empty[buf]);
+          JVPFA_TR(0, it, 3);
+          if (has_next) issue_xa(it + 1);
+          JVPFA_TR(0, it, 4);
         }
-        ++it;
+        j = jn;
       }
       if (it > 0) umma_commit(&acc_final);
       else mbar_arrive(&acc_final);
@@ -287,108 +358,150 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
     __syncwarp();
   } else {
     // ------------------------------------------------------------------ element-wise + epilogue
-    const int r = warp * 32 + lane;
+    const int wg = warp >> 2;          // element-wise warpgroup: columns [32 wg, 32 wg + 32) of every tile
+    const int r = (warp & 3) * 32 + lane;
     const int gr = r0 + r;             // global sequence index of this thread's row
     const int gr_c = min(gr, N - 1);
-    const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
-    const uint32_t T0 = tmem + C::TMEM_T + lane_off, T1 = T0 + 64, T2 = T0 + 128, T3 = T0 + 192;
-    const uint32_t E0 = (FAM == FAM_V) ? T0 : T2, E1 = (FAM == FAM_V) ? T1 : T3;
+    const bool tr = (lane == 0 && (warp & 3) == 0);
+    const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t TS0 = tmem + C::TMEM_T + lane_off;
     float4 st_row = make_float4(0.f, 0.f, 0.f, 0.f);
     if (FAM == FAM_Q) {
       st_row = p.stats[static_cast<size_t>(row_base) + gr_c];
       if (st_row.x == -INFINITY) st_row.x = INFINITY;  // fully excluded query: P = 0
     }
     int it = 0;
-    for (int j = j_begin; j < j_end; ++j) {
+    for (int j = next_active(j_begin); j < j_end; j = next_active(j + 1), ++it) {
       const uint8_t bits = tile_bits(j);
-      if (!(bits & kTileAnyKept)) continue;
       const int c0 = j * C::BC;
+      const int cw = c0 + 32 * wg;   // first column of this thread
       if (FAM != FAM_Q) {
-        if (r < C::BC) {
+        if (tid < C::BC) {
           float4 sv = make_float4(INFINITY, 0.f, 0.f, 0.f);
-          if (c0 + r < N) {
-            sv = p.stats[static_cast<size_t>(row_base) + c0 + r];
+          if (c0 + tid < N) {
+            sv = p.stats[static_cast<size_t>(row_base) + c0 + tid];
             if (sv.x == -INFINITY) sv.x = INFINITY;
           }
-          stats_s[it & 1][r] = sv;
+          stats_s[it & 1][tid] = sv;
         }
-        named_bar_sync(1, 128);
+        named_bar_sync(1, 256);
       }
-      mbar_wait(&s_full, it & 1, w, 30);
+      const int sb = (FAM == FAM_V) ? (it & 1) : 0;
+      const uint32_t T0 = TS0 + sb * 128 + 32 * wg, T1 = T0 + 64;
+      if (tr) JVPFA_TR(1 + wg, it, 0);
+      mbar_wait(&st_full[sb], (FAM == FAM_V) ? ((it >> 1) & 1) : (it & 1), w, 30);
       tc_fence_after_sync();
-      const bool need_causal = p.causal && ((FAM == FAM_Q) ? (c0 + C::BC - 1 > r0) : (r0 + C::BR - 1 > c0));
-      const bool need_bound = (FAM == FAM_Q) && (c0 + C::BC > N);
-      const bool need_mask = p.mv.kind != JVPFA_MASK_NONE && (bits & kTileAnyMasked);
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t t0[16], t1[16], t2[16], t3[16];
-        tmem_ld_x16(T0 + 16 * c, t0);
-        tmem_ld_x16(T1 + 16 * c, t1);
-        if constexpr (FAM != FAM_V) {
-          tmem_ld_x16(T2 + 16 * c, t2);
-          tmem_ld_x16(T3 + 16 * c, t3);
-        }
-        float bias[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) bias[i] = 0.f;
-        if (need_mask) {
-          if (FAM == FAM_Q) mask_bias_run<16>(bias, p.mv, b, h, gr_c, c0 + 16 * c, N, true);
-          else mask_bias_run<16>(bias, p.mv, b, h, c0 + 16 * c, gr_c, N, false);
-        }
-        if (need_causal) {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const int col = c0 + 16 * c + i;
-            const bool ok = (FAM == FAM_Q) ? (col <= gr) : (gr <= col);
-            if (!ok) bias[i] = -INFINITY;
-          }
-        }
-        if (need_bound) {
-#pragma unroll
-          for (int i = 0; i < 16; ++i)
-            if (c0 + 16 * c + i >= N) bias[i] = -INFINITY;
-        }
+      if (tr) JVPFA_TR(1 + wg, it, 1);
+      // ---- phase 1: P and ts of this thread's 32 columns
+      float P[32], ts[32];
+      {
+        uint32_t a0[32], a1[32];
+        tmem_ld_x32(T0, a0);
+        tmem_ld_x32(T1, a1);
         tmem_wait_ld();
-        uint32_t e0[8], e1[8];
+        if constexpr (FAM != FAM_V) {
+          tc_fence_before_sync();
+          mbar_arrive(&ph1_done);   // S, tS are in registers: the next tile's products may overwrite them
+        }
+        if (tr) JVPFA_TR(1 + wg, it, 2);
+        const bool need_causal = p.causal && ((FAM == FAM_Q) ? (c0 + C::BC - 1 > r0) : (r0 + C::BR - 1 > c0));
+        const bool need_bound = (FAM == FAM_Q) && (c0 + C::BC > N);
+        const bool need_mask = p.mv.kind != JVPFA_MASK_NONE && (bits & kTileAnyMasked);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          float v0[2], v1[2];
+        for (int hch = 0; hch < 2; ++hch) {
+          float bias[16];
 #pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int ii = 2 * i + u;
-            float4 sq;
-            if (FAM == FAM_Q) sq = st_row;
-            else sq = stats_s[it & 1][16 * c + ii];
-            const float P = fast_exp2(fmaf(__uint_as_float(t0[ii]), p.c1, bias[ii]) - sq.x);
-            const float ts = __uint_as_float(t1[ii]) * p.s;
-            if constexpr (FAM == FAM_V) {
-              v0[u] = P;
-              v1[u] = P * (ts - sq.y);
-            } else {
-              const float X = __uint_as_float(t2[ii]);
-              const float A = __uint_as_float(t3[ii]);
-              const float dp = X + A * (ts - sq.y) - sq.w * ts;
-              v0[u] = P * (dp - sq.z);   // dS
-              v1[u] = P * (A - sq.w);    // dtS
+          for (int i = 0; i < 16; ++i) bias[i] = 0.f;
+          if (need_mask) {
+            if (FAM == FAM_Q) mask_bias_run<16>(bias, p.mv, b, h, gr_c, cw + 16 * hch, N, true);
+            else mask_bias_run<16>(bias, p.mv, b, h, cw + 16 * hch, gr_c, N, false);
+          }
+          if (need_causal) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const int col = cw + 16 * hch + i;
+              const bool ok = (FAM == FAM_Q) ? (col <= gr) : (gr <= col);
+              if (!ok) bias[i] = -INFINITY;
             }
           }
-          e0[i] = pack2<BF16>(v0[0], v0[1]);
-          e1[i] = pack2<BF16>(v1[0], v1[1]);
+          if (need_bound) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              if (cw + 16 * hch + i >= N) bias[i] = -INFINITY;
+          }
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int ii = 16 * hch + i;
+            const float lse = (FAM == FAM_Q) ? st_row.x : stats_s[it & 1][32 * wg + ii].x;
+            P[ii] = fast_exp2(fmaf(__uint_as_float(a0[ii]), p.c1, bias[i]) - lse);
+            ts[ii] = __uint_as_float(a1[ii]) * p.s;
+          }
         }
-        tmem_st_x8(E0 + 8 * c, e0);
-        tmem_st_x8(E1 + 8 * c, e1);
       }
+      if (tr) JVPFA_TR(1 + wg, it, 3);
+      if constexpr (FAM == FAM_V) {
+        // P and tP = P (ts - mu) back into this thread's own columns of the score buffer
+#pragma unroll
+        for (int hch = 0; hch < 2; ++hch) {
+          uint32_t e0[8], e1[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int i0 = 16 * hch + 2 * i, i1 = i0 + 1;
+            const float mu0 = stats_s[it & 1][32 * wg + i0].y, mu1 = stats_s[it & 1][32 * wg + i1].y;
+            e0[i] = pack2<BF16>(P[i0], P[i1]);
+            e1[i] = pack2<BF16>(P[i0] * (ts[i0] - mu0), P[i1] * (ts[i1] - mu1));
+          }
+          tmem_st_x8(T0 + 8 * hch, e0);
+          tmem_st_x8(T1 + 8 * hch, e1);
+        }
+      } else {
+        // ---- phase 2: X, A -> dS, dtS
+        const uint32_t T2 = TS0 + 128 + 32 * wg, T3 = T2 + 64;
+        mbar_wait(&xa_full, it & 1, w, 31);
+        tc_fence_after_sync();
+        if (tr) JVPFA_TR(1 + wg, it, 4);
+#pragma unroll
+        for (int hch = 0; hch < 2; ++hch) {
+          uint32_t x2[16], x3[16];
+          tmem_ld_x16(T2 + 16 * hch, x2);
+          tmem_ld_x16(T3 + 16 * hch, x3);
+          tmem_wait_ld();
+          uint32_t e0[8], e1[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            float v0[2], v1[2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              const int ii = 2 * i + u, ic = 16 * hch + ii;
+              float4 sq;
+              if (FAM == FAM_Q) sq = st_row;
+              else sq = stats_s[it & 1][32 * wg + ic];
+              const float A = __uint_as_float(FAM == FAM_Q ? x2[ii] : x3[ii]);
+              const float X = __uint_as_float(FAM == FAM_Q ? x3[ii] : x2[ii]);
+              const float d = A - sq.w;                                   // A - a
+              const float t = fmaf(ts[ic], d, X - sq.z) - sq.y * A;      // X - Delta + ts (A - a) - mu A
+              v0[u] = P[ic] * t;   // dS
+              v1[u] = P[ic] * d;   // dtS
+            }
+            e0[i] = pack2<BF16>(v0[0], v0[1]);
+            e1[i] = pack2<BF16>(v1[0], v1[1]);
+          }
+          tmem_st_x8(T2 + 8 * hch, e0);
+          tmem_st_x8(T3 + 8 * hch, e1);
+        }
+      }
+      if (tr) JVPFA_TR(1 + wg, it, 5);
       tmem_wait_st();
       tc_fence_before_sync();
-      mbar_arrive(&p_full);
-      ++it;
+      mbar_arrive(&p_full[sb]);
+      if (tr) JVPFA_TR(1 + wg, it, 6);
     }
     // epilogue
-    mbar_wait(&acc_final, 0, w, 31);
+    mbar_wait(&acc_final, 0, w, 32);
     tc_fence_after_sync();
     const size_t orow = (static_cast<size_t>(row_base) + gr) * D;
 #pragma unroll
-    for (int c = 0; c < D / 32; ++c) {
+    for (int c = wg * (D / 64); c < (wg + 1) * (D / 64); ++c) {
       uint32_t a0[32], a1[32];
       if (it > 0) {
         tmem_ld_x32(tmem + lane_off + C::TMEM_ACC0 + c * 32, a0);
@@ -417,7 +530,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
   }
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 5) tmem_dealloc(tmem, C::TMEM_COLS);
+  if (warp == 9) tmem_dealloc(tmem, C::TMEM_COLS);
 }
 
 // stats[row] = (lse2, mu, Delta, a) with a = rowsum(gtO o O), Delta = rowsum(gO o O) + rowsum(gtO o tO) - a mu.
@@ -473,11 +586,11 @@ int launch_family(const jvpfa_bwd_args& a, const float4* stats, cudaStream_t str
   float out_scale;
   if (FAM == FAM_Q) {
     rsrc[0] = a.q; rsrc[1] = a.tq; rsrc[2] = a.go; rsrc[3] = a.gto;
-    csrc[0] = a.v; csrc[1] = a.tv; csrc[2] = a.k; csrc[3] = a.tk;
+    csrc[0] = a.k; csrc[1] = a.tk; csrc[2] = a.v; csrc[3] = a.tv;
     out0 = a.dq; out1 = a.dtq; out_scale = a.sm_scale;
   } else if (FAM == FAM_K) {
     rsrc[0] = a.k; rsrc[1] = a.tk; rsrc[2] = a.v; rsrc[3] = a.tv;
-    csrc[0] = a.go; csrc[1] = a.gto; csrc[2] = a.q; csrc[3] = a.tq;
+    csrc[0] = a.q; csrc[1] = a.tq; csrc[2] = a.go; csrc[3] = a.gto;
     out0 = a.dk; out1 = a.dtk; out_scale = a.sm_scale;
   } else {
     rsrc[0] = a.k; rsrc[1] = a.tk; rsrc[2] = a.k; rsrc[3] = a.tk;
@@ -487,7 +600,7 @@ int launch_family(const jvpfa_bwd_args& a, const float4* stats, cudaStream_t str
   CUtensorMap rm[4], cm[4];
   for (int i = 0; i < 4; ++i) {
     if (!make_tile_map(&rm[i], rsrc[i], rows, D, C::BR, a.dtype)) return JVPFA_ERR_LAUNCH;
-    if (!make_tile_map(&cm[i], csrc[i], rows, D, C::BC, a.dtype)) return JVPFA_ERR_LAUNCH;
+    if (!make_tile_map(&cm[i], csrc[i], rows, D, C::BC, a.dtype, 1)) return JVPFA_ERR_LAUNCH;
   }
   BwdKParams p{};
   p.H = a.H; p.N = a.N; p.causal = a.causal;
@@ -509,7 +622,7 @@ int launch_family(const jvpfa_bwd_args& a, const float4* stats, cudaStream_t str
     return JVPFA_ERR_LAUNCH;
   dim3 grid((a.N + C::BR - 1) / C::BR, a.B * a.H);
   ScopedKernelTimer timer(FAM == FAM_Q ? KERNEL_BWD_Q : (FAM == FAM_K ? KERNEL_BWD_K : KERNEL_BWD_V), stream);
-  kern<<<grid, 192, smem, stream>>>(rm[0], rm[1], rm[2], rm[3], cm[0], cm[1], cm[2], cm[3], p);
+  kern<<<grid, 320, smem, stream>>>(rm[0], rm[1], rm[2], rm[3], cm[0], cm[1], cm[2], cm[3], p);
   return cudaGetLastError() == cudaSuccess ? JVPFA_OK : JVPFA_ERR_LAUNCH;
 }
 
@@ -534,6 +647,12 @@ int launch_all(const jvpfa_bwd_args& a, cudaStream_t stream) {
 }
 
 }  // namespace
+
+#ifdef JVPFA_TRACE
+extern "C" int jvpfa_bwd_trace_read(long long* host_out) {
+  return cudaMemcpyFromSymbol(host_out, g_bwd_trace, sizeof(g_bwd_trace)) == cudaSuccess ? 0 : 1;
+}
+#endif
 
 size_t bwd_sm100_workspace_bytes(const jvpfa_bwd_args& a) {
   return kStatusBytes + static_cast<size_t>(a.B) * a.H * a.N * sizeof(float4);

@@ -19,7 +19,8 @@ TensorMapEncodeFn tensor_map_encoder();
 // one TMA copy of box (64, box_rows, D/64) lands in shared memory as D/64 slabs of
 // [box_rows][64 elements], each slab in the 128-byte-swizzled layout the MMA descriptors expect.
 // Returns false if the driver rejects the encoding.
-bool make_tile_map(CUtensorMap* out, const void* base, uint64_t rows, int D, int box_rows, int dtype);
+// `box_slabs` = 0 copies all D/64 slabs with one box; 1 copies a single slab (the slab index is coordinate 2).
+bool make_tile_map(CUtensorMap* out, const void* base, uint64_t rows, int D, int box_rows, int dtype, int box_slabs = 0);
 
 // Wait budget of a single device-side mbarrier wait, in nanoseconds (JVPFA_WAIT_BUDGET_MS, default 4000 ms).
 uint64_t wait_budget_ns();
