@@ -37,12 +37,12 @@ namespace {
 enum { FAM_Q = 0, FAM_K = 1, FAM_V = 2 };
 
 // Optional cycle trace of CTA (0,0) for kernel tuning (compile with -DJVPFA_TRACE): role 0 = MMA issuer,
-// 1 / 2 = first lane of element-wise warpgroup 0 / 1; 8 time stamps per tile for the first 64 tiles.
+// 1 / 2 = first lane of element-wise warpgroup 0 / 1; 8 time stamps per tile for the first 64 tiles, per family.
 #ifdef JVPFA_TRACE
-__device__ long long g_bwd_trace[3 * 64 * 8];
+__device__ long long g_bwd_trace[3 * 3 * 64 * 8];  // [family][role][tile][stamp]
 #define JVPFA_TR(role, it, k)                                                                        \
   do {                                                                                               \
-    if (blockIdx.x == 0 && blockIdx.y == 0 && (it) < 64) g_bwd_trace[((role)*64 + (it)) * 8 + (k)] = clock64(); \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && (it) < 64) g_bwd_trace[((FAM * 3 + (role)) * 64 + (it)) * 8 + (k)] = clock64(); \
   } while (0)
 #else
 #define JVPFA_TR(role, it, k) do { } while (0)
@@ -252,7 +252,13 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
     __syncwarp();
   } else if (warp == 9) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    {
+      // all lanes run the loop so that addresses and descriptors stay warp-uniform; lane 0 issues
+      const bool leader = lane == 0;
+      auto wait_all = [&](uint64_t* bar, uint32_t parity, int site) {
+        mbar_wait(bar, parity, w, site);
+        __syncwarp();
+      };
       constexpr uint32_t FMT = BF16 ? FMT_BF16 : FMT_F16;
       const uint32_t idesc_64 = make_idesc(FMT, 128, 64, 0, 0);
       const uint32_t idesc_128 = make_idesc(FMT, 128, 128, 0, 0);
@@ -261,36 +267,38 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
 
       // dst[128 x n] (+)= R[128 x D] * Cc[n x D]^T, Cc = n rows starting at `ctile` inside a pair buffer
       auto mma_nt = [&](uint32_t dst, const uint8_t* rtile, const uint8_t* ctile, uint32_t idesc, uint32_t acc) {
-        const uint32_t a = smem_u32(rtile), bb = smem_u32(ctile);
+        // descriptors of the later K steps differ from the first only in the 16-byte-unit start address
+        const uint64_t da = desc_kmajor_sw128(smem_u32(rtile)), db = desc_kmajor_sw128(smem_u32(ctile));
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
-          const uint32_t o = (k >> 2) * C::SLAB + (k & 3) * 32;
-          umma_ss(dst, desc_kmajor_sw128(a + o), desc_kmajor_sw128(bb + o), idesc, acc | (k > 0));
+          const uint64_t o = static_cast<uint64_t>(((k >> 2) * C::SLAB + (k & 3) * 32) >> 4);
+          if (leader) umma_ss(dst, da + o, db + o, idesc, acc | (k > 0));
         }
       };
       // acc[128 x D] (+)= E[128 x 64] (TMEM, 16-bit, two column groups of 16) * Cc[64 x D]
       auto mma_out = [&](uint32_t accum, uint32_t e, const uint8_t* ctile, uint32_t acc) {
-        const uint32_t bb = smem_u32(ctile);
+        const uint64_t db = desc_mnmajor_sw128(smem_u32(ctile), C::SLAB);
 #pragma unroll
         for (int k = 0; k < C::BC / 16; ++k)
-          umma_ts(accum, e + (k & 1) * 8 + (k >> 1) * 32, desc_mnmajor_sw128(bb + k * 2048, C::SLAB), idesc_out,
-                  acc | (k > 0));
+          if (leader)
+            umma_ts(accum, e + (k & 1) * 8 + (k >> 1) * 32, db + static_cast<uint64_t>((k * 2048) >> 4), idesc_out,
+                    acc | (k > 0));
       };
       // S, tS of tile i into score buffer sb
       auto issue_st = [&](int i, int sb) {
         const int buf = i % NA;
-        mbar_wait(&a_full[buf], (i / NA) & 1, w, 20);
+        wait_all(&a_full[buf], (i / NA) & 1, 20);
         tc_fence_after_sync();
         const uint32_t T0 = TS0 + sb * 128;
         mma_nt(T0, sR(0), sA(buf), idesc_128, 0);        // [S | R0 c1^T]
         mma_nt(T0 + 64, sR(1), sA(buf), idesc_64, 1);    // tS += R1 c0^T
-        umma_commit(&st_full[sb]);
-        if constexpr (FAM == FAM_V) umma_commit(&a_empty[buf]);
+        if (leader) umma_commit(&st_full[sb]);
+        if constexpr (FAM == FAM_V) if (leader) umma_commit(&a_empty[buf]);
       };
       // X, A of tile i (families Q, K)
       auto issue_xa = [&](int i) {
         const int buf = i % NB;
-        mbar_wait(&b_full[buf], (i / NB) & 1, w, 21);
+        wait_all(&b_full[buf], (i / NB) & 1, 21);
         tc_fence_after_sync();
         const uint32_t T2 = TS0 + 128;
         if constexpr (FAM == FAM_Q) {
@@ -300,11 +308,11 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
           mma_nt(T2, sR(2), sB(buf), idesc_128, 0);               // [V gO^T | A^T]
           mma_nt(T2, sR(3), sB(buf) + C::HALF, idesc_64, 1);      // X^T += tV gtO^T
         }
-        umma_commit(&xa_full);
-        umma_commit(&b_empty[buf]);
+        if (leader) umma_commit(&xa_full);
+        if (leader) umma_commit(&b_empty[buf]);
       };
 
-      mbar_wait(&r_full, 0, w, 22);
+      wait_all(&r_full, 0, 22);
       int j = next_active(j_begin);
       int it = 0;
       if (j < j_end) {
@@ -319,24 +327,24 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
           if (has_next) issue_st(it + 1, (it + 1) & 1);
           JVPFA_TR(0, it, 1);
           const int buf = it % NB;
-          mbar_wait(&p_full[it & 1], (it >> 1) & 1, w, 23);
-          mbar_wait(&b_full[buf], (it / NB) & 1, w, 24);
+          wait_all(&p_full[it & 1], (it >> 1) & 1, 23);
+          wait_all(&b_full[buf], (it / NB) & 1, 24);
           tc_fence_after_sync();
           JVPFA_TR(0, it, 2);
           const uint32_t E0 = TS0 + (it & 1) * 128, E1 = E0 + 64;
           mma_out(tmem + C::TMEM_ACC0, E0, sB(buf), it > 0);               // dV  += P^T gO + tP^T gtO
           mma_out(tmem + C::TMEM_ACC0, E1, sB(buf) + C::HALF, 1);
           mma_out(tmem + C::TMEM_ACC1, E0, sB(buf) + C::HALF, it > 0);     // dtV += P^T gtO
-          umma_commit(&b_empty[buf]);
+          if (leader) umma_commit(&b_empty[buf]);
           JVPFA_TR(0, it, 3);
         } else {
           if (has_next) {
-            mbar_wait(&ph1_done, it & 1, w, 25);
+            wait_all(&ph1_done, it & 1, 25);
             issue_st(it + 1, 0);
           }
           JVPFA_TR(0, it, 1);
           const int buf = it % NA;
-          mbar_wait(&p_full[0], it & 1, w, 26);
+          wait_all(&p_full[0], it & 1, 26);
           tc_fence_after_sync();
           JVPFA_TR(0, it, 2);
           // dS in the first score tile of the second group, dtS in the second; for family K the
@@ -345,15 +353,15 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
           mma_out(tmem + C::TMEM_ACC0, E0, sA(buf), it > 0);               // dS c0 + dtS c1
           mma_out(tmem + C::TMEM_ACC0, E1, sA(buf) + C::HALF, 1);
           mma_out(tmem + C::TMEM_ACC1, E1, sA(buf), it > 0);               // dtS c0
-          umma_commit(&a_empty[buf]);
+          if (leader) umma_commit(&a_empty[buf]);
           JVPFA_TR(0, it, 3);
           if (has_next) issue_xa(it + 1);
           JVPFA_TR(0, it, 4);
         }
         j = jn;
       }
-      if (it > 0) umma_commit(&acc_final);
-      else mbar_arrive(&acc_final);
+      if (it > 0) { if (leader) umma_commit(&acc_final); }
+      else if (leader) mbar_arrive(&acc_final);
     }
     __syncwarp();
   } else {

@@ -23,6 +23,18 @@ using namespace sm100;
 
 namespace {
 
+// Optional cycle trace of CTA (0,0) for kernel tuning (compile with -DJVPFA_TRACE): role 0 = MMA issuer,
+// 1 / 2 = first lane of softmax warpgroup 0 / 1; 8 time stamps per tile for the first 64 tiles.
+#ifdef JVPFA_TRACE
+__device__ long long g_fwd_trace[3 * 64 * 8];
+#define JVPFA_FTR(role, it, k)                                                                       \
+  do {                                                                                               \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && (it) < 64) g_fwd_trace[((role)*64 + (it)) * 8 + (k)] = clock64(); \
+  } while (0)
+#else
+#define JVPFA_FTR(role, it, k) do { } while (0)
+#endif
+
 struct FwdKParams {
   int H, N;
   int causal;
@@ -61,39 +73,62 @@ struct FwdCfg {
   static constexpr int BN = 64;
   static constexpr int STAGES = (D == 64) ? 4 : 2;
   static constexpr int TILE_Q = BM * D * 2;
-  static constexpr int TILE_K = BN * D * 2;
+  static constexpr int TILE_V = BN * D * 2;
+  static constexpr int PAIR_K = 2 * BN * D * 2;  // K and tK stacked as one 128-row operand
+  static constexpr int SLAB = 128 * 128;          // bytes of one 64-column slab of a 128-row tile
+  static constexpr int HALF = BN * 128;           // byte offset of tK inside a slab of the pair
+  static constexpr int STAGE = PAIR_K + 2 * TILE_V;
   static constexpr int TMEM_O = 0;
   static constexpr int TMEM_T = D;
   static constexpr int TMEM_S = 2 * D;  // buffer b at TMEM_S + 128*b; tS 64 columns further
   static constexpr int TMEM_COLS = 512;
-  static constexpr size_t smem_bytes(bool dual) {
-    return 1024 + (dual ? 2 : 1) * TILE_Q + STAGES * (dual ? 4 : 2) * TILE_K;
-  }
+  static constexpr int NBAR = 4 + 4 * STAGES + 4;
+  static constexpr size_t smem_bytes() { return 2 * TILE_Q + STAGES * STAGE + 2 * 2 * 128 * 4 + (NBAR + 2) * 8; }
 };
 
+__device__ __forceinline__ void mbar_wait_warp(uint64_t* bar, uint32_t parity, const WaitCtx& w, int site) {
+  mbar_wait(bar, parity, w, site);
+  __syncwarp();
+}
+
+// Warps 0-7: two softmax warpgroups that split the 64 columns of every score tile (thread = TMEM lane =
+// one score row, 32 columns; the row maximum and the final row sums are exchanged through shared
+// memory); warp 8: TMA producer; warp 9: MMA issuer (all lanes run the loop so that operands stay
+// warp-uniform, lane 0 issues) and owner of the TMEM allocation.
 template <int D, bool DUAL, bool BF16>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmTQ,
                  const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmTK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmTV,
                  const FwdKParams p) {
   using C = FwdCfg<D>;
   constexpr int ST = C::STAGES;
-  constexpr int NT = DUAL ? 2 : 1;  // tensors per operand family
+  constexpr int SLABS = D / 64;
 
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* sQ = smem;
-  uint8_t* sTQ = sQ + C::TILE_Q;  // only with DUAL
-  uint8_t* sKV = smem + NT * C::TILE_Q;
-  auto sK = [&](int st) { return sKV + st * (2 * NT) * C::TILE_K; };
-  auto sTK = [&](int st) { return sK(st) + C::TILE_K; };  // only with DUAL
-  auto sV = [&](int st) { return sK(st) + NT * C::TILE_K; };
-  auto sTV = [&](int st) { return sV(st) + C::TILE_K; };  // only with DUAL
-
-  __shared__ uint64_t q_full, k_full[ST], v_full[ST], k_empty[ST], v_empty[ST], s_full[2], p_full[2], o_done, o_final;
-  __shared__ uint32_t tmem_base_s;
-  __shared__ int poisoned;
+  uint8_t* sTQ = sQ + C::TILE_Q;
+  auto sK = [&](int st) { return smem + 2 * C::TILE_Q + st * C::STAGE; };   // [K; tK] pair
+  auto sV = [&](int st) { return sK(st) + C::PAIR_K; };
+  auto sTV = [&](int st) { return sV(st) + C::TILE_V; };
+  uint8_t* tail = smem + 2 * C::TILE_Q + ST * C::STAGE;
+  float(*xch)[2][128] = reinterpret_cast<float(*)[2][128]>(tail);          // [parity][warpgroup][row]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(tail + 2 * 2 * 128 * 4);
+  uint64_t& q_full = bars[0];
+  uint64_t& o_done = bars[1];
+  uint64_t& o_final = bars[2];
+  uint64_t* s_full = bars + 4;       // [2]
+  uint64_t* p_full = bars + 6;       // [2]
+  uint64_t* k_full = bars + 8;
+  uint64_t* v_full = k_full + ST;
+  uint64_t* k_empty = v_full + ST;
+  uint64_t* v_empty = k_empty + ST;
+  uint32_t& tmem_base_s = *reinterpret_cast<uint32_t*>(bars + C::NBAR);
+  int& poisoned = *reinterpret_cast<int*>(bars + C::NBAR + 1);
+  if ((smem_u32(smem) & 1023u) != 0u) {  // the swizzled layouts need this; never observed otherwise
+    if (threadIdx.x == 0) atomicCAS(p.status, 0, WAIT_TIMEOUT_BASE + 99);
+    return;
+  }
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int qt = p.causal ? (static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x)) : blockIdx.x;
@@ -118,14 +153,14 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s_full[i], 1);
-      mbar_init(&p_full[i], 128);
+      mbar_init(&p_full[i], 256);
     }
     mbar_init(&o_done, 1);
     mbar_init(&o_final, 1);
     fence_mbar_init();
   }
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 9) {
     tmem_alloc(&tmem_base_s, C::TMEM_COLS);
     tmem_relinquish();
   }
@@ -142,13 +177,13 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     return bits;
   };
 
-  if (warp == 4) {
+  if (warp == 8) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       tma_prefetch_desc(&tmQ);
       tma_prefetch_desc(&tmK);
       tma_prefetch_desc(&tmV);
-      mbar_arrive_expect_tx(&q_full, NT * C::TILE_Q);
+      mbar_arrive_expect_tx(&q_full, (DUAL ? 2 : 1) * C::TILE_Q);
       tma_load_3d(sQ, &tmQ, &q_full, 0, row_base + q0, 0);
       if constexpr (DUAL) tma_load_3d(sTQ, &tmTQ, &q_full, 0, row_base + q0, 0);
       int it = 0;
@@ -158,133 +193,140 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const uint32_t ph = (it / ST) & 1;
         const int krow = row_base + j * C::BN;
         mbar_wait(&k_empty[st], ph ^ 1, w, 10);
-        mbar_arrive_expect_tx(&k_full[st], NT * C::TILE_K);
-        tma_load_3d(sK(st), &tmK, &k_full[st], 0, krow, 0);
-        if constexpr (DUAL) tma_load_3d(sTK(st), &tmTK, &k_full[st], 0, krow, 0);
+        mbar_arrive_expect_tx(&k_full[st], (DUAL ? 2 : 1) * C::TILE_V);
+#pragma unroll
+        for (int sl = 0; sl < SLABS; ++sl) {
+          tma_load_3d(sK(st) + sl * C::SLAB, &tmK, &k_full[st], 0, krow, sl);
+          if constexpr (DUAL) tma_load_3d(sK(st) + sl * C::SLAB + C::HALF, &tmTK, &k_full[st], 0, krow, sl);
+        }
         mbar_wait(&v_empty[st], ph ^ 1, w, 11);
-        mbar_arrive_expect_tx(&v_full[st], NT * C::TILE_K);
+        mbar_arrive_expect_tx(&v_full[st], (DUAL ? 2 : 1) * C::TILE_V);
         tma_load_3d(sV(st), &tmV, &v_full[st], 0, krow, 0);
         if constexpr (DUAL) tma_load_3d(sTV(st), &tmTV, &v_full[st], 0, krow, 0);
         ++it;
       }
     }
     __syncwarp();
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t FMT = BF16 ? FMT_BF16 : FMT_F16;
-      const uint32_t idesc_qk = make_idesc(FMT, 128, C::BN, 0, 0);
-      const uint32_t idesc_pv = make_idesc(FMT, 128, D, 0, 1);
-      const uint32_t aQ = smem_u32(sQ), aTQ = smem_u32(sTQ);
+    const bool leader = lane == 0;
+    constexpr uint32_t FMT = BF16 ? FMT_BF16 : FMT_F16;
+    const uint32_t idesc_64 = make_idesc(FMT, 128, 64, 0, 0);
+    const uint32_t idesc_128 = make_idesc(FMT, 128, 128, 0, 0);
+    const uint32_t idesc_pv = make_idesc(FMT, 128, D, 0, 1);
+    const uint64_t dQ = desc_kmajor_sw128(smem_u32(sQ)), dTQ = desc_kmajor_sw128(smem_u32(sTQ));
 
-      auto issue_qk = [&](int it) {
-        const int st = it % ST;
-        const uint32_t ph = (it / ST) & 1;
-        const uint32_t S_t = tmem + C::TMEM_S + (it & 1) * 128;
-        const uint32_t tS_t = S_t + 64;
-        mbar_wait(&k_full[st], ph, w, 20);
-        tc_fence_after_sync();
-        const uint32_t bK = smem_u32(sK(st)), bTK = smem_u32(sTK(st));
+    auto issue_qk = [&](int it) {
+      const int st = it % ST;
+      const uint32_t ph = (it / ST) & 1;
+      const uint32_t S_t = tmem + C::TMEM_S + (it & 1) * 128;
+      if (leader) JVPFA_FTR(0, it, 0);
+      mbar_wait_warp(&k_full[st], ph, w, 20);
+      tc_fence_after_sync();
+      if (leader) JVPFA_FTR(0, it, 1);
+      const uint64_t dK = desc_kmajor_sw128(smem_u32(sK(st)));
+      if (leader) {
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
-          const uint32_t oa = (k >> 2) * (C::BM * 128) + (k & 3) * 32;
-          const uint32_t ob = (k >> 2) * (C::BN * 128) + (k & 3) * 32;
-          umma_ss(S_t, desc_kmajor_sw128(aQ + oa), desc_kmajor_sw128(bK + ob), idesc_qk, k > 0);
+          const uint64_t o = static_cast<uint64_t>(((k >> 2) * C::SLAB + (k & 3) * 32) >> 4);
+          umma_ss(S_t, dQ + o, dK + o, DUAL ? idesc_128 : idesc_64, k > 0);   // [S | Q tK^T]
         }
         if constexpr (DUAL) {
 #pragma unroll
           for (int k = 0; k < D / 16; ++k) {
-            const uint32_t oa = (k >> 2) * (C::BM * 128) + (k & 3) * 32;
-            const uint32_t ob = (k >> 2) * (C::BN * 128) + (k & 3) * 32;
-            umma_ss(tS_t, desc_kmajor_sw128(aTQ + oa), desc_kmajor_sw128(bK + ob), idesc_qk, k > 0);
-          }
-#pragma unroll
-          for (int k = 0; k < D / 16; ++k) {
-            const uint32_t oa = (k >> 2) * (C::BM * 128) + (k & 3) * 32;
-            const uint32_t ob = (k >> 2) * (C::BN * 128) + (k & 3) * 32;
-            umma_ss(tS_t, desc_kmajor_sw128(aQ + oa), desc_kmajor_sw128(bTK + ob), idesc_qk, 1);
+            const uint64_t o = static_cast<uint64_t>(((k >> 2) * C::SLAB + (k & 3) * 32) >> 4);
+            umma_ss(S_t + 64, dTQ + o, dK + o, idesc_64, 1);                    // tS += tQ K^T
           }
         }
         umma_commit(&s_full[it & 1]);
         umma_commit(&k_empty[st]);
-      };
-      auto issue_pv = [&](int it, bool last) {
-        const int st = it % ST;
-        const uint32_t ph = (it / ST) & 1;
-        const uint32_t P_t = tmem + C::TMEM_S + (it & 1) * 128;
-        const uint32_t W_t = P_t + 64;
-        mbar_wait(&p_full[it & 1], (it >> 1) & 1, w, 21);
-        mbar_wait(&v_full[st], ph, w, 22);
-        tc_fence_after_sync();
-        const uint32_t bV = smem_u32(sV(st)), bTV = smem_u32(sTV(st));
-        const uint32_t acc0 = it > 0;
+      }
+      __syncwarp();
+      if (leader) JVPFA_FTR(0, it, 2);
+    };
+    auto issue_pv = [&](int it, bool last) {
+      const int st = it % ST;
+      const uint32_t ph = (it / ST) & 1;
+      const uint32_t P_t = tmem + C::TMEM_S + (it & 1) * 128;
+      const uint32_t W_t = P_t + 64;
+      if (leader) JVPFA_FTR(0, it, 3);
+      mbar_wait_warp(&p_full[it & 1], (it >> 1) & 1, w, 21);
+      if (leader) JVPFA_FTR(0, it, 4);
+      mbar_wait_warp(&v_full[st], ph, w, 22);
+      tc_fence_after_sync();
+      if (leader) JVPFA_FTR(0, it, 5);
+      const uint64_t dV0 = desc_mnmajor_sw128(smem_u32(sV(st)), C::BN * 128);
+      const uint64_t dTV0 = desc_mnmajor_sw128(smem_u32(sTV(st)), C::BN * 128);
+      const uint32_t acc0 = it > 0;
+      if (leader) {
 #pragma unroll
         for (int k = 0; k < C::BN / 16; ++k) {
-          const uint64_t dV = desc_mnmajor_sw128(bV + k * 2048, C::BN * 128);
-          umma_ts(tmem + C::TMEM_O, P_t + k * 8, dV, idesc_pv, acc0 | (k > 0));
+          const uint64_t ok = static_cast<uint64_t>((k * 2048) >> 4);
+          const uint32_t eo = (k & 1) * 8 + (k >> 1) * 32;
+          umma_ts(tmem + C::TMEM_O, P_t + eo, dV0 + ok, idesc_pv, acc0 | (k > 0));
           if constexpr (DUAL) {
-            const uint64_t dTV = desc_mnmajor_sw128(bTV + k * 2048, C::BN * 128);
-            umma_ts(tmem + C::TMEM_T, W_t + k * 8, dV, idesc_pv, acc0 | (k > 0));
-            umma_ts(tmem + C::TMEM_T, P_t + k * 8, dTV, idesc_pv, 1);
+            umma_ts(tmem + C::TMEM_T, W_t + eo, dV0 + ok, idesc_pv, acc0 | (k > 0));
+            umma_ts(tmem + C::TMEM_T, P_t + eo, dTV0 + ok, idesc_pv, 1);
           }
         }
         umma_commit(&v_empty[st]);
         umma_commit(&o_done);
         if (last) umma_commit(&o_final);
-      };
-
-      mbar_wait(&q_full, 0, w, 23);
-      int it = 0;
-      for (int j = 0; j < n_kt; ++j) {
-        if (!(tile_bits(j) & kTileAnyKept)) continue;
-        issue_qk(it);
-        if (it > 0) issue_pv(it - 1, false);
-        ++it;
       }
-      if (it > 0) issue_pv(it - 1, true);
+      __syncwarp();
+      if (leader) JVPFA_FTR(0, it, 6);
+    };
+
+    mbar_wait_warp(&q_full, 0, w, 23);
+    int it = 0;
+    for (int j = 0; j < n_kt; ++j) {
+      if (!(tile_bits(j) & kTileAnyKept)) continue;
+      issue_qk(it);
+      if (it > 0) issue_pv(it - 1, false);
+      ++it;
     }
-    __syncwarp();
+    if (it > 0) issue_pv(it - 1, true);
   } else {
     // ------------------------------------------------------------------ softmax, correction, epilogue
-    const int r = warp * 32 + lane;
+    const int wg = warp >> 2;
+    const int r = (warp & 3) * 32 + lane;
     const int qi = q0 + r;
     const int qi_c = min(qi, N - 1);
-    const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
-    float m_used = -INFINITY, l = 0.f, mu = 0.f;
+    const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    float m_used = -INFINITY, l = 0.f, mu = 0.f;   // l, mu: partial sums over this thread's columns
     int it = 0;
     for (int j = 0; j < n_kt; ++j) {
       const uint8_t bits = tile_bits(j);
       if (!(bits & kTileAnyKept)) continue;
-      const uint32_t S_t = tmem + C::TMEM_S + (it & 1) * 128 + lane_off;
+      const uint32_t S_t = tmem + C::TMEM_S + (it & 1) * 128 + lane_off + 32 * wg;
       const uint32_t tS_t = S_t + 64;
+      const bool tr = lane == 0 && (warp & 3) == 0;
+      if (tr) JVPFA_FTR(1 + wg, it, 0);
       mbar_wait(&s_full[it & 1], (it >> 1) & 1, w, 30);
       tc_fence_after_sync();
-      float x[64];
+      if (tr) JVPFA_FTR(1 + wg, it, 1);
+      float x[32];
       {
-        uint32_t r0[32], r1[32];
+        uint32_t r0[32];
         tmem_ld_x32(S_t, r0);
-        tmem_ld_x32(S_t + 32, r1);
         tmem_wait_ld();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          x[i] = __uint_as_float(r0[i]) * p.c1;
-          x[32 + i] = __uint_as_float(r1[i]) * p.c1;
-        }
+        for (int i = 0; i < 32; ++i) x[i] = __uint_as_float(r0[i]) * p.c1;
       }
-      const int k0 = j * C::BN;
-      if (p.causal && k0 + C::BN - 1 > q0) {
+      const int k0 = j * C::BN + 32 * wg;   // first key of this thread's columns
+      if (p.causal && j * C::BN + C::BN - 1 > q0) {
 #pragma unroll
-        for (int i = 0; i < 64; ++i)
+        for (int i = 0; i < 32; ++i)
           if (k0 + i > qi) x[i] = -INFINITY;
       }
-      if (k0 + C::BN > N) {
+      if (j * C::BN + C::BN > N) {
 #pragma unroll
-        for (int i = 0; i < 64; ++i)
+        for (int i = 0; i < 32; ++i)
           if (k0 + i >= N) x[i] = -INFINITY;
       }
       if (p.mv.kind != JVPFA_MASK_NONE && (bits & kTileAnyMasked)) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
           float bias[16];
           mask_bias_run<16>(bias, p.mv, b, h, qi_c, k0 + 16 * c, N, true);
 #pragma unroll
@@ -293,22 +335,32 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
       float m_tile = x[0];
 #pragma unroll
-      for (int i = 1; i < 64; ++i) m_tile = fmaxf(m_tile, x[i]);
+      for (int i = 1; i < 32; ++i) m_tile = fmaxf(m_tile, x[i]);
+      // row maximum over both warpgroups
+      if (tr) JVPFA_FTR(1 + wg, it, 2);
+      xch[it & 1][wg][r] = m_tile;
+      named_bar_sync(1, 256);
+      if (tr) JVPFA_FTR(1 + wg, it, 3);
+      m_tile = fmaxf(m_tile, xch[it & 1][wg ^ 1][r]);
       const float m_new = fmaxf(m_used, m_tile);
       const bool need = m_new > m_used + p.thresh;
-      if (__any_sync(0xFFFFFFFFu, need)) {
+      if (__any_sync(0xFFFFFFFFu, need)) {   // same rows, same values in both warpgroups: same decision
         const float alpha = (m_used == -INFINITY) ? 1.0f : fast_exp2(m_used - m_new);
         if (it > 0) {
           mbar_wait(&o_done, (it - 1) & 1, w, 31);
           tc_fence_after_sync();
+          // warpgroup 0 rescales O, warpgroup 1 rescales T
+          if (DUAL || wg == 0) {
+            const uint32_t base = tmem + lane_off + (wg == 0 ? C::TMEM_O : C::TMEM_T);
 #pragma unroll
-          for (int c = 0; c < (DUAL ? 2 : 1) * D / 32; ++c) {
-            uint32_t a[32];
-            tmem_ld_x32(tmem + lane_off + c * 32, a);
-            tmem_wait_ld();
+            for (int c = 0; c < D / 32; ++c) {
+              uint32_t a[32];
+              tmem_ld_x32(base + c * 32, a);
+              tmem_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) a[i] = __float_as_uint(__uint_as_float(a[i]) * alpha);
-            tmem_st_x32(tmem + lane_off + c * 32, a);
+              for (int i = 0; i < 32; ++i) a[i] = __float_as_uint(__uint_as_float(a[i]) * alpha);
+              tmem_st_x32(base + c * 32, a);
+            }
           }
         }
         l *= alpha;
@@ -316,38 +368,50 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         m_used = m_new;
       }
       const float m_eff = (m_used == -INFINITY) ? 0.f : m_used;
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      if (tr) JVPFA_FTR(1 + wg, it, 4);
+      {
         uint32_t ts[32];
         if constexpr (DUAL) {
-          tmem_ld_x32(tS_t + 32 * c, ts);
+          tmem_ld_x32(tS_t, ts);
           tmem_wait_ld();
         }
-        uint32_t pk[16], wk[16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float p0 = fast_exp2(x[32 * c + 2 * i] - m_eff);
-          const float p1 = fast_exp2(x[32 * c + 2 * i + 1] - m_eff);
-          l += p0 + p1;
-          pk[i] = pack2<BF16>(p0, p1);
-          if constexpr (DUAL) {
-            const float w0 = p0 * (__uint_as_float(ts[2 * i]) * p.s);
-            const float w1 = p1 * (__uint_as_float(ts[2 * i + 1]) * p.s);
-            mu += w0 + w1;
-            wk[i] = pack2<BF16>(w0, w1);
+        for (int c = 0; c < 2; ++c) {
+          uint32_t pk[8], wk[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int i0 = 16 * c + 2 * i, i1 = i0 + 1;
+            const float p0 = fast_exp2(x[i0] - m_eff);
+            const float p1 = fast_exp2(x[i1] - m_eff);
+            l += p0 + p1;
+            pk[i] = pack2<BF16>(p0, p1);
+            if constexpr (DUAL) {
+              const float w0 = p0 * (__uint_as_float(ts[i0]) * p.s);
+              const float w1 = p1 * (__uint_as_float(ts[i1]) * p.s);
+              mu += w0 + w1;
+              wk[i] = pack2<BF16>(w0, w1);
+            }
           }
+          tmem_st_x8(S_t + 8 * c, pk);
+          if constexpr (DUAL) tmem_st_x8(tS_t + 8 * c, wk);
         }
-        tmem_st_x16(S_t + 16 * c, pk);
-        if constexpr (DUAL) tmem_st_x16(tS_t + 16 * c, wk);
       }
+      if (tr) JVPFA_FTR(1 + wg, it, 5);
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive(&p_full[it & 1]);
+      if (tr) JVPFA_FTR(1 + wg, it, 6);
       ++it;
     }
-    // epilogue
+    // epilogue: total row sums over both warpgroups, then each warpgroup writes half of the head dimension.
     // o_done flips once per key tile and a parity wait is only meaningful within one phase of the
     // barrier, so the end of the last accumulation has a barrier of its own.
+    named_bar_sync(1, 256);
+    xch[0][wg][r] = l;
+    xch[1][wg][r] = mu;
+    named_bar_sync(1, 256);
+    l += xch[0][wg ^ 1][r];
+    mu += xch[1][wg ^ 1][r];
     if (it > 0) {
       mbar_wait(&o_final, 0, w, 32);
       tc_fence_after_sync();
@@ -356,7 +420,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const float mul = mu * linv;
     const size_t orow = (static_cast<size_t>(row_base) + qi) * D;
 #pragma unroll
-    for (int c = 0; c < D / 32; ++c) {
+    for (int c = wg * (D / 64); c < (wg + 1) * (D / 64); ++c) {
       uint32_t ov[32], tv[32];
       if (it > 0) {
         tmem_ld_x32(tmem + lane_off + C::TMEM_O + c * 32, ov);
@@ -388,14 +452,14 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
       }
     }
-    if (qi < N) {
+    if (qi < N && wg == 0) {
       p.lse2[static_cast<size_t>(row_base) + qi] = (l > 0.f) ? m_used + log2f(l) : -INFINITY;
       p.mu[static_cast<size_t>(row_base) + qi] = mul;
     }
   }
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 5) tmem_dealloc(tmem, C::TMEM_COLS);
+  if (warp == 9) tmem_dealloc(tmem, C::TMEM_COLS);
 }
 
 template <int D, bool DUAL, bool BF16>
@@ -403,10 +467,10 @@ int launch_one(const jvpfa_fwd_args& a, cudaStream_t stream) {
   using C = FwdCfg<D>;
   const uint64_t rows = static_cast<uint64_t>(a.B) * a.H * a.N;
   CUtensorMap mQ, mTQ, mK, mTK, mV, mTV;
-  bool ok = make_tile_map(&mQ, a.q, rows, D, C::BM, a.dtype) && make_tile_map(&mK, a.k, rows, D, C::BN, a.dtype) &&
+  bool ok = make_tile_map(&mQ, a.q, rows, D, C::BM, a.dtype) && make_tile_map(&mK, a.k, rows, D, C::BN, a.dtype, 1) &&
             make_tile_map(&mV, a.v, rows, D, C::BN, a.dtype);
   if (DUAL) {
-    ok = ok && make_tile_map(&mTQ, a.tq, rows, D, C::BM, a.dtype) && make_tile_map(&mTK, a.tk, rows, D, C::BN, a.dtype) &&
+    ok = ok && make_tile_map(&mTQ, a.tq, rows, D, C::BM, a.dtype) && make_tile_map(&mTK, a.tk, rows, D, C::BN, a.dtype, 1) &&
          make_tile_map(&mTV, a.tv, rows, D, C::BN, a.dtype);
   } else {
     mTQ = mQ; mTK = mK; mTV = mV;
@@ -426,16 +490,22 @@ int launch_one(const jvpfa_fwd_args& a, cudaStream_t stream) {
   p.status = static_cast<int*>(a.workspace);
   p.budget_ns = wait_budget_ns();
   auto kern = fwd_sm100_kernel<D, DUAL, BF16>;
-  const size_t smem = C::smem_bytes(DUAL);
+  const size_t smem = C::smem_bytes();
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
     return JVPFA_ERR_LAUNCH;
   dim3 grid((a.N + C::BM - 1) / C::BM, a.B * a.H);
   ScopedKernelTimer timer(KERNEL_FWD, stream);
-  kern<<<grid, 192, smem, stream>>>(mQ, mTQ, mK, mTK, mV, mTV, p);
+  kern<<<grid, 320, smem, stream>>>(mQ, mTQ, mK, mTK, mV, mTV, p);
   return cudaGetLastError() == cudaSuccess ? JVPFA_OK : JVPFA_ERR_LAUNCH;
 }
 
 }  // namespace
+
+#ifdef JVPFA_TRACE
+extern "C" int jvpfa_fwd_trace_read(long long* host_out) {
+  return cudaMemcpyFromSymbol(host_out, g_fwd_trace, sizeof(g_fwd_trace)) == cudaSuccess ? 0 : 1;
+}
+#endif
 
 bool sm100_path_supported(int dtype, int D, int N) {
   return (dtype == JVPFA_BF16 || dtype == JVPFA_F16) && (D == 64 || D == 128) && N >= 1;
