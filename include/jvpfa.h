@@ -111,6 +111,29 @@ int jvpfa_bwd(const jvpfa_bwd_args* args, void* stream);
  * 100 + the id of the wait that gave up). */
 int jvpfa_read_status(void* workspace, void* stream, int32_t* detail);
 
+/* Largest problem (B*H*N query rows) the allocation-free backward accepts; its scratch is 256 B + 16 B per row. */
+#define JVPFA_NO_ALLOC_MAX_ROWS 262144
+
+/* Dual backward that allocates nothing. It has no counterpart in the reference (whose backward allocates
+ * its scratch with torch, jvp_attention.py:3130-3133, 3153).
+ *
+ * For callers that cannot or must not allocate device memory: a plug-in inside a process whose memory
+ * pool already holds nearly all of the GPU's memory (cudaMalloc would fail), or a latency-critical
+ * path that must avoid the device-wide synchronisation of cudaMalloc / cudaFree. Same inputs, outputs
+ * and results as jvpfa_bwd, except that `workspace` / `workspace_bytes` in `args` are ignored: the
+ * scratch (status word + per-row statistics) is a fixed array inside the library image, 4 MiB + 256 B,
+ * held by every GPU that loads the library until the process exits. Problems with more than
+ * JVPFA_NO_ALLOC_MAX_ROWS rows (B*H*N) are refused with JVPFA_ERR_NO_ALLOC_LIMIT before anything runs.
+ *
+ * The first call on each device looks up the device address of that array (with that device current);
+ * make that first call before starting any stream capture. Every call clears the status word at the
+ * start of the array on `stream` and then reuses the rest as it is. All calls on a device share the
+ * one array: two calls whose kernels can overlap on the GPU (different streams without an ordering
+ * between them) race on it and give undefined results -- order them yourself.
+ * If `status_word_out` (a device pointer) is not NULL the status word is copied there after the
+ * kernels, on `stream`: 0 means no device-side wait gave up. */
+int jvpfa_bwd_noalloc(const jvpfa_bwd_args* args, int32_t* status_word_out, void* stream);
+
 /* Per-kernel timing for benchmarks. Collects what was measured since the last call -- summed
  * milliseconds and launch counts for the five kernel kinds, in the order forward, backward
  * preprocess, backward family Q, K, V (either pointer may be NULL) -- waits for those launches

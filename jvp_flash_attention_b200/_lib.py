@@ -31,6 +31,7 @@ EXPORTED_SYMBOLS = (
     "jvpfa_bwd",
     "jvpfa_read_status",
     "jvpfa_kernel_timing",
+    "jvpfa_bwd_noalloc",
 )
 
 
@@ -111,6 +112,8 @@ def lib():
                 L.jvpfa_read_status.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_int32)]
                 L.jvpfa_kernel_timing.restype = C.c_int
                 L.jvpfa_kernel_timing.argtypes = [C.c_int, C.POINTER(C.c_float), C.POINTER(C.c_int32)]
+                L.jvpfa_bwd_noalloc.restype = C.c_int
+                L.jvpfa_bwd_noalloc.argtypes = [C.POINTER(BwdArgs), C.c_void_p, C.c_void_p]
                 _lib = L
     return _lib
 
