@@ -193,9 +193,6 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const uint32_t ph = (it / ST) & 1;
         const int krow = row_base + j * C::BN;
         mbar_wait(&k_empty[st], ph ^ 1, w, 10);
-#if defined(JVPFA_EXP) && JVPFA_EXP == 1
-        if (it >= ST) { mbar_arrive(&k_full[st]); mbar_wait(&v_empty[st], ph ^ 1, w, 11); mbar_arrive(&v_full[st]); ++it; continue; }
-#endif
         mbar_arrive_expect_tx(&k_full[st], (DUAL ? 2 : 1) * C::TILE_V);
 #pragma unroll
         for (int sl = 0; sl < SLABS; ++sl) {
@@ -308,12 +305,6 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_wait(&s_full[it & 1], (it >> 1) & 1, w, 30);
       tc_fence_after_sync();
       if (tr) JVPFA_FTR(1 + wg, it, 1);
-#if defined(JVPFA_EXP) && JVPFA_EXP == 6
-      tc_fence_before_sync();
-      mbar_arrive(&p_full[it & 1]);
-      ++it;
-      continue;
-#endif
       float x[32];
       {
         uint32_t r0[32];
@@ -347,12 +338,10 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       for (int i = 1; i < 32; ++i) m_tile = fmaxf(m_tile, x[i]);
       // row maximum over both warpgroups
       if (tr) JVPFA_FTR(1 + wg, it, 2);
-#if !(defined(JVPFA_EXP) && JVPFA_EXP == 3)
       xch[it & 1][wg][r] = m_tile;
       named_bar_sync(1, 256);
       if (tr) JVPFA_FTR(1 + wg, it, 3);
       m_tile = fmaxf(m_tile, xch[it & 1][wg ^ 1][r]);
-#endif
       const float m_new = fmaxf(m_used, m_tile);
       const bool need = m_new > m_used + p.thresh;
       if (__any_sync(0xFFFFFFFFu, need)) {   // same rows, same values in both warpgroups: same decision
@@ -382,28 +371,18 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (tr) JVPFA_FTR(1 + wg, it, 4);
       {
         uint32_t ts[32];
-#if defined(JVPFA_EXP) && JVPFA_EXP == 5
-#pragma unroll
-        for (int i = 0; i < 32; ++i) ts[i] = __float_as_uint(x[i]);
-#else
         if constexpr (DUAL) {
           tmem_ld_x32(tS_t, ts);
           tmem_wait_ld();
         }
-#endif
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           uint32_t pk[8], wk[8];
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             const int i0 = 16 * c + 2 * i, i1 = i0 + 1;
-#if defined(JVPFA_EXP) && JVPFA_EXP == 2
-            const float p0 = x[i0] - m_eff;
-            const float p1 = x[i1] - m_eff;
-#else
             const float p0 = fast_exp2(x[i0] - m_eff);
             const float p1 = fast_exp2(x[i1] - m_eff);
-#endif
             l += p0 + p1;
             pk[i] = pack2<BF16>(p0, p1);
             if constexpr (DUAL) {
@@ -413,12 +392,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
               wk[i] = pack2<BF16>(w0, w1);
             }
           }
-#if !(defined(JVPFA_EXP) && JVPFA_EXP == 4)
           tmem_st_x8(S_t + 8 * c, pk);
           if constexpr (DUAL) tmem_st_x8(tS_t + 8 * c, wk);
-#else
-          if (pk[0] == 0x12345678u && wk[0] == 0x9abcdef0u) p.lse2[0] = 1.f;
-#endif
         }
       }
       if (tr) JVPFA_FTR(1 + wg, it, 5);
