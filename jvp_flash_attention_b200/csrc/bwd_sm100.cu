@@ -128,7 +128,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
   auto sA = [&](int k) { return smem + C::NR * C::TILE_R + k * C::PAIR; };
   auto sB = [&](int k) { return smem + C::NR * C::TILE_R + (NA + k) * C::PAIR; };
   uint8_t* tail = smem + C::NR * C::TILE_R + (NA + NB) * C::PAIR;
-  float4(*stats_s)[C::BC] = reinterpret_cast<float4(*)[C::BC]>(tail);
+  // per-query statistics of the current column tile, negated, one array per field: [buffer][-lse2, -mu, -Delta, -a][column]
+  float(*stats_s)[4][C::BC] = reinterpret_cast<float(*)[4][C::BC]>(tail);
   uint64_t* bars = reinterpret_cast<uint64_t*>(tail + 2 * C::BC * sizeof(float4));
   uint64_t& r_full = bars[0];
   uint64_t* st_full = bars + 1;   // [2] (family V uses both, Q/K only [0])
@@ -373,11 +374,14 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
     const bool tr = (lane == 0 && (warp & 3) == 0);
     const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t TS0 = tmem + C::TMEM_T + lane_off;
-    float4 st_row = make_float4(0.f, 0.f, 0.f, 0.f);
+    // negated statistics of this thread's query row (family Q): -lse2, -mu, -Delta, -a
+    float4 nst = make_float4(0.f, 0.f, 0.f, 0.f);
     if (FAM == FAM_Q) {
-      st_row = p.stats[static_cast<size_t>(row_base) + gr_c];
-      if (st_row.x == -INFINITY) st_row.x = INFINITY;  // fully excluded query: P = 0
+      const float4 st = p.stats[static_cast<size_t>(row_base) + gr_c];
+      nst = make_float4(-st.x, -st.y, -st.z, -st.w);
+      if (st.x == -INFINITY) nst.x = -INFINITY;  // fully excluded query: P = 0
     }
+    const float2 c1_2 = make_float2(p.c1, p.c1), s_2 = make_float2(p.s, p.s);
     int it = 0;
     for (int j = next_active(j_begin); j < j_end; j = next_active(j + 1), ++it) {
       const uint8_t bits = tile_bits(j);
@@ -390,18 +394,30 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
             sv = p.stats[static_cast<size_t>(row_base) + c0 + tid];
             if (sv.x == -INFINITY) sv.x = INFINITY;
           }
-          stats_s[it & 1][tid] = sv;
+          stats_s[it & 1][0][tid] = -sv.x;
+          stats_s[it & 1][1][tid] = -sv.y;
+          stats_s[it & 1][2][tid] = -sv.z;
+          stats_s[it & 1][3][tid] = -sv.w;
         }
         named_bar_sync(1, 256);
       }
+      // pair of negated statistics for columns (2 i, 2 i + 1) of this thread
+      auto stat2 = [&](int field, int i) -> float2 {
+        if (FAM == FAM_Q) {
+          const float v = field == 0 ? nst.x : (field == 1 ? nst.y : (field == 2 ? nst.z : nst.w));
+          return make_float2(v, v);
+        }
+        return *reinterpret_cast<const float2*>(&stats_s[it & 1][field][32 * wg + 2 * i]);
+      };
       const int sb = (FAM == FAM_V) ? (it & 1) : 0;
       const uint32_t T0 = TS0 + sb * 128 + 32 * wg, T1 = T0 + 64;
       if (tr) JVPFA_TR(1 + wg, it, 0);
       mbar_wait(&st_full[sb], (FAM == FAM_V) ? ((it >> 1) & 1) : (it & 1), w, 30);
       tc_fence_after_sync();
       if (tr) JVPFA_TR(1 + wg, it, 1);
-      // ---- phase 1: P and ts of this thread's 32 columns
-      float P[32], ts[32];
+      // ---- phase 1: P and ts of this thread's 32 columns (packed fp32x2 arithmetic: the element-wise
+      // warps share their schedulers with the MMA-issuing warp, so every instruction saved here counts)
+      float2 P2[16], ts2[16];
       {
         uint32_t a0[32], a1[32];
         tmem_ld_x32(T0, a0);
@@ -415,36 +431,42 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
         const bool need_causal = p.causal && ((FAM == FAM_Q) ? (c0 + C::BC - 1 > r0) : (r0 + C::BR - 1 > c0));
         const bool need_bound = (FAM == FAM_Q) && (c0 + C::BC > N);
         const bool need_mask = p.mv.kind != JVPFA_MASK_NONE && (bits & kTileAnyMasked);
+        float2 x2[16];
 #pragma unroll
-        for (int hch = 0; hch < 2; ++hch) {
-          float bias[16];
+        for (int i = 0; i < 16; ++i) {
+          x2[i] = __ffma2_rn(make_float2(__uint_as_float(a0[2 * i]), __uint_as_float(a0[2 * i + 1])), c1_2, stat2(0, i));
+          ts2[i] = __fmul2_rn(make_float2(__uint_as_float(a1[2 * i]), __uint_as_float(a1[2 * i + 1])), s_2);
+        }
+        if (need_causal || need_bound || need_mask) {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) bias[i] = 0.f;
-          if (need_mask) {
-            if (FAM == FAM_Q) mask_bias_run<16>(bias, p.mv, b, h, gr_c, cw + 16 * hch, N, true);
-            else mask_bias_run<16>(bias, p.mv, b, h, cw + 16 * hch, gr_c, N, false);
-          }
-          if (need_causal) {
+          for (int hch = 0; hch < 2; ++hch) {
+            float bias[16];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const int col = cw + 16 * hch + i;
-              const bool ok = (FAM == FAM_Q) ? (col <= gr) : (gr <= col);
-              if (!ok) bias[i] = -INFINITY;
+            for (int i = 0; i < 16; ++i) bias[i] = 0.f;
+            if (need_mask) {
+              if (FAM == FAM_Q) mask_bias_run<16>(bias, p.mv, b, h, gr_c, cw + 16 * hch, N, true);
+              else mask_bias_run<16>(bias, p.mv, b, h, cw + 16 * hch, gr_c, N, false);
             }
-          }
-          if (need_bound) {
+            if (need_causal) {
 #pragma unroll
-            for (int i = 0; i < 16; ++i)
-              if (cw + 16 * hch + i >= N) bias[i] = -INFINITY;
-          }
+              for (int i = 0; i < 16; ++i) {
+                const int col = cw + 16 * hch + i;
+                const bool ok = (FAM == FAM_Q) ? (col <= gr) : (gr <= col);
+                if (!ok) bias[i] = -INFINITY;
+              }
+            }
+            if (need_bound) {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const int ii = 16 * hch + i;
-            const float lse = (FAM == FAM_Q) ? st_row.x : stats_s[it & 1][32 * wg + ii].x;
-            P[ii] = fast_exp2(fmaf(__uint_as_float(a0[ii]), p.c1, bias[i]) - lse);
-            ts[ii] = __uint_as_float(a1[ii]) * p.s;
+              for (int i = 0; i < 16; ++i)
+                if (cw + 16 * hch + i >= N) bias[i] = -INFINITY;
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              x2[8 * hch + i] = __fadd2_rn(x2[8 * hch + i], make_float2(bias[2 * i], bias[2 * i + 1]));
           }
         }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) P2[i] = make_float2(fast_exp2(x2[i].x), fast_exp2(x2[i].y));
       }
       if (tr) JVPFA_TR(1 + wg, it, 3);
       if constexpr (FAM == FAM_V) {
@@ -454,45 +476,40 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
           uint32_t e0[8], e1[8];
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
-            const int i0 = 16 * hch + 2 * i, i1 = i0 + 1;
-            const float mu0 = stats_s[it & 1][32 * wg + i0].y, mu1 = stats_s[it & 1][32 * wg + i1].y;
-            e0[i] = pack2<BF16>(P[i0], P[i1]);
-            e1[i] = pack2<BF16>(P[i0] * (ts[i0] - mu0), P[i1] * (ts[i1] - mu1));
+            const int ip = 8 * hch + i;
+            const float2 tp = __fmul2_rn(P2[ip], __fadd2_rn(ts2[ip], stat2(1, ip)));
+            e0[i] = pack2<BF16>(P2[ip].x, P2[ip].y);
+            e1[i] = pack2<BF16>(tp.x, tp.y);
           }
           tmem_st_x8(T0 + 8 * hch, e0);
           tmem_st_x8(T1 + 8 * hch, e1);
         }
       } else {
-        // ---- phase 2: X, A -> dS, dtS
+        // ---- phase 2: X, A -> dS = P (X - Delta + ts (A - a) - mu A), dtS = P (A - a)
         const uint32_t T2 = TS0 + 128 + 32 * wg, T3 = T2 + 64;
         mbar_wait(&xa_full, it & 1, w, 31);
         tc_fence_after_sync();
         if (tr) JVPFA_TR(1 + wg, it, 4);
 #pragma unroll
         for (int hch = 0; hch < 2; ++hch) {
-          uint32_t x2[16], x3[16];
-          tmem_ld_x16(T2 + 16 * hch, x2);
-          tmem_ld_x16(T3 + 16 * hch, x3);
+          uint32_t x2r[16], x3r[16];
+          tmem_ld_x16(T2 + 16 * hch, x2r);
+          tmem_ld_x16(T3 + 16 * hch, x3r);
           tmem_wait_ld();
           uint32_t e0[8], e1[8];
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
-            float v0[2], v1[2];
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-              const int ii = 2 * i + u, ic = 16 * hch + ii;
-              float4 sq;
-              if (FAM == FAM_Q) sq = st_row;
-              else sq = stats_s[it & 1][32 * wg + ic];
-              const float A = __uint_as_float(FAM == FAM_Q ? x2[ii] : x3[ii]);
-              const float X = __uint_as_float(FAM == FAM_Q ? x3[ii] : x2[ii]);
-              const float d = A - sq.w;                                   // A - a
-              const float t = fmaf(ts[ic], d, X - sq.z) - sq.y * A;      // X - Delta + ts (A - a) - mu A
-              v0[u] = P[ic] * t;   // dS
-              v1[u] = P[ic] * d;   // dtS
-            }
-            e0[i] = pack2<BF16>(v0[0], v0[1]);
-            e1[i] = pack2<BF16>(v1[0], v1[1]);
+            const int ip = 8 * hch + i;
+            const float2 t2v = make_float2(__uint_as_float(x2r[2 * i]), __uint_as_float(x2r[2 * i + 1]));
+            const float2 t3v = make_float2(__uint_as_float(x3r[2 * i]), __uint_as_float(x3r[2 * i + 1]));
+            const float2 A = (FAM == FAM_Q) ? t2v : t3v;
+            const float2 X = (FAM == FAM_Q) ? t3v : t2v;
+            const float2 d = __fadd2_rn(A, stat2(3, ip));                       // A - a
+            float2 t = __ffma2_rn(ts2[ip], d, __fadd2_rn(X, stat2(2, ip)));     // X - Delta + ts (A - a)
+            t = __ffma2_rn(stat2(1, ip), A, t);                                 // - mu A
+            const float2 ds = __fmul2_rn(P2[ip], t), dts = __fmul2_rn(P2[ip], d);
+            e0[i] = pack2<BF16>(ds.x, ds.y);
+            e1[i] = pack2<BF16>(dts.x, dts.y);
           }
           tmem_st_x8(T2 + 8 * hch, e0);
           tmem_st_x8(T3 + 8 * hch, e1);

@@ -293,7 +293,9 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const int qi = q0 + r;
     const int qi_c = min(qi, N - 1);
     const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    float m_used = -INFINITY, l = 0.f, mu = 0.f;   // l, mu: partial sums over this thread's columns
+    float m_used = -INFINITY;
+    float2 l2 = make_float2(0.f, 0.f), mu2 = make_float2(0.f, 0.f);   // partial row sums over this thread's columns
+    const float2 c1_2 = make_float2(p.c1, p.c1), s_2 = make_float2(p.s, p.s);
     int it = 0;
     for (int j = 0; j < n_kt; ++j) {
       const uint8_t bits = tile_bits(j);
@@ -305,37 +307,45 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_wait(&s_full[it & 1], (it >> 1) & 1, w, 30);
       tc_fence_after_sync();
       if (tr) JVPFA_FTR(1 + wg, it, 1);
-      float x[32];
+      // scores of this thread's 32 columns in the log2 domain, two per register pair (packed fp32x2
+      // arithmetic: the softmax warps share their schedulers with the MMA-issuing warp)
+      float2 x2[16];
       {
         uint32_t r0[32];
         tmem_ld_x32(S_t, r0);
         tmem_wait_ld();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) x[i] = __uint_as_float(r0[i]) * p.c1;
+        for (int i = 0; i < 16; ++i)
+          x2[i] = __fmul2_rn(make_float2(__uint_as_float(r0[2 * i]), __uint_as_float(r0[2 * i + 1])), c1_2);
       }
       const int k0 = j * C::BN + 32 * wg;   // first key of this thread's columns
-      if (p.causal && j * C::BN + C::BN - 1 > q0) {
-#pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (k0 + i > qi) x[i] = -INFINITY;
-      }
-      if (j * C::BN + C::BN > N) {
-#pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (k0 + i >= N) x[i] = -INFINITY;
-      }
-      if (p.mv.kind != JVPFA_MASK_NONE && (bits & kTileAnyMasked)) {
+      const bool need_causal = p.causal && j * C::BN + C::BN - 1 > q0;
+      const bool need_bound = j * C::BN + C::BN > N;
+      const bool need_mask = p.mv.kind != JVPFA_MASK_NONE && (bits & kTileAnyMasked);
+      if (need_causal || need_bound || need_mask) {
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           float bias[16];
-          mask_bias_run<16>(bias, p.mv, b, h, qi_c, k0 + 16 * c, N, true);
 #pragma unroll
-          for (int i = 0; i < 16; ++i) x[16 * c + i] += bias[i];
+          for (int i = 0; i < 16; ++i) bias[i] = 0.f;
+          if (need_mask) mask_bias_run<16>(bias, p.mv, b, h, qi_c, k0 + 16 * c, N, true);
+          if (need_causal) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              if (k0 + 16 * c + i > qi) bias[i] = -INFINITY;
+          }
+          if (need_bound) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              if (k0 + 16 * c + i >= N) bias[i] = -INFINITY;
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) x2[8 * c + i] = __fadd2_rn(x2[8 * c + i], make_float2(bias[2 * i], bias[2 * i + 1]));
         }
       }
-      float m_tile = x[0];
+      float m_tile = fmaxf(x2[0].x, x2[0].y);
 #pragma unroll
-      for (int i = 1; i < 32; ++i) m_tile = fmaxf(m_tile, x[i]);
+      for (int i = 1; i < 16; ++i) m_tile = fmaxf(m_tile, fmaxf(x2[i].x, x2[i].y));
       // row maximum over both warpgroups
       if (tr) JVPFA_FTR(1 + wg, it, 2);
       xch[it & 1][wg][r] = m_tile;
@@ -363,11 +373,12 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             }
           }
         }
-        l *= alpha;
-        mu *= alpha;
+        l2.x *= alpha; l2.y *= alpha;
+        mu2.x *= alpha; mu2.y *= alpha;
         m_used = m_new;
       }
       const float m_eff = (m_used == -INFINITY) ? 0.f : m_used;
+      const float2 nm2 = make_float2(-m_eff, -m_eff);
       if (tr) JVPFA_FTR(1 + wg, it, 4);
       {
         uint32_t ts[32];
@@ -380,16 +391,16 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           uint32_t pk[8], wk[8];
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
-            const int i0 = 16 * c + 2 * i, i1 = i0 + 1;
-            const float p0 = fast_exp2(x[i0] - m_eff);
-            const float p1 = fast_exp2(x[i1] - m_eff);
-            l += p0 + p1;
-            pk[i] = pack2<BF16>(p0, p1);
+            const int ip = 8 * c + i;
+            const float2 e = __fadd2_rn(x2[ip], nm2);
+            const float2 pp = make_float2(fast_exp2(e.x), fast_exp2(e.y));
+            l2 = __fadd2_rn(l2, pp);
+            pk[i] = pack2<BF16>(pp.x, pp.y);
             if constexpr (DUAL) {
-              const float w0 = p0 * (__uint_as_float(ts[i0]) * p.s);
-              const float w1 = p1 * (__uint_as_float(ts[i1]) * p.s);
-              mu += w0 + w1;
-              wk[i] = pack2<BF16>(w0, w1);
+              const float2 tsv = __fmul2_rn(make_float2(__uint_as_float(ts[2 * ip]), __uint_as_float(ts[2 * ip + 1])), s_2);
+              const float2 ww = __fmul2_rn(pp, tsv);
+              mu2 = __fadd2_rn(mu2, ww);
+              wk[i] = pack2<BF16>(ww.x, ww.y);
             }
           }
           tmem_st_x8(S_t + 8 * c, pk);
@@ -406,6 +417,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     // epilogue: total row sums over both warpgroups, then each warpgroup writes half of the head dimension.
     // o_done flips once per key tile and a parity wait is only meaningful within one phase of the
     // barrier, so the end of the last accumulation has a barrier of its own.
+    float l = l2.x + l2.y, mu = mu2.x + mu2.y;
     named_bar_sync(1, 256);
     xch[0][wg][r] = l;
     xch[1][wg][r] = mu;
