@@ -23,6 +23,7 @@
 // Roles: warps 0-7 element-wise as two warpgroups that split the 64 columns of every score tile
 // (thread = TMEM lane = one score row, 32 columns), warp 8 TMA producer, warp 9 MMA issuer. Column-side tiles flow through a ring of shared-memory slots in the
 // order in which the MMA issuer releases them (tiles only the score MMAs read come first).
+#include <type_traits>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include "host_common.h"
@@ -50,6 +51,7 @@ __device__ long long g_bwd_trace[3 * 3 * 64 * 8];  // [family][role][tile][stamp
 
 struct BwdKParams {
   int H, N;
+  int D;     // head dimension of the tensors (the kernel is compiled for it rounded up to 64 or 128)
   int causal;
   float c1;  // sm_scale * log2(e)
   float s;   // sm_scale
@@ -110,7 +112,9 @@ struct BwdCfg {
 // Families Q and K keep one set of score tiles and overlap in two phases per tile: phase 1 reads S, tS
 // (which frees them for the next tile's products), phase 2 reads X, A and writes the 16-bit dS, dtS operands;
 // family V double-buffers S, tS.
-template <int D, int FAM, bool BF16>
+// PAD: the tensors' head dimension is smaller than D (columns beyond it are zero-filled by TMA); the K steps and
+// output columns that would only see zeros are then skipped at run time.
+template <int D, int FAM, bool BF16, bool PAD>
 __global__ void __launch_bounds__(320, 1)
 bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant__ CUtensorMap rm1,
                  const __grid_constant__ CUtensorMap rm2, const __grid_constant__ CUtensorMap rm3,
@@ -219,11 +223,14 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       mbar_arrive_expect_tx(&r_full, C::NR * C::TILE_R);
-      tma_load_3d(sR(0), &rm0, &r_full, 0, row_base + r0, 0);
-      tma_load_3d(sR(1), &rm1, &r_full, 0, row_base + r0, 0);
-      if constexpr (C::NR == 4) {
-        tma_load_3d(sR(2), &rm2, &r_full, 0, row_base + r0, 0);
-        tma_load_3d(sR(3), &rm3, &r_full, 0, row_base + r0, 0);
+#pragma unroll
+      for (int sl = 0; sl < SLABS; ++sl) {
+        tma_load_2d(sR(0) + sl * C::SLAB, &rm0, &r_full, 64 * sl, row_base + r0);
+        tma_load_2d(sR(1) + sl * C::SLAB, &rm1, &r_full, 64 * sl, row_base + r0);
+        if constexpr (C::NR == 4) {
+          tma_load_2d(sR(2) + sl * C::SLAB, &rm2, &r_full, 64 * sl, row_base + r0);
+          tma_load_2d(sR(3) + sl * C::SLAB, &rm3, &r_full, 64 * sl, row_base + r0);
+        }
       }
       int it = 0;
       for (int j = next_active(j_begin); j < j_end; j = next_active(j + 1), ++it) {
@@ -234,8 +241,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
           mbar_arrive_expect_tx(&a_full[buf], C::PAIR);
 #pragma unroll
           for (int sl = 0; sl < SLABS; ++sl) {
-            tma_load_3d(sA(buf) + sl * C::SLAB, &cm0, &a_full[buf], 0, crow, sl);
-            tma_load_3d(sA(buf) + sl * C::SLAB + C::HALF, &cm1, &a_full[buf], 0, crow, sl);
+            tma_load_2d(sA(buf) + sl * C::SLAB, &cm0, &a_full[buf], 64 * sl, crow);
+            tma_load_2d(sA(buf) + sl * C::SLAB + C::HALF, &cm1, &a_full[buf], 64 * sl, crow);
           }
         }
         {
@@ -244,8 +251,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
           mbar_arrive_expect_tx(&b_full[buf], C::PAIR);
 #pragma unroll
           for (int sl = 0; sl < SLABS; ++sl) {
-            tma_load_3d(sB(buf) + sl * C::SLAB, &cm2, &b_full[buf], 0, crow, sl);
-            tma_load_3d(sB(buf) + sl * C::SLAB + C::HALF, &cm3, &b_full[buf], 0, crow, sl);
+            tma_load_2d(sB(buf) + sl * C::SLAB, &cm2, &b_full[buf], 64 * sl, crow);
+            tma_load_2d(sB(buf) + sl * C::SLAB + C::HALF, &cm3, &b_full[buf], 64 * sl, crow);
           }
         }
       }
@@ -263,7 +270,9 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
       constexpr uint32_t FMT = BF16 ? FMT_BF16 : FMT_F16;
       const uint32_t idesc_64 = make_idesc(FMT, 128, 64, 0, 0);
       const uint32_t idesc_128 = make_idesc(FMT, 128, 128, 0, 0);
-      const uint32_t idesc_out = make_idesc(FMT, 128, D, 0, 1);
+      const int dn = PAD ? ((p.D + 15) & ~15) : D;   // head dimension rounded up to the MMA granularity
+      const int ksteps = dn / 16;                     // K steps of the score products that hold data
+      const uint32_t idesc_out = make_idesc(FMT, 128, dn, 0, 1);
       const uint32_t TS0 = tmem + C::TMEM_T;
 
       // dst[128 x n] (+)= R[128 x D] * Cc[n x D]^T, Cc = n rows starting at `ctile` inside a pair buffer
@@ -273,7 +282,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint64_t o = static_cast<uint64_t>(((k >> 2) * C::SLAB + (k & 3) * 32) >> 4);
-          if (leader) umma_ss(dst, da + o, db + o, idesc, acc | (k > 0));
+          if (leader && (!PAD || k < ksteps)) umma_ss(dst, da + o, db + o, idesc, acc | (k > 0));
         }
       };
       // acc[128 x D] (+)= E[128 x 64] (TMEM, 16-bit, two column groups of 16) * Cc[64 x D]
@@ -524,7 +533,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
     // epilogue
     mbar_wait(&acc_final, 0, w, 32);
     tc_fence_after_sync();
-    const size_t orow = (static_cast<size_t>(row_base) + gr) * D;
+    const size_t orow = (static_cast<size_t>(row_base) + gr) * p.D;
 #pragma unroll
     for (int c = wg * (D / 64); c < (wg + 1) * (D / 64); ++c) {
       uint32_t a0[32], a1[32];
@@ -547,8 +556,10 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
         uint4* o1 = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.out1) + orow + c * 32);
 #pragma unroll
         for (int v4 = 0; v4 < 4; ++v4) {
-          o0[v4] = make_uint4(q0[4 * v4], q0[4 * v4 + 1], q0[4 * v4 + 2], q0[4 * v4 + 3]);
-          o1[v4] = make_uint4(q1[4 * v4], q1[4 * v4 + 1], q1[4 * v4 + 2], q1[4 * v4 + 3]);
+          if (c * 32 + v4 * 8 < p.D) {
+            o0[v4] = make_uint4(q0[4 * v4], q0[4 * v4 + 1], q0[4 * v4 + 2], q0[4 * v4 + 3]);
+            o1[v4] = make_uint4(q1[4 * v4], q1[4 * v4 + 1], q1[4 * v4 + 2], q1[4 * v4 + 3]);
+          }
         }
       }
     }
@@ -601,7 +612,7 @@ __global__ void bwd_preprocess_kernel(const uint16_t* __restrict__ o, const uint
   }
 }
 
-template <int D, int FAM, bool BF16>
+template <int D, int FAM, bool BF16, bool PAD>
 int launch_family(const jvpfa_bwd_args& a, const float4* stats, cudaStream_t stream) {
   using C = BwdCfg<D, FAM>;
   const uint64_t rows = static_cast<uint64_t>(a.B) * a.H * a.N;
@@ -624,11 +635,11 @@ int launch_family(const jvpfa_bwd_args& a, const float4* stats, cudaStream_t str
   }
   CUtensorMap rm[4], cm[4];
   for (int i = 0; i < 4; ++i) {
-    if (!make_tile_map(&rm[i], rsrc[i], rows, D, C::BR, a.dtype)) return JVPFA_ERR_LAUNCH;
-    if (!make_tile_map(&cm[i], csrc[i], rows, D, C::BC, a.dtype, 1)) return JVPFA_ERR_LAUNCH;
+    if (!make_tile_map(&rm[i], rsrc[i], rows, a.D, C::BR, a.dtype)) return JVPFA_ERR_LAUNCH;
+    if (!make_tile_map(&cm[i], csrc[i], rows, a.D, C::BC, a.dtype)) return JVPFA_ERR_LAUNCH;
   }
   BwdKParams p{};
-  p.H = a.H; p.N = a.N; p.causal = a.causal;
+  p.H = a.H; p.N = a.N; p.D = a.D; p.causal = a.causal;
   p.s = a.sm_scale;
   p.c1 = a.sm_scale * 1.4426950408889634f;
   p.out_scale = out_scale;
@@ -641,7 +652,7 @@ int launch_family(const jvpfa_bwd_args& a, const float4* stats, cudaStream_t str
   p.out0 = out0; p.out1 = out1;
   p.status = static_cast<int*>(a.workspace);
   p.budget_ns = wait_budget_ns();
-  auto kern = bwd_sm100_kernel<D, FAM, BF16>;
+  auto kern = bwd_sm100_kernel<D, FAM, BF16, PAD>;
   const size_t smem = C::smem_bytes();
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
     return JVPFA_ERR_LAUNCH;
@@ -661,14 +672,21 @@ int launch_all(const jvpfa_bwd_args& a, cudaStream_t stream) {
   ScopedKernelTimer timer(KERNEL_BWD_PREPROCESS, stream);
   bwd_preprocess_kernel<BF16><<<blocks, warps_per_block * 32, 0, stream>>>(
       static_cast<const uint16_t*>(a.o), static_cast<const uint16_t*>(a.to), static_cast<const uint16_t*>(a.go),
-      static_cast<const uint16_t*>(a.gto), a.lse2, a.mu, stats, rows, D);
+      static_cast<const uint16_t*>(a.gto), a.lse2, a.mu, stats, rows, a.D);
   }
   if (cudaGetLastError() != cudaSuccess) return JVPFA_ERR_LAUNCH;
-  int rc = launch_family<D, FAM_Q, BF16>(a, stats, stream);
+  if (a.D == D) {
+    int rc = launch_family<D, FAM_Q, BF16, false>(a, stats, stream);
+    if (rc != JVPFA_OK) return rc;
+    rc = launch_family<D, FAM_K, BF16, false>(a, stats, stream);
+    if (rc != JVPFA_OK) return rc;
+    return launch_family<D, FAM_V, BF16, false>(a, stats, stream);
+  }
+  int rc = launch_family<D, FAM_Q, BF16, true>(a, stats, stream);
   if (rc != JVPFA_OK) return rc;
-  rc = launch_family<D, FAM_K, BF16>(a, stats, stream);
+  rc = launch_family<D, FAM_K, BF16, true>(a, stats, stream);
   if (rc != JVPFA_OK) return rc;
-  return launch_family<D, FAM_V, BF16>(a, stats, stream);
+  return launch_family<D, FAM_V, BF16, true>(a, stats, stream);
 }
 
 }  // namespace
@@ -686,7 +704,7 @@ size_t bwd_sm100_workspace_bytes(const jvpfa_bwd_args& a) {
 int launch_bwd_sm100(const jvpfa_bwd_args& a, cudaStream_t stream) {
   if (a.gto == nullptr) return JVPFA_ERR_BAD_ARG;  // the tensor-core path wants an explicit (possibly zero) gtO
   const bool bf = a.dtype == JVPFA_BF16;
-  if (a.D == 64) return bf ? launch_all<64, true>(a, stream) : launch_all<64, false>(a, stream);
+  if (sm100_padded_dim(a.D) == 64) return bf ? launch_all<64, true>(a, stream) : launch_all<64, false>(a, stream);
   return bf ? launch_all<128, true>(a, stream) : launch_all<128, false>(a, stream);
 }
 

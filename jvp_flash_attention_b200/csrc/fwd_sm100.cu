@@ -12,6 +12,7 @@
 // Epilogue: O/l, tO = T/l - (mu/l) O/l, lse2 = m + log2 l, mu/l.
 // TMEM columns: O [0,D), T [D,2D), then two score buffers of (S 64 | tS 64) columns; P and W
 // overwrite the first 32 columns of S and tS of their buffer.
+#include <type_traits>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include "host_common.h"
@@ -37,6 +38,7 @@ __device__ long long g_fwd_trace[3 * 64 * 8];
 
 struct FwdKParams {
   int H, N;
+  int D;       // head dimension of the tensors (the kernel is compiled for it rounded up to 64 or 128)
   int causal;
   float c1;      // sm_scale * log2(e)
   float s;       // sm_scale
@@ -95,7 +97,9 @@ __device__ __forceinline__ void mbar_wait_warp(uint64_t* bar, uint32_t parity, c
 // one score row, 32 columns; the row maximum and the final row sums are exchanged through shared
 // memory); warp 8: TMA producer; warp 9: MMA issuer (all lanes run the loop so that operands stay
 // warp-uniform, lane 0 issues) and owner of the TMEM allocation.
-template <int D, bool DUAL, bool BF16>
+// PAD: the tensors' head dimension is smaller than D (columns beyond it are zero-filled by TMA); the K steps and
+// output columns that would only see zeros are then skipped at run time.
+template <int D, bool DUAL, bool BF16, bool PAD>
 __global__ void __launch_bounds__(320, 1)
 fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmTQ,
                  const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmTK,
@@ -184,8 +188,11 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tma_prefetch_desc(&tmK);
       tma_prefetch_desc(&tmV);
       mbar_arrive_expect_tx(&q_full, (DUAL ? 2 : 1) * C::TILE_Q);
-      tma_load_3d(sQ, &tmQ, &q_full, 0, row_base + q0, 0);
-      if constexpr (DUAL) tma_load_3d(sTQ, &tmTQ, &q_full, 0, row_base + q0, 0);
+#pragma unroll
+      for (int sl = 0; sl < SLABS; ++sl) {
+        tma_load_2d(sQ + sl * C::SLAB, &tmQ, &q_full, 64 * sl, row_base + q0);
+        if constexpr (DUAL) tma_load_2d(sTQ + sl * C::SLAB, &tmTQ, &q_full, 64 * sl, row_base + q0);
+      }
       int it = 0;
       for (int j = 0; j < n_kt; ++j) {
         if (!(tile_bits(j) & kTileAnyKept)) continue;
@@ -196,13 +203,16 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         mbar_arrive_expect_tx(&k_full[st], (DUAL ? 2 : 1) * C::TILE_V);
 #pragma unroll
         for (int sl = 0; sl < SLABS; ++sl) {
-          tma_load_3d(sK(st) + sl * C::SLAB, &tmK, &k_full[st], 0, krow, sl);
-          if constexpr (DUAL) tma_load_3d(sK(st) + sl * C::SLAB + C::HALF, &tmTK, &k_full[st], 0, krow, sl);
+          tma_load_2d(sK(st) + sl * C::SLAB, &tmK, &k_full[st], 64 * sl, krow);
+          if constexpr (DUAL) tma_load_2d(sK(st) + sl * C::SLAB + C::HALF, &tmTK, &k_full[st], 64 * sl, krow);
         }
         mbar_wait(&v_empty[st], ph ^ 1, w, 11);
         mbar_arrive_expect_tx(&v_full[st], (DUAL ? 2 : 1) * C::TILE_V);
-        tma_load_3d(sV(st), &tmV, &v_full[st], 0, krow, 0);
-        if constexpr (DUAL) tma_load_3d(sTV(st), &tmTV, &v_full[st], 0, krow, 0);
+#pragma unroll
+        for (int sl = 0; sl < SLABS; ++sl) {
+          tma_load_2d(sV(st) + sl * C::HALF, &tmV, &v_full[st], 64 * sl, krow);
+          if constexpr (DUAL) tma_load_2d(sTV(st) + sl * C::HALF, &tmTV, &v_full[st], 64 * sl, krow);
+        }
         ++it;
       }
     }
@@ -213,7 +223,9 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     constexpr uint32_t FMT = BF16 ? FMT_BF16 : FMT_F16;
     const uint32_t idesc_64 = make_idesc(FMT, 128, 64, 0, 0);
     const uint32_t idesc_128 = make_idesc(FMT, 128, 128, 0, 0);
-    const uint32_t idesc_pv = make_idesc(FMT, 128, D, 0, 1);
+    const int dn = PAD ? ((p.D + 15) & ~15) : D;           // head dimension rounded up to the MMA granularity
+    const int ksteps = dn / 16;                            // K steps of the score products that hold data
+    const uint32_t idesc_pv = make_idesc(FMT, 128, dn, 0, 1);
     const uint64_t dQ = desc_kmajor_sw128(smem_u32(sQ)), dTQ = desc_kmajor_sw128(smem_u32(sTQ));
 
     auto issue_qk = [&](int it) {
@@ -229,13 +241,13 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint64_t o = static_cast<uint64_t>(((k >> 2) * C::SLAB + (k & 3) * 32) >> 4);
-          umma_ss(S_t, dQ + o, dK + o, DUAL ? idesc_128 : idesc_64, k > 0);   // [S | Q tK^T]
+          if (!PAD || k < ksteps) umma_ss(S_t, dQ + o, dK + o, DUAL ? idesc_128 : idesc_64, k > 0);   // [S | Q tK^T]
         }
         if constexpr (DUAL) {
 #pragma unroll
           for (int k = 0; k < D / 16; ++k) {
             const uint64_t o = static_cast<uint64_t>(((k >> 2) * C::SLAB + (k & 3) * 32) >> 4);
-            umma_ss(S_t + 64, dTQ + o, dK + o, idesc_64, 1);                    // tS += tQ K^T
+            if (!PAD || k < ksteps) umma_ss(S_t + 64, dTQ + o, dK + o, idesc_64, 1);                    // tS += tQ K^T
           }
         }
         umma_commit(&s_full[it & 1]);
@@ -430,7 +442,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
     const float linv = (l > 0.f) ? 1.0f / l : 0.f;
     const float mul = mu * linv;
-    const size_t orow = (static_cast<size_t>(row_base) + qi) * D;
+    const size_t orow = (static_cast<size_t>(row_base) + qi) * p.D;
 #pragma unroll
     for (int c = wg * (D / 64); c < (wg + 1) * (D / 64); ++c) {
       uint32_t ov[32], tv[32];
@@ -456,11 +468,13 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (qi < N) {
         uint4* op = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.o) + orow + c * 32);
 #pragma unroll
-        for (int v4 = 0; v4 < 4; ++v4) op[v4] = make_uint4(po[4 * v4], po[4 * v4 + 1], po[4 * v4 + 2], po[4 * v4 + 3]);
+        for (int v4 = 0; v4 < 4; ++v4)
+          if (c * 32 + v4 * 8 < p.D) op[v4] = make_uint4(po[4 * v4], po[4 * v4 + 1], po[4 * v4 + 2], po[4 * v4 + 3]);
         if constexpr (DUAL) {
           uint4* tp = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.to) + orow + c * 32);
 #pragma unroll
-          for (int v4 = 0; v4 < 4; ++v4) tp[v4] = make_uint4(pt[4 * v4], pt[4 * v4 + 1], pt[4 * v4 + 2], pt[4 * v4 + 3]);
+          for (int v4 = 0; v4 < 4; ++v4)
+            if (c * 32 + v4 * 8 < p.D) tp[v4] = make_uint4(pt[4 * v4], pt[4 * v4 + 1], pt[4 * v4 + 2], pt[4 * v4 + 3]);
         }
       }
     }
@@ -474,22 +488,22 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   if (warp == 9) tmem_dealloc(tmem, C::TMEM_COLS);
 }
 
-template <int D, bool DUAL, bool BF16>
+template <int D, bool DUAL, bool BF16, bool PAD>
 int launch_one(const jvpfa_fwd_args& a, cudaStream_t stream) {
   using C = FwdCfg<D>;
   const uint64_t rows = static_cast<uint64_t>(a.B) * a.H * a.N;
   CUtensorMap mQ, mTQ, mK, mTK, mV, mTV;
-  bool ok = make_tile_map(&mQ, a.q, rows, D, C::BM, a.dtype) && make_tile_map(&mK, a.k, rows, D, C::BN, a.dtype, 1) &&
-            make_tile_map(&mV, a.v, rows, D, C::BN, a.dtype);
+  bool ok = make_tile_map(&mQ, a.q, rows, a.D, C::BM, a.dtype) && make_tile_map(&mK, a.k, rows, a.D, C::BN, a.dtype) &&
+            make_tile_map(&mV, a.v, rows, a.D, C::BN, a.dtype);
   if (DUAL) {
-    ok = ok && make_tile_map(&mTQ, a.tq, rows, D, C::BM, a.dtype) && make_tile_map(&mTK, a.tk, rows, D, C::BN, a.dtype, 1) &&
-         make_tile_map(&mTV, a.tv, rows, D, C::BN, a.dtype);
+    ok = ok && make_tile_map(&mTQ, a.tq, rows, a.D, C::BM, a.dtype) && make_tile_map(&mTK, a.tk, rows, a.D, C::BN, a.dtype) &&
+         make_tile_map(&mTV, a.tv, rows, a.D, C::BN, a.dtype);
   } else {
     mTQ = mQ; mTK = mK; mTV = mV;
   }
   if (!ok) return JVPFA_ERR_LAUNCH;
   FwdKParams p{};
-  p.H = a.H; p.N = a.N; p.causal = a.causal;
+  p.H = a.H; p.N = a.N; p.D = a.D; p.causal = a.causal;
   p.s = a.sm_scale;
   p.c1 = a.sm_scale * 1.4426950408889634f;
   p.thresh = BF16 ? 8.0f : 6.0f;
@@ -501,7 +515,7 @@ int launch_one(const jvpfa_fwd_args& a, cudaStream_t stream) {
   p.o = a.o; p.to = a.to; p.lse2 = a.lse2; p.mu = a.mu;
   p.status = static_cast<int*>(a.workspace);
   p.budget_ns = wait_budget_ns();
-  auto kern = fwd_sm100_kernel<D, DUAL, BF16>;
+  auto kern = fwd_sm100_kernel<D, DUAL, BF16, PAD>;
   const size_t smem = C::smem_bytes();
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
     return JVPFA_ERR_LAUNCH;
@@ -520,18 +534,23 @@ extern "C" int jvpfa_fwd_trace_read(long long* host_out) {
 #endif
 
 bool sm100_path_supported(int dtype, int D, int N) {
-  return (dtype == JVPFA_BF16 || dtype == JVPFA_F16) && (D == 64 || D == 128) && N >= 1;
+  // head dimensions other than 64 / 128 run on the next wider kernel with zero-filled columns
+  return (dtype == JVPFA_BF16 || dtype == JVPFA_F16) && D >= 8 && D <= 128 && (D % 8) == 0 && N >= 1;
 }
 
-int launch_fwd_sm100(const jvpfa_fwd_args& a, cudaStream_t stream) {
+namespace {
+template <int D, bool PAD>
+int launch_by_mode(const jvpfa_fwd_args& a, cudaStream_t stream) {
   const bool dual = a.tq != nullptr;
   const bool bf = a.dtype == JVPFA_BF16;
-  if (a.D == 64) {
-    if (dual) return bf ? launch_one<64, true, true>(a, stream) : launch_one<64, true, false>(a, stream);
-    return bf ? launch_one<64, false, true>(a, stream) : launch_one<64, false, false>(a, stream);
-  }
-  if (dual) return bf ? launch_one<128, true, true>(a, stream) : launch_one<128, true, false>(a, stream);
-  return bf ? launch_one<128, false, true>(a, stream) : launch_one<128, false, false>(a, stream);
+  if (dual) return bf ? launch_one<D, true, true, PAD>(a, stream) : launch_one<D, true, false, PAD>(a, stream);
+  return bf ? launch_one<D, false, true, PAD>(a, stream) : launch_one<D, false, false, PAD>(a, stream);
+}
+}  // namespace
+
+int launch_fwd_sm100(const jvpfa_fwd_args& a, cudaStream_t stream) {
+  if (sm100_padded_dim(a.D) == 64) return a.D == 64 ? launch_by_mode<64, false>(a, stream) : launch_by_mode<64, true>(a, stream);
+  return a.D == 128 ? launch_by_mode<128, false>(a, stream) : launch_by_mode<128, true>(a, stream);
 }
 
 }  // namespace jvpfa

@@ -15,12 +15,12 @@ typedef CUresult (*TensorMapEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint3
 
 TensorMapEncodeFn tensor_map_encoder();
 
-// A (rows x D) matrix of 16-bit elements, D a multiple of 64, viewed as (64, rows, D/64) so that
-// one TMA copy of box (64, box_rows, D/64) lands in shared memory as D/64 slabs of
-// [box_rows][64 elements], each slab in the 128-byte-swizzled layout the MMA descriptors expect.
+// A (rows x D) row-major matrix of 16-bit elements, D a multiple of 8, as a 2-D tensor map with a box of
+// (64 columns, box_rows rows): one TMA copy per 64-column slab lands in shared memory as [box_rows][64
+// elements] in the 128-byte-swizzled layout the MMA descriptors expect; columns at or beyond D read as
+// zero, which is how head dimensions that are not 64 or 128 ride on the 64- and 128-wide kernels.
 // Returns false if the driver rejects the encoding.
-// `box_slabs` = 0 copies all D/64 slabs with one box; 1 copies a single slab (the slab index is coordinate 2).
-bool make_tile_map(CUtensorMap* out, const void* base, uint64_t rows, int D, int box_rows, int dtype, int box_slabs = 0);
+bool make_tile_map(CUtensorMap* out, const void* base, uint64_t rows, int D, int box_rows, int dtype);
 
 // Wait budget of a single device-side mbarrier wait, in nanoseconds (JVPFA_WAIT_BUDGET_MS, default 4000 ms).
 uint64_t wait_budget_ns();
@@ -45,6 +45,7 @@ int launch_fwd_sm100(const jvpfa_fwd_args& a, cudaStream_t stream);
 int launch_bwd_sm100(const jvpfa_bwd_args& a, cudaStream_t stream);
 size_t bwd_sm100_workspace_bytes(const jvpfa_bwd_args& a);
 bool sm100_path_supported(int dtype, int D, int N);
+inline int sm100_padded_dim(int D) { return D <= 64 ? 64 : 128; }
 
 int launch_fwd_generic(const jvpfa_fwd_args& a, cudaStream_t stream);
 int launch_bwd_generic(const jvpfa_bwd_args& a, cudaStream_t stream);
