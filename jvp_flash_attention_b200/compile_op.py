@@ -1,0 +1,68 @@
+"""Opaque ``torch.library`` operators so that ``torch.compile`` can carry the attention call through a graph.
+
+Counterpart of the reference's ``jvp_flash_attention::attn_fwd_dual_triton`` custom op and its fake
+(jvp_flash_attention/jvp_attention.py:2247-2427), extended with a registered backward: the reference's compiled
+path has no autograd (its op is called under ``no_grad``, :2677-2692), here gradients flow through both outputs.
+``JVPAttn.dual`` switches to these operators while a graph is being compiled; eager calls keep using the
+``autograd.Function`` in ``jvp_attention.py``.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+from torch import Tensor
+
+from . import _lib
+
+
+@torch.library.custom_op("jvp_flash_attention_b200::attn_fwd_dual", mutates_args=())
+def attn_fwd_dual(q: Tensor, k: Tensor, v: Tensor, q_t: Tensor, k_t: Tensor, v_t: Tensor, mask: Optional[Tensor],
+                  sm_scale: float, causal: bool) -> Tuple[Tensor, Tensor, Tensor, Tensor]:
+    B, H, N, D = q.shape
+    q, k, v, q_t, k_t, v_t = (t.contiguous() for t in (q, k, v, q_t, k_t, v_t))
+    mask_c = _lib.make_mask(mask, B, H, N)
+    summary = _lib.mask_summary(mask_c, mask, B, H, N) if mask is not None else None
+    o, o_t, lse2, mu = _lib.fwd(q, k, v, q_t, k_t, v_t, mask_c, summary, causal, sm_scale)
+    return o, o_t, lse2, mu
+
+
+@attn_fwd_dual.register_fake
+def _(q, k, v, q_t, k_t, v_t, mask, sm_scale, causal):
+    B, H, N, D = q.shape
+    stats = q.new_empty((B, H, N), dtype=torch.float32)
+    return torch.empty_like(q), torch.empty_like(q), stats, torch.empty_like(stats)
+
+
+@torch.library.custom_op("jvp_flash_attention_b200::attn_bwd_dual", mutates_args=())
+def attn_bwd_dual(q: Tensor, k: Tensor, v: Tensor, q_t: Tensor, k_t: Tensor, v_t: Tensor, o: Tensor, o_t: Tensor,
+                  lse2: Tensor, mu: Tensor, go: Tensor, go_t: Tensor, mask: Optional[Tensor], sm_scale: float,
+                  causal: bool) -> Tuple[Tensor, Tensor, Tensor, Tensor, Tensor, Tensor]:
+    B, H, N, D = q.shape
+    mask_c = _lib.make_mask(mask, B, H, N)
+    summary = _lib.mask_summary(mask_c, mask, B, H, N) if mask is not None else None
+    return _lib.bwd(q.contiguous(), k.contiguous(), v.contiguous(), q_t.contiguous(), k_t.contiguous(), v_t.contiguous(),
+                    o, o_t, lse2, mu, go.contiguous(), go_t.contiguous(), mask_c, summary, causal, sm_scale)
+
+
+@attn_bwd_dual.register_fake
+def _(q, k, v, q_t, k_t, v_t, o, o_t, lse2, mu, go, go_t, mask, sm_scale, causal):
+    return tuple(torch.empty_like(q) for _ in range(6))
+
+
+def _setup_context(ctx, inputs, output):
+    q, k, v, q_t, k_t, v_t, mask, sm_scale, causal = inputs
+    o, o_t, lse2, mu = output
+    ctx.save_for_backward(q, k, v, q_t, k_t, v_t, o, o_t, lse2, mu)
+    ctx.mask, ctx.sm_scale, ctx.causal = mask, sm_scale, causal
+
+
+def _backward(ctx, go, go_t, _g_lse, _g_mu):
+    q, k, v, q_t, k_t, v_t, o, o_t, lse2, mu = ctx.saved_tensors
+    go = torch.zeros_like(o) if go is None else go
+    go_t = torch.zeros_like(o) if go_t is None else go_t
+    grads = attn_bwd_dual(q, k, v, q_t, k_t, v_t, o, o_t, lse2, mu, go, go_t, ctx.mask, ctx.sm_scale, ctx.causal)
+    return (*grads, None, None, None)
+
+
+attn_fwd_dual.register_autograd(_backward, setup_context=_setup_context)

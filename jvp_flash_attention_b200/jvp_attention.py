@@ -188,6 +188,14 @@ class JVPAttn:
         """Explicit-tangent form: returns ``(o, to)`` as ordinary tensors, both connected to autograd
         (gradients reach q, k, v and the three tangents). No reference counterpart; this is what
         ``fwd_dual`` calls once it has unpacked the dual tensors."""
+        if torch.compiler.is_compiling():
+            # inside torch.compile: the opaque operator pair of compile_op.py (no data-dependent checks in a graph)
+            from .compile_op import attn_fwd_dual
+            if sm_scale is None:
+                sm_scale = q.shape[-1] ** -0.5
+            o, to, _, _ = attn_fwd_dual(q, k, v, q_t, k_t, v_t, _mask_for_kernel(attn_mask, q), float(sm_scale),
+                                        bool(causal))
+            return o, to
         _validate(q, k, v, attn_mask, 0.0, causal, verify_attn_mask)
         q, k, v, q_t, k_t, v_t = (t.contiguous() for t in (q, k, v, q_t, k_t, v_t))
         if sm_scale is None:

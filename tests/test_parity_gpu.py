@@ -276,3 +276,25 @@ def test_backward_determinism_and_zero_upstream(dev):
     assert all(torch.equal(a, b) for a, b in zip(g1, g2))
     g0 = torch.autograd.grad((O * 0).sum() + (tO * 0).sum(), leaves)
     assert all(float(x.abs().max()) == 0.0 for x in g0)
+
+
+def test_torch_compile_operator(dev):
+    """``JVPAttn.dual`` inside ``torch.compile``: same outputs and gradients as the eager call (bit-equal: same kernels)."""
+    JVPAttn, _ = _api()
+    ts = [t.to(dev) for t in make_inputs(2, 2, 256, 64, dtype=torch.bfloat16, seed=4, scale=0.5)]
+
+    def fn(q, k, v, tq, tk, tv, go, gto):
+        o, to = JVPAttn.dual(q, k, v, tq, tk, tv, causal=True)
+        return (o * go).sum() + (to * gto).sum(), o, to
+
+    def run(f):
+        leaves = [t.clone().requires_grad_(True) for t in ts[:6]]
+        loss, o, to = f(*leaves, ts[6], ts[7])
+        return o.detach(), to.detach(), torch.autograd.grad(loss, leaves)
+
+    o1, t1, g1 = run(fn)
+    o2, t2, g2 = run(torch.compile(fn, fullgraph=True))
+    assert torch.equal(o1, o2) and torch.equal(t1, t2)
+    assert all(torch.equal(a, b) for a, b in zip(g1, g2))
+    torch.library.opcheck(torch.ops.jvp_flash_attention_b200.attn_fwd_dual.default,
+                          (*ts[:6], None, 0.125, True), test_utils=("test_schema", "test_faketensor"))
