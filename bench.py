@@ -225,7 +225,10 @@ def run_cuda(args, rank, world, local_rank):
     ach = (bwd_f / 3.0) / ((bwd_ms / max(bwd_launches, 1)) * 1e-3) / 1e12 if bwd_launches else None
     roofline = {"bound": "tensor", "kernel": "bwd_sm100_kernel (families Q, K, V)", "achieved": ach, "peak": peak_sustained,
                 "unit": "TFLOP/s", "frac": (ach / peak_sustained if ach else None), "peak_kind": f"{peak_kind} sustained bf16 cuBLAS",
-                "traffic": None,
+                # DRAM bytes per backward-family launch: ncu capture of the B=2 case (profiles/bwd_fwd_sm100_full_set_small.md:
+                # 321.9 / 320.9 / 251.3 MB read+write for families Q / K / V), scaled by B/2 -- traffic grows with the
+                # number of (batch, head) units, every unit's tensors are read from HBM once per launch
+                "traffic": (321.9e6 + 320.9e6 + 251.3e6) / 3.0 * (B / 2.0), "traffic_unit": "bytes per launch",
                 "fwd_kernel": {"achieved": fwd_f / (kt["fwd"][0] / max(kt["fwd"][1], 1) * 1e-3) / 1e12 if kt["fwd"][1] else None}}
     if roofline["fwd_kernel"]["achieved"]:
         roofline["fwd_kernel"]["frac"] = roofline["fwd_kernel"]["achieved"] / peak_sustained

@@ -2,16 +2,18 @@
 // pass, with tcgen05 MMAs accumulating in TMEM and K/tK/V/tV tiles staged by TMA.
 //
 // Replaces the reference's _attn_fwd_tma / _attn_fwd_inner_tma (jvp_flash_attention/jvp_attention.py:
-// 1100-1392, 350-559). Per (128-row query tile, batch*head) one CTA of 6 warps:
-//   warps 0-3  softmax: thread r owns score row r (TMEM lane r); keeps m, l, mu in registers, turns the
-//              score tile S and tangent-score tile tS into 16-bit P and W = P o (s tS) written back to TMEM
-//   warp 4     TMA producer (one lane)
-//   warp 5     MMA issuer (one lane); owns the TMEM allocation
-// Per 64-column key tile: S = Q K^T, tS = tQ K^T + Q tK^T (operands in shared memory), then
-// O += P V, T += W V + P tV (P, W read from TMEM; V, tV as MN-major shared-memory operands).
-// Epilogue: O/l, tO = T/l - (mu/l) O/l, lse2 = m + log2 l, mu/l.
-// TMEM columns: O [0,D), T [D,2D), then two score buffers of (S 64 | tS 64) columns; P and W
-// overwrite the first 32 columns of S and tS of their buffer.
+// 1100-1392, 350-559). Per (128-row query tile, batch*head) one CTA of 10 warps:
+//   warps 0-7  two softmax warpgroups that split the 64 columns of every score tile: thread r of a
+//              warpgroup owns score row r (TMEM lane r) and 32 columns; keeps m, l, mu in registers, turns the
+//              score tile S and tangent-score tile tS into 16-bit P and W = P o (s tS) written back to TMEM;
+//              the two halves of a row exchange their maxima (and, at the end, their sums) through shared memory
+//   warp 8     TMA producer (one lane)
+//   warp 9     MMA issuer (lane 0 issues); owns the TMEM allocation
+// Per 64-column key tile: [S | Q tK^T] = Q [K; tK]^T as one N = 128 product against the stacked pair, then
+// tS += tQ K^T (operands in shared memory), then O += P V, T += W V + P tV (P, W read from TMEM; V, tV as
+// MN-major shared-memory operands). Epilogue: O/l, tO = T/l - (mu/l) O/l, lse2 = m + log2 l, mu/l.
+// TMEM columns: O [0,D), T [D,2D), then two score buffers of (S 64 | tS 64) columns; P and W overwrite
+// 16 of the 32 columns of S and tS that their thread has already read.
 #include <type_traits>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
