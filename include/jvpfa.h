@@ -67,7 +67,9 @@ typedef struct jvpfa_fwd_args {
  * _attn_bwd_preprocess + _attn_bwd / _attn_bwd_causal in JVPAttn.backward
  * (jvp_attention.py:3171, 3189), and adds what the reference leaves out: the gradient through
  * the tangent output and the tangent-input gradients (jvp_attention.py:3081, 3226).
- * All pointers are required; pass a zero tensor as gto when only the primal output has a gradient. */
+ * Pass a zero tensor as gto when only the primal output has a gradient. tq == NULL selects the primal-only
+ * backward (the reference's own case, jvp_attention.py:3080-3226): tk, tv, to, gto, dtq, dtk, dtv are then ignored
+ * and only dq, dk, dv are written. */
 typedef struct jvpfa_bwd_args {
   int32_t B, H, N, D;
   int32_t dtype;

@@ -217,19 +217,25 @@ def fwd(q, k, v, tq, tk, tv, mask_c: Mask, summary, causal: bool, sm_scale: floa
 
 
 def bwd(q, k, v, tq, tk, tv, o, to, lse2, mu, go, gto, mask_c: Mask, summary, causal: bool, sm_scale: float):
-    """Launches the dual backward; returns (dq, dk, dv, dtq, dtk, dtv)."""
+    """Launches the backward. Dual form: returns (dq, dk, dv, dtq, dtk, dtv). With tq None (primal-only: tk, tv,
+    to, gto are ignored) returns (dq, dk, dv)."""
     B, H, N, D = q.shape
-    outs = [torch.empty_like(q) for _ in range(6)]
+    dual = tq is not None
+    outs = [torch.empty_like(q) for _ in range(6 if dual else 3)]
     a = BwdArgs()
     a.B, a.H, a.N, a.D = B, H, N, D
     a.dtype, a.causal, a.sm_scale = dtype_code(q.dtype), int(bool(causal)), float(sm_scale)
     a.mask = mask_c
     a.mask_summary = None if summary is None else summary.data_ptr()
-    a.q, a.k, a.v, a.tq, a.tk, a.tv = (t.data_ptr() for t in (q, k, v, tq, tk, tv))
-    a.o, a.to, a.lse2, a.mu = o.data_ptr(), to.data_ptr(), lse2.data_ptr(), mu.data_ptr()
+    a.q, a.k, a.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
+    a.o, a.lse2, a.mu = o.data_ptr(), lse2.data_ptr(), mu.data_ptr()
     a.go = go.data_ptr()
-    a.gto = None if gto is None else gto.data_ptr()
-    a.dq, a.dk, a.dv, a.dtq, a.dtk, a.dtv = (t.data_ptr() for t in outs)
+    a.dq, a.dk, a.dv = (t.data_ptr() for t in outs[:3])
+    if dual:
+        a.tq, a.tk, a.tv, a.to, a.gto = (t.data_ptr() for t in (tq, tk, tv, to, gto))
+        a.dtq, a.dtk, a.dtv = (t.data_ptr() for t in outs[3:])
+    else:
+        a.tq = a.tk = a.tv = a.to = a.gto = a.dtq = a.dtk = a.dtv = None
     need = lib().jvpfa_bwd_workspace_bytes(C.byref(a))
     ws = workspace(q.device, need)
     a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()

@@ -114,7 +114,9 @@ struct BwdCfg {
 // family V double-buffers S, tS.
 // PAD: the tensors' head dimension is smaller than D (columns beyond it are zero-filled by TMA); the K steps and
 // output columns that would only see zeros are then skipped at run time.
-template <int D, int FAM, bool BF16, bool PAD>
+// DUAL = false: primal-only backward (no tangents, no gradient through a tangent output): S and X = gO V^T only,
+// dS = P (X - Delta); dQ = s dS K, dK = s dS^T Q, dV = P^T gO. Tangent tiles are neither loaded nor multiplied.
+template <int D, int FAM, bool BF16, bool PAD, bool DUAL>
 __global__ void __launch_bounds__(320, 1)
 bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant__ CUtensorMap rm1,
                  const __grid_constant__ CUtensorMap rm2, const __grid_constant__ CUtensorMap rm3,
@@ -222,14 +224,14 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
   if (warp == 8) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      mbar_arrive_expect_tx(&r_full, C::NR * C::TILE_R);
+      mbar_arrive_expect_tx(&r_full, (DUAL ? C::NR : C::NR / 2) * C::TILE_R);
 #pragma unroll
       for (int sl = 0; sl < SLABS; ++sl) {
         tma_load_2d(sR(0) + sl * C::SLAB, &rm0, &r_full, 64 * sl, row_base + r0);
-        tma_load_2d(sR(1) + sl * C::SLAB, &rm1, &r_full, 64 * sl, row_base + r0);
+        if constexpr (DUAL) tma_load_2d(sR(1) + sl * C::SLAB, &rm1, &r_full, 64 * sl, row_base + r0);
         if constexpr (C::NR == 4) {
           tma_load_2d(sR(2) + sl * C::SLAB, &rm2, &r_full, 64 * sl, row_base + r0);
-          tma_load_2d(sR(3) + sl * C::SLAB, &rm3, &r_full, 64 * sl, row_base + r0);
+          if constexpr (DUAL) tma_load_2d(sR(3) + sl * C::SLAB, &rm3, &r_full, 64 * sl, row_base + r0);
         }
       }
       int it = 0;
@@ -238,21 +240,21 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
         {
           const int buf = it % NA;
           mbar_wait(&a_empty[buf], ((it / NA) & 1) ^ 1, w, 10);
-          mbar_arrive_expect_tx(&a_full[buf], C::PAIR);
+          mbar_arrive_expect_tx(&a_full[buf], DUAL ? C::PAIR : C::PAIR / 2);
 #pragma unroll
           for (int sl = 0; sl < SLABS; ++sl) {
             tma_load_2d(sA(buf) + sl * C::SLAB, &cm0, &a_full[buf], 64 * sl, crow);
-            tma_load_2d(sA(buf) + sl * C::SLAB + C::HALF, &cm1, &a_full[buf], 64 * sl, crow);
+            if constexpr (DUAL) tma_load_2d(sA(buf) + sl * C::SLAB + C::HALF, &cm1, &a_full[buf], 64 * sl, crow);
           }
         }
         {
           const int buf = it % NB;
           mbar_wait(&b_empty[buf], ((it / NB) & 1) ^ 1, w, 11);
-          mbar_arrive_expect_tx(&b_full[buf], C::PAIR);
+          mbar_arrive_expect_tx(&b_full[buf], DUAL ? C::PAIR : C::PAIR / 2);
 #pragma unroll
           for (int sl = 0; sl < SLABS; ++sl) {
             tma_load_2d(sB(buf) + sl * C::SLAB, &cm2, &b_full[buf], 64 * sl, crow);
-            tma_load_2d(sB(buf) + sl * C::SLAB + C::HALF, &cm3, &b_full[buf], 64 * sl, crow);
+            if constexpr (DUAL) tma_load_2d(sB(buf) + sl * C::SLAB + C::HALF, &cm3, &b_full[buf], 64 * sl, crow);
           }
         }
       }
@@ -303,8 +305,12 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
         wait_all(&a_full[buf], (i / NA) & 1, 20);
         tc_fence_after_sync();
         const uint32_t T0 = TS0 + sb * 128;
-        mma_nt(T0, sR(0), sA(buf), idesc_128, 0);        // [S | R0 c1^T]
-        mma_nt(T0 + 64, sR(1), sA(buf), idesc_64, 1);    // tS += R1 c0^T
+        if constexpr (DUAL) {
+          mma_nt(T0, sR(0), sA(buf), idesc_128, 0);        // [S | R0 c1^T]
+          mma_nt(T0 + 64, sR(1), sA(buf), idesc_64, 1);    // tS += R1 c0^T
+        } else {
+          mma_nt(T0, sR(0), sA(buf), idesc_64, 0);         // S
+        }
         if (leader) umma_commit(&st_full[sb]);
         if constexpr (FAM == FAM_V) if (leader) umma_commit(&a_empty[buf]);
       };
@@ -314,7 +320,9 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
         wait_all(&b_full[buf], (i / NB) & 1, 21);
         tc_fence_after_sync();
         const uint32_t T2 = TS0 + 128;
-        if constexpr (FAM == FAM_Q) {
+        if constexpr (!DUAL) {
+          mma_nt(FAM == FAM_Q ? T2 + 64 : T2, sR(2), sB(buf), idesc_64, 0);   // X = gO V^T (family K: its transpose)
+        } else if constexpr (FAM == FAM_Q) {
           mma_nt(T2, sR(3), sB(buf), idesc_128, 0);               // [A | gtO tV^T]
           mma_nt(T2 + 64, sR(2), sB(buf), idesc_64, 1);           // X += gO V^T
         } else {
@@ -346,8 +354,10 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
           JVPFA_TR(0, it, 2);
           const uint32_t E0 = TS0 + (it & 1) * 128, E1 = E0 + 64;
           mma_out(tmem + C::TMEM_ACC0, E0, sB(buf), it > 0);               // dV  += P^T gO + tP^T gtO
-          mma_out(tmem + C::TMEM_ACC0, E1, sB(buf) + C::HALF, 1);
-          mma_out(tmem + C::TMEM_ACC1, E0, sB(buf) + C::HALF, it > 0);     // dtV += P^T gtO
+          if constexpr (DUAL) {
+            mma_out(tmem + C::TMEM_ACC0, E1, sB(buf) + C::HALF, 1);
+            mma_out(tmem + C::TMEM_ACC1, E0, sB(buf) + C::HALF, it > 0);   // dtV += P^T gtO
+          }
           if (leader) umma_commit(&b_empty[buf]);
           JVPFA_TR(0, it, 3);
         } else {
@@ -364,8 +374,10 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
           // pair product leaves X first and A second, the element-wise code writes them the same way
           const uint32_t E0 = TS0 + 128, E1 = TS0 + 192;
           mma_out(tmem + C::TMEM_ACC0, E0, sA(buf), it > 0);               // dS c0 + dtS c1
-          mma_out(tmem + C::TMEM_ACC0, E1, sA(buf) + C::HALF, 1);
-          mma_out(tmem + C::TMEM_ACC1, E1, sA(buf), it > 0);               // dtS c0
+          if constexpr (DUAL) {
+            mma_out(tmem + C::TMEM_ACC0, E1, sA(buf) + C::HALF, 1);
+            mma_out(tmem + C::TMEM_ACC1, E1, sA(buf), it > 0);             // dtS c0
+          }
           if (leader) umma_commit(&a_empty[buf]);
           JVPFA_TR(0, it, 3);
           if (has_next) issue_xa(it + 1);
@@ -433,7 +445,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
       {
         uint32_t a0[32], a1[32];
         tmem_ld_x32(T0, a0);
-        tmem_ld_x32(T1, a1);
+        if constexpr (DUAL) tmem_ld_x32(T1, a1);
         tmem_wait_ld();
         if constexpr (FAM != FAM_V) {
           tc_fence_before_sync();
@@ -447,7 +459,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
           x2[i] = __ffma2_rn(make_float2(__uint_as_float(a0[2 * i]), __uint_as_float(a0[2 * i + 1])), c1_2, stat2(0, i));
-          ts2[i] = __fmul2_rn(make_float2(__uint_as_float(a1[2 * i]), __uint_as_float(a1[2 * i + 1])), s_2);
+          if constexpr (DUAL) ts2[i] = __fmul2_rn(make_float2(__uint_as_float(a1[2 * i]), __uint_as_float(a1[2 * i + 1])), s_2);
         }
         if (need_causal || need_bound || need_mask) {
 #pragma unroll
@@ -489,12 +501,14 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             const int ip = 8 * hch + i;
-            const float2 tp = __fmul2_rn(P2[ip], __fadd2_rn(ts2[ip], stat2(1, ip)));
             e0[i] = pack2<BF16>(P2[ip].x, P2[ip].y);
-            e1[i] = pack2<BF16>(tp.x, tp.y);
+            if constexpr (DUAL) {
+              const float2 tp = __fmul2_rn(P2[ip], __fadd2_rn(ts2[ip], stat2(1, ip)));
+              e1[i] = pack2<BF16>(tp.x, tp.y);
+            }
           }
           tmem_st_x8(T0 + 8 * hch, e0);
-          tmem_st_x8(T1 + 8 * hch, e1);
+          if constexpr (DUAL) tmem_st_x8(T1 + 8 * hch, e1);
         }
       } else {
         // ---- phase 2: X, A -> dS = P (X - Delta + ts (A - a) - mu A), dtS = P (A - a)
@@ -505,26 +519,33 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
 #pragma unroll
         for (int hch = 0; hch < 2; ++hch) {
           uint32_t x2r[16], x3r[16];
-          tmem_ld_x16(T2 + 16 * hch, x2r);
-          tmem_ld_x16(T3 + 16 * hch, x3r);
+          if (DUAL || FAM != FAM_Q) tmem_ld_x16(T2 + 16 * hch, x2r);
+          if (DUAL || FAM == FAM_Q) tmem_ld_x16(T3 + 16 * hch, x3r);
           tmem_wait_ld();
           uint32_t e0[8], e1[8];
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             const int ip = 8 * hch + i;
-            const float2 t2v = make_float2(__uint_as_float(x2r[2 * i]), __uint_as_float(x2r[2 * i + 1]));
-            const float2 t3v = make_float2(__uint_as_float(x3r[2 * i]), __uint_as_float(x3r[2 * i + 1]));
-            const float2 A = (FAM == FAM_Q) ? t2v : t3v;
-            const float2 X = (FAM == FAM_Q) ? t3v : t2v;
-            const float2 d = __fadd2_rn(A, stat2(3, ip));                       // A - a
-            float2 t = __ffma2_rn(ts2[ip], d, __fadd2_rn(X, stat2(2, ip)));     // X - Delta + ts (A - a)
-            t = __ffma2_rn(stat2(1, ip), A, t);                                 // - mu A
-            const float2 ds = __fmul2_rn(P2[ip], t), dts = __fmul2_rn(P2[ip], d);
-            e0[i] = pack2<BF16>(ds.x, ds.y);
-            e1[i] = pack2<BF16>(dts.x, dts.y);
+            if constexpr (DUAL) {
+              const float2 t2v = make_float2(__uint_as_float(x2r[2 * i]), __uint_as_float(x2r[2 * i + 1]));
+              const float2 t3v = make_float2(__uint_as_float(x3r[2 * i]), __uint_as_float(x3r[2 * i + 1]));
+              const float2 A = (FAM == FAM_Q) ? t2v : t3v;
+              const float2 X = (FAM == FAM_Q) ? t3v : t2v;
+              const float2 d = __fadd2_rn(A, stat2(3, ip));                       // A - a
+              float2 t = __ffma2_rn(ts2[ip], d, __fadd2_rn(X, stat2(2, ip)));     // X - Delta + ts (A - a)
+              t = __ffma2_rn(stat2(1, ip), A, t);                                 // - mu A
+              const float2 ds = __fmul2_rn(P2[ip], t), dts = __fmul2_rn(P2[ip], d);
+              e0[i] = pack2<BF16>(ds.x, ds.y);
+              e1[i] = pack2<BF16>(dts.x, dts.y);
+            } else {
+              const float2 X = (FAM == FAM_Q) ? make_float2(__uint_as_float(x3r[2 * i]), __uint_as_float(x3r[2 * i + 1]))
+                                              : make_float2(__uint_as_float(x2r[2 * i]), __uint_as_float(x2r[2 * i + 1]));
+              const float2 ds = __fmul2_rn(P2[ip], __fadd2_rn(X, stat2(2, ip)));  // P (X - Delta)
+              e0[i] = pack2<BF16>(ds.x, ds.y);
+            }
           }
           tmem_st_x8(T2 + 8 * hch, e0);
-          tmem_st_x8(T3 + 8 * hch, e1);
+          if constexpr (DUAL) tmem_st_x8(T3 + 8 * hch, e1);
         }
       }
       if (tr) JVPFA_TR(1 + wg, it, 5);
@@ -542,7 +563,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
       uint32_t a0[32], a1[32];
       if (it > 0) {
         tmem_ld_x32(tmem + lane_off + C::TMEM_ACC0 + c * 32, a0);
-        tmem_ld_x32(tmem + lane_off + C::TMEM_ACC1 + c * 32, a1);
+        if constexpr (DUAL) tmem_ld_x32(tmem + lane_off + C::TMEM_ACC1 + c * 32, a1);
         tmem_wait_ld();
       } else {
 #pragma unroll
@@ -553,7 +574,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
           q0[i] = pack2<BF16>(__uint_as_float(a0[2 * i]) * p.out_scale, __uint_as_float(a0[2 * i + 1]) * p.out_scale);
-          q1[i] = pack2<BF16>(__uint_as_float(a1[2 * i]) * p.out_scale, __uint_as_float(a1[2 * i + 1]) * p.out_scale);
+          if constexpr (DUAL)
+            q1[i] = pack2<BF16>(__uint_as_float(a1[2 * i]) * p.out_scale, __uint_as_float(a1[2 * i + 1]) * p.out_scale);
         }
         uint4* o0 = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.out0) + orow + c * 32);
         uint4* o1 = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.out1) + orow + c * 32);
@@ -561,7 +583,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
         for (int v4 = 0; v4 < 4; ++v4) {
           if (c * 32 + v4 * 8 < p.D) {
             o0[v4] = make_uint4(q0[4 * v4], q0[4 * v4 + 1], q0[4 * v4 + 2], q0[4 * v4 + 3]);
-            o1[v4] = make_uint4(q1[4 * v4], q1[4 * v4 + 1], q1[4 * v4 + 2], q1[4 * v4 + 3]);
+            if constexpr (DUAL) o1[v4] = make_uint4(q1[4 * v4], q1[4 * v4 + 1], q1[4 * v4 + 2], q1[4 * v4 + 3]);
           }
         }
       }
@@ -591,7 +613,7 @@ __global__ void bwd_preprocess_kernel(const uint16_t* __restrict__ o, const uint
   for (int d = lane * 2; d < D; d += 64) {
     const size_t idx = static_cast<size_t>(row) * D + d;
     const uint32_t ov = *reinterpret_cast<const uint32_t*>(o + idx);
-    const uint32_t tov = *reinterpret_cast<const uint32_t*>(to + idx);
+    const uint32_t tov = gto ? *reinterpret_cast<const uint32_t*>(to + idx) : 0u;
     const uint32_t gov = *reinterpret_cast<const uint32_t*>(go + idx);
     const uint32_t gtov = gto ? *reinterpret_cast<const uint32_t*>(gto + idx) : 0u;
 #pragma unroll
@@ -615,7 +637,7 @@ __global__ void bwd_preprocess_kernel(const uint16_t* __restrict__ o, const uint
   }
 }
 
-template <int D, int FAM, bool BF16, bool PAD>
+template <int D, int FAM, bool BF16, bool PAD, bool DUAL>
 int launch_family(const jvpfa_bwd_args& a, const float4* stats, cudaStream_t stream) {
   using C = BwdCfg<D, FAM>;
   const uint64_t rows = static_cast<uint64_t>(a.B) * a.H * a.N;
@@ -636,6 +658,10 @@ int launch_family(const jvpfa_bwd_args& a, const float4* stats, cudaStream_t str
     csrc[0] = a.q; csrc[1] = a.tq; csrc[2] = a.go; csrc[3] = a.gto;
     out0 = a.dv; out1 = a.dtv; out_scale = 1.0f;
   }
+  if (!DUAL) {  // tensors that do not exist in the primal-only call: alias the maps to existing ones, they are never used
+    rsrc[1] = rsrc[0]; rsrc[3] = rsrc[2];
+    csrc[1] = csrc[0]; csrc[3] = csrc[2];
+  }
   CUtensorMap rm[4], cm[4];
   for (int i = 0; i < 4; ++i) {
     if (!make_tile_map(&rm[i], rsrc[i], rows, a.D, C::BR, a.dtype)) return JVPFA_ERR_LAUNCH;
@@ -655,7 +681,7 @@ int launch_family(const jvpfa_bwd_args& a, const float4* stats, cudaStream_t str
   p.out0 = out0; p.out1 = out1;
   p.status = static_cast<int*>(a.workspace);
   p.budget_ns = wait_budget_ns();
-  auto kern = bwd_sm100_kernel<D, FAM, BF16, PAD>;
+  auto kern = bwd_sm100_kernel<D, FAM, BF16, PAD, DUAL>;
   const size_t smem = C::smem_bytes();
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
     return JVPFA_ERR_LAUNCH;
@@ -678,18 +704,17 @@ int launch_all(const jvpfa_bwd_args& a, cudaStream_t stream) {
       static_cast<const uint16_t*>(a.gto), a.lse2, a.mu, stats, rows, a.D);
   }
   if (cudaGetLastError() != cudaSuccess) return JVPFA_ERR_LAUNCH;
-  if (a.D == D) {
-    int rc = launch_family<D, FAM_Q, BF16, false>(a, stats, stream);
+  auto three = [&](auto pad, auto dual) {
+    constexpr bool P = decltype(pad)::value, DU = decltype(dual)::value;
+    int rc = launch_family<D, FAM_Q, BF16, P, DU>(a, stats, stream);
     if (rc != JVPFA_OK) return rc;
-    rc = launch_family<D, FAM_K, BF16, false>(a, stats, stream);
+    rc = launch_family<D, FAM_K, BF16, P, DU>(a, stats, stream);
     if (rc != JVPFA_OK) return rc;
-    return launch_family<D, FAM_V, BF16, false>(a, stats, stream);
-  }
-  int rc = launch_family<D, FAM_Q, BF16, true>(a, stats, stream);
-  if (rc != JVPFA_OK) return rc;
-  rc = launch_family<D, FAM_K, BF16, true>(a, stats, stream);
-  if (rc != JVPFA_OK) return rc;
-  return launch_family<D, FAM_V, BF16, true>(a, stats, stream);
+    return launch_family<D, FAM_V, BF16, P, DU>(a, stats, stream);
+  };
+  const bool dual = a.tq != nullptr;
+  if (a.D == D) return dual ? three(std::false_type{}, std::true_type{}) : three(std::false_type{}, std::false_type{});
+  return dual ? three(std::true_type{}, std::true_type{}) : three(std::true_type{}, std::false_type{});
 }
 
 }  // namespace
@@ -705,7 +730,6 @@ size_t bwd_sm100_workspace_bytes(const jvpfa_bwd_args& a) {
 }
 
 int launch_bwd_sm100(const jvpfa_bwd_args& a, cudaStream_t stream) {
-  if (a.gto == nullptr) return JVPFA_ERR_BAD_ARG;  // the tensor-core path wants an explicit (possibly zero) gtO
   const bool bf = a.dtype == JVPFA_BF16;
   if (sm100_padded_dim(a.D) == 64) return bf ? launch_all<64, true>(a, stream) : launch_all<64, false>(a, stream);
   return bf ? launch_all<128, true>(a, stream) : launch_all<128, false>(a, stream);

@@ -49,6 +49,7 @@ struct GenParams {
   MaskView mv;
   const float4* stats;
   float out_scale;
+  int dual;   // 0: primal-only backward, tangent tensors are absent
 };
 
 // score block of this thread: rows ty + 16 i, cols tx + 16 j (i, j < 2); acc[i][j] += sum_d A[d][row] B[d][col]
@@ -228,7 +229,7 @@ __global__ void generic_preprocess_kernel(const T* __restrict__ o, const T* __re
   float s1 = 0.f, s2 = 0.f, s3 = 0.f;
   for (int d = lane; d < D; d += 32) {
     const size_t idx = static_cast<size_t>(row) * D + d;
-    const float fo = to_f<T>(o[idx]), fto = to_f<T>(to[idx]), fgo = to_f<T>(go[idx]);
+    const float fo = to_f<T>(o[idx]), fto = gto ? to_f<T>(to[idx]) : 0.f, fgo = to_f<T>(go[idx]);
     const float fgto = gto ? to_f<T>(gto[idx]) : 0.f;
     s1 = fmaf(fgo, fo, s1);
     s2 = fmaf(fgto, fto, s2);
@@ -277,10 +278,11 @@ generic_bwd_kernel(const T* __restrict__ r0p, const T* __restrict__ r1p, const T
   const size_t base = static_cast<size_t>(bh) * N * D;
   const int r0 = rt * TB;
   load_tile_t<T>(R0, r0p + base, r0, N, D);
-  load_tile_t<T>(R1, r1p + base, r0, N, D);
+  const bool dual = p.dual != 0;
+  if (dual) load_tile_t<T>(R1, r1p + base, r0, N, D);
   if (FAM != FAM_V) {
     load_tile_t<T>(R2, r2p + base, r0, N, D);
-    load_tile_t<T>(R3, r3p + base, r0, N, D);
+    if (dual) load_tile_t<T>(R3, r3p + base, r0, N, D);
   }
   float acc0[2][NJ], acc1[2][NJ];
 #pragma unroll
@@ -300,9 +302,9 @@ generic_bwd_kernel(const T* __restrict__ r0p, const T* __restrict__ r1p, const T
     const int c0 = ct * TB;
     __syncthreads();
     load_tile_t<T>(C0, c0p + base, c0, N, D);
-    load_tile_t<T>(C1, c1p + base, c0, N, D);
+    if (dual) load_tile_t<T>(C1, c1p + base, c0, N, D);
     load_tile_t<T>(C2, c2p + base, c0, N, D);
-    load_tile_t<T>(C3, c3p + base, c0, N, D);
+    if (dual) load_tile_t<T>(C3, c3p + base, c0, N, D);
     // statistics of the query positions of this tile pair
     if (threadIdx.x < TB) {
       const int qpos = (FAM == FAM_Q ? r0 : c0) + threadIdx.x;
@@ -317,13 +319,17 @@ generic_bwd_kernel(const T* __restrict__ r0p, const T* __restrict__ r1p, const T
     float T0[2][2] = {{0.f, 0.f}, {0.f, 0.f}}, T1[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
     float T2[2][2] = {{0.f, 0.f}, {0.f, 0.f}}, T3[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
     score_mac(T0, R0, C0, D, ty, tx);
-    score_mac(T1, R1, C0, D, ty, tx);
-    score_mac(T1, R0, C1, D, ty, tx);
+    if (dual) {
+      score_mac(T1, R1, C0, D, ty, tx);
+      score_mac(T1, R0, C1, D, ty, tx);
+    }
     if (FAM != FAM_V) {
       score_mac(T2, R2, C2, D, ty, tx);
-      score_mac(T2, R3, C3, D, ty, tx);
-      if (FAM == FAM_Q) score_mac(T3, R3, C2, D, ty, tx);
-      else score_mac(T3, R2, C3, D, ty, tx);
+      if (dual) {
+        score_mac(T2, R3, C3, D, ty, tx);
+        if (FAM == FAM_Q) score_mac(T3, R3, C2, D, ty, tx);
+        else score_mac(T3, R2, C3, D, ty, tx);
+      }
     }
     const bool use_mask = p.mv.kind != JVPFA_MASK_NONE && (bits & kTileAnyMasked);
 #pragma unroll
@@ -351,12 +357,16 @@ generic_bwd_kernel(const T* __restrict__ r0p, const T* __restrict__ r1p, const T
     __syncthreads();
     if (FAM == FAM_V) {
       out_mac<NJ>(acc0, E0, C2, D, ty, tx);
-      out_mac<NJ>(acc0, E1, C3, D, ty, tx);
-      out_mac<NJ>(acc1, E0, C3, D, ty, tx);
+      if (dual) {
+        out_mac<NJ>(acc0, E1, C3, D, ty, tx);
+        out_mac<NJ>(acc1, E0, C3, D, ty, tx);
+      }
     } else {
       out_mac<NJ>(acc0, E0, C0, D, ty, tx);
-      out_mac<NJ>(acc0, E1, C1, D, ty, tx);
-      out_mac<NJ>(acc1, E1, C0, D, ty, tx);
+      if (dual) {
+        out_mac<NJ>(acc0, E1, C1, D, ty, tx);
+        out_mac<NJ>(acc1, E1, C0, D, ty, tx);
+      }
     }
   }
 #pragma unroll
@@ -368,7 +378,7 @@ generic_bwd_kernel(const T* __restrict__ r0p, const T* __restrict__ r1p, const T
       const int dc = tx + 16 * j;
       if (dc < D) {
         out0[base + static_cast<size_t>(row) * D + dc] = from_f<T>(acc0[i][j] * p.out_scale);
-        out1[base + static_cast<size_t>(row) * D + dc] = from_f<T>(acc1[i][j] * p.out_scale);
+        if (dual) out1[base + static_cast<size_t>(row) * D + dc] = from_f<T>(acc1[i][j] * p.out_scale);
       }
     }
   }
@@ -416,6 +426,7 @@ template <typename T, int NJ, int FAM>
 int bwd_family(const jvpfa_bwd_args& a, const float4* stats, cudaStream_t stream) {
   GenParams p = make_params(a.H, a.N, a.D, a.causal, a.sm_scale, a.mask, a.mask_summary);
   p.stats = stats;
+  p.dual = a.tq != nullptr;
   const T *r[4], *c[4];
   T *o0, *o1;
   auto cp = [](const void* x) { return static_cast<const T*>(x); };

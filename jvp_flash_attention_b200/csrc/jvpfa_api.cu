@@ -208,12 +208,17 @@ int jvpfa_bwd(const jvpfa_bwd_args* a, void* stream) {
   int rc = check_common(a->B, a->H, a->N, a->D, a->dtype, a->causal, a->mask, a->workspace, a->workspace_bytes,
                         jvpfa_bwd_workspace_bytes(a));
   if (rc != JVPFA_OK) return rc;
-  if (!a->q || !a->k || !a->v || !a->tq || !a->tk || !a->tv || !a->o || !a->to || !a->lse2 || !a->mu || !a->go || !a->gto ||
-      !a->dq || !a->dk || !a->dv || !a->dtq || !a->dtk || !a->dtv)
-    return JVPFA_ERR_BAD_ARG;
-  const void* ptrs[] = {a->q, a->k, a->v, a->tq, a->tk, a->tv, a->o, a->to, a->go, a->gto, a->dq, a->dk, a->dv, a->dtq, a->dtk, a->dtv};
+  if (!a->q || !a->k || !a->v || !a->o || !a->lse2 || !a->mu || !a->go || !a->dq || !a->dk || !a->dv) return JVPFA_ERR_BAD_ARG;
+  const bool dual = a->tq != nullptr;   // tq == NULL: primal-only backward, the tangent-side pointers are ignored
+  if (dual && (!a->tk || !a->tv || !a->to || !a->gto || !a->dtq || !a->dtk || !a->dtv)) return JVPFA_ERR_BAD_ARG;
+  const void* ptrs[] = {a->q, a->k, a->v, a->o, a->go, a->dq, a->dk, a->dv};
   for (const void* p : ptrs)
     if (!aligned16(p)) return JVPFA_ERR_BAD_ARG;
+  if (dual) {
+    const void* tptrs[] = {a->tq, a->tk, a->tv, a->to, a->gto, a->dtq, a->dtk, a->dtv};
+    for (const void* p : tptrs)
+      if (!aligned16(p)) return JVPFA_ERR_BAD_ARG;
+  }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (sm100_path_supported(a->dtype, a->D, a->N)) return launch_bwd_sm100(*a, s);
   return launch_bwd_generic(*a, s);

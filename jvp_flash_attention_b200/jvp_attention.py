@@ -133,11 +133,10 @@ class _PrimalAttention(Function):
         q, k, v, o, lse2, mu, summary = ctx.saved_tensors
         B, H, N, D = q.shape
         go = go.contiguous()
-        zeros = torch.zeros_like(q)
         mask_c = _lib.make_mask(ctx.attn_mask, B, H, N)
         summ = summary if summary.numel() > 0 else None
-        dq, dk, dv, _, _, _ = _lib.bwd(q, k, v, zeros, zeros, zeros, o, zeros, lse2, mu, go, zeros, mask_c, summ,
-                                       ctx.causal, ctx.sm_scale)
+        dq, dk, dv = _lib.bwd(q, k, v, None, None, None, o, None, lse2, mu, go, None, mask_c, summ, ctx.causal,
+                              ctx.sm_scale)
         return dq, dk, dv, None, None, None
 
 
