@@ -1,5 +1,5 @@
 """Writes the golden fixtures of this folder. Run once in a container that holds the reference
-checkout (REFERENCE_ROOT, default /root/reference); the fixtures travel, the reference does not.
+checkout (its path in the REFERENCE_ROOT environment variable); the fixtures travel, the reference does not.
 
 reference_interp_*.npz
     Inputs and outputs of the reference's own Triton kernels (jvp_flash_attention/jvp_attention.py,
@@ -17,7 +17,7 @@ from pathlib import Path
 os.environ["TRITON_INTERPRET"] = "1"
 HERE = Path(__file__).resolve().parent
 REPO = HERE.parent.parent
-REF = Path(os.environ.get("REFERENCE_ROOT", "/root/reference"))
+REF = Path(os.environ["REFERENCE_ROOT"])
 sys.path.insert(0, str(REPO))
 
 import numpy as np
