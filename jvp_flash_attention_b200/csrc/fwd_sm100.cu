@@ -90,15 +90,9 @@ struct FwdCfg {
   static constexpr size_t smem_bytes() { return 2 * TILE_Q + STAGES * STAGE + 2 * 2 * 128 * 4 + (NBAR + 2) * 8; }
 };
 
-__device__ __forceinline__ void mbar_wait_warp(uint64_t* bar, uint32_t parity, const WaitCtx& w, int site) {
-  mbar_wait(bar, parity, w, site);
-  __syncwarp();
-}
-
 // Warps 0-7: two softmax warpgroups that split the 64 columns of every score tile (thread = TMEM lane =
 // one score row, 32 columns; the row maximum and the final row sums are exchanged through shared
-// memory); warp 8: TMA producer; warp 9: MMA issuer (all lanes run the loop so that operands stay
-// warp-uniform, lane 0 issues) and owner of the TMEM allocation.
+// memory); warp 8: TMA producer (one lane); warp 9: MMA issuer (one lane) and owner of the TMEM allocation.
 // PAD: the tensors' head dimension is smaller than D (columns beyond it are zero-filled by TMA); the K steps and
 // output columns that would only see zeros are then skipped at run time.
 template <int D, bool DUAL, bool BF16, bool PAD>
@@ -222,6 +216,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   } else if (warp == 9) {
     // ------------------------------------------------------------------ MMA issuer
     const bool leader = lane == 0;
+    if (leader) {
     constexpr uint32_t FMT = BF16 ? FMT_BF16 : FMT_F16;
     const uint32_t idesc_64 = make_idesc(FMT, 128, 64, 0, 0);
     const uint32_t idesc_128 = make_idesc(FMT, 128, 128, 0, 0);
@@ -235,7 +230,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const uint32_t ph = (it / ST) & 1;
       const uint32_t S_t = tmem + C::TMEM_S + (it & 1) * 128;
       if (leader) JVPFA_FTR(0, it, 0);
-      mbar_wait_warp(&k_full[st], ph, w, 20);
+      mbar_wait(&k_full[st], ph, w, 20);
       tc_fence_after_sync();
       if (leader) JVPFA_FTR(0, it, 1);
       const uint64_t dK = desc_kmajor_sw128(smem_u32(sK(st)));
@@ -255,7 +250,6 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         umma_commit(&s_full[it & 1]);
         umma_commit(&k_empty[st]);
       }
-      __syncwarp();
       if (leader) JVPFA_FTR(0, it, 2);
     };
     auto issue_pv = [&](int it, bool last) {
@@ -264,9 +258,9 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const uint32_t P_t = tmem + C::TMEM_S + (it & 1) * 128;
       const uint32_t W_t = P_t + 64;
       if (leader) JVPFA_FTR(0, it, 3);
-      mbar_wait_warp(&p_full[it & 1], (it >> 1) & 1, w, 21);
+      mbar_wait(&p_full[it & 1], (it >> 1) & 1, w, 21);
       if (leader) JVPFA_FTR(0, it, 4);
-      mbar_wait_warp(&v_full[st], ph, w, 22);
+      mbar_wait(&v_full[st], ph, w, 22);
       tc_fence_after_sync();
       if (leader) JVPFA_FTR(0, it, 5);
       const uint64_t dV0 = desc_mnmajor_sw128(smem_u32(sV(st)), C::BN * 128);
@@ -287,11 +281,10 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         umma_commit(&o_done);
         if (last) umma_commit(&o_final);
       }
-      __syncwarp();
       if (leader) JVPFA_FTR(0, it, 6);
     };
 
-    mbar_wait_warp(&q_full, 0, w, 23);
+    mbar_wait(&q_full, 0, w, 23);
     int it = 0;
     for (int j = 0; j < n_kt; ++j) {
       if (!(tile_bits(j) & kTileAnyKept)) continue;
@@ -300,6 +293,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       ++it;
     }
     if (it > 0) issue_pv(it - 1, true);
+    }
+    __syncwarp();
   } else {
     // ------------------------------------------------------------------ softmax, correction, epilogue
     const int wg = warp >> 2;
