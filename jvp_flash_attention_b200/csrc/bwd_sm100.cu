@@ -96,7 +96,7 @@ struct BwdCfg {
   static constexpr int TMEM_ACC1 = D;
   static constexpr int TMEM_T = 2 * D;                   // score tiles, 64 columns each
   static constexpr int TMEM_COLS = 512;
-  static constexpr int NBAR = 8 + 2 * NA + 2 * NB;
+  static constexpr int NBAR = 8 + 2 * NA + 2 * NB + 2;
   static constexpr size_t smem_bytes() { return NR * TILE_R + (NA + NB) * PAIR + 2 * BC * 16 + (NBAR + 2) * 8; }
 };
 
@@ -117,7 +117,7 @@ struct BwdCfg {
 // DUAL = false: primal-only backward (no tangents, no gradient through a tangent output): S and X = gO V^T only,
 // dS = P (X - Delta); dQ = s dS K, dK = s dS^T Q, dV = P^T gO. Tangent tiles are neither loaded nor multiplied.
 template <int D, int FAM, bool BF16, bool PAD, bool DUAL>
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(352, 1)
 bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant__ CUtensorMap rm1,
                  const __grid_constant__ CUtensorMap rm2, const __grid_constant__ CUtensorMap rm3,
                  const __grid_constant__ CUtensorMap cm0, const __grid_constant__ CUtensorMap cm1,
@@ -147,6 +147,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
   uint64_t* a_empty = a_full + NA;
   uint64_t* b_full = a_empty + NA;
   uint64_t* b_empty = b_full + NB;
+  uint64_t* e_free = b_empty + NB;   // [2] family V: the output products that read score buffer b have completed
   uint32_t& tmem_base_s = *reinterpret_cast<uint32_t*>(bars + C::NBAR);
   int& poisoned = *reinterpret_cast<int*>(bars + C::NBAR + 1);
   if ((smem_u32(smem) & 1023u) != 0u) {  // the swizzled layouts need this; never observed otherwise
@@ -178,6 +179,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
     for (int i = 0; i < 2; ++i) {
       mbar_init(&st_full[i], 1);
       mbar_init(&p_full[i], 256);
+      mbar_init(&e_free[i], 1);
     }
     mbar_init(&ph1_done, 256);
     mbar_init(&xa_full, 1);
@@ -260,8 +262,9 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
       }
     }
     __syncwarp();
-  } else if (warp == 9) {
-    // ------------------------------------------------------------------ MMA issuer
+  } else if (warp >= 9) {
+    // ------------------------------------------------------------------ MMA issuers: warp 9 the score products S, tS;
+    // warp 10 the output products and X, A (two instruction streams keep the tensor pipe fed while one of them waits)
     {
       // all lanes run the loop so that addresses and descriptors stay warp-uniform; lane 0 issues
       const bool leader = lane == 0;
@@ -336,57 +339,68 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
       wait_all(&r_full, 0, 22);
       int j = next_active(j_begin);
       int it = 0;
-      if (j < j_end) {
-        issue_st(0, 0);
-        if constexpr (FAM != FAM_V) issue_xa(0);
-      }
-      for (; j < j_end; ++it) {
-        const int jn = next_active(j + 1);
-        const bool has_next = jn < j_end;
-        JVPFA_TR(0, it, 0);
-        if constexpr (FAM == FAM_V) {
-          if (has_next) issue_st(it + 1, (it + 1) & 1);
-          JVPFA_TR(0, it, 1);
-          const int buf = it % NB;
-          wait_all(&p_full[it & 1], (it >> 1) & 1, 23);
-          wait_all(&b_full[buf], (it / NB) & 1, 24);
-          tc_fence_after_sync();
-          JVPFA_TR(0, it, 2);
-          const uint32_t E0 = TS0 + (it & 1) * 128, E1 = E0 + 64;
-          mma_out(tmem + C::TMEM_ACC0, E0, sB(buf), it > 0);               // dV  += P^T gO + tP^T gtO
-          if constexpr (DUAL) {
-            mma_out(tmem + C::TMEM_ACC0, E1, sB(buf) + C::HALF, 1);
-            mma_out(tmem + C::TMEM_ACC1, E0, sB(buf) + C::HALF, it > 0);   // dtV += P^T gtO
-          }
-          if (leader) umma_commit(&b_empty[buf]);
-          JVPFA_TR(0, it, 3);
-        } else {
-          if (has_next) {
-            wait_all(&ph1_done, it & 1, 25);
-            issue_st(it + 1, 0);
+      if (warp == 9) {
+        // ---- score issuer: S, tS of tile it + 1 as soon as the element-wise warps have read those of tile it
+        if (j < j_end) issue_st(0, 0);
+        for (; j < j_end; ++it) {
+          const int jn = next_active(j + 1);
+          JVPFA_TR(0, it, 0);
+          if (jn < j_end) {
+            if constexpr (FAM == FAM_V) {
+              if (it >= 1) wait_all(&e_free[(it + 1) & 1], ((it - 1) >> 1) & 1, 27);
+              issue_st(it + 1, (it + 1) & 1);
+            } else {
+              wait_all(&ph1_done, it & 1, 25);
+              issue_st(it + 1, 0);
+            }
           }
           JVPFA_TR(0, it, 1);
-          const int buf = it % NA;
-          wait_all(&p_full[0], it & 1, 26);
-          tc_fence_after_sync();
-          JVPFA_TR(0, it, 2);
-          // dS in the first score tile of the second group, dtS in the second; for family K the
-          // pair product leaves X first and A second, the element-wise code writes them the same way
-          const uint32_t E0 = TS0 + 128, E1 = TS0 + 192;
-          mma_out(tmem + C::TMEM_ACC0, E0, sA(buf), it > 0);               // dS c0 + dtS c1
-          if constexpr (DUAL) {
-            mma_out(tmem + C::TMEM_ACC0, E1, sA(buf) + C::HALF, 1);
-            mma_out(tmem + C::TMEM_ACC1, E1, sA(buf), it > 0);             // dtS c0
-          }
-          if (leader) umma_commit(&a_empty[buf]);
-          JVPFA_TR(0, it, 3);
-          if (has_next) issue_xa(it + 1);
-          JVPFA_TR(0, it, 4);
+          j = jn;
         }
-        j = jn;
+      } else {
+        // ---- output issuer
+        if constexpr (FAM != FAM_V) if (j < j_end) issue_xa(0);
+        for (; j < j_end; ++it) {
+          const int jn = next_active(j + 1);
+          const bool has_next = jn < j_end;
+          if constexpr (FAM == FAM_V) {
+            const int buf = it % NB;
+            wait_all(&p_full[it & 1], (it >> 1) & 1, 23);
+            wait_all(&b_full[buf], (it / NB) & 1, 24);
+            tc_fence_after_sync();
+            JVPFA_TR(0, it, 2);
+            const uint32_t E0 = TS0 + (it & 1) * 128, E1 = E0 + 64;
+            mma_out(tmem + C::TMEM_ACC0, E0, sB(buf), it > 0);               // dV  += P^T gO + tP^T gtO
+            if constexpr (DUAL) {
+              mma_out(tmem + C::TMEM_ACC0, E1, sB(buf) + C::HALF, 1);
+              mma_out(tmem + C::TMEM_ACC1, E0, sB(buf) + C::HALF, it > 0);   // dtV += P^T gtO
+            }
+            if (leader) umma_commit(&b_empty[buf]);
+            if (leader) umma_commit(&e_free[it & 1]);
+            JVPFA_TR(0, it, 3);
+          } else {
+            const int buf = it % NA;
+            wait_all(&p_full[0], it & 1, 26);
+            tc_fence_after_sync();
+            JVPFA_TR(0, it, 2);
+            // dS in the first score tile of the second group, dtS in the second; for family K the
+            // pair product leaves X first and A second, the element-wise code writes them the same way
+            const uint32_t E0 = TS0 + 128, E1 = TS0 + 192;
+            mma_out(tmem + C::TMEM_ACC0, E0, sA(buf), it > 0);               // dS c0 + dtS c1
+            if constexpr (DUAL) {
+              mma_out(tmem + C::TMEM_ACC0, E1, sA(buf) + C::HALF, 1);
+              mma_out(tmem + C::TMEM_ACC1, E1, sA(buf), it > 0);             // dtS c0
+            }
+            if (leader) umma_commit(&a_empty[buf]);
+            JVPFA_TR(0, it, 3);
+            if (has_next) issue_xa(it + 1);
+            JVPFA_TR(0, it, 4);
+          }
+          j = jn;
+        }
+        if (it > 0) { if (leader) umma_commit(&acc_final); }
+        else if (leader) mbar_arrive(&acc_final);
       }
-      if (it > 0) { if (leader) umma_commit(&acc_final); }
-      else if (leader) mbar_arrive(&acc_final);
     }
     __syncwarp();
   } else {
@@ -687,7 +701,7 @@ int launch_family(const jvpfa_bwd_args& a, const float4* stats, cudaStream_t str
     return JVPFA_ERR_LAUNCH;
   dim3 grid((a.N + C::BR - 1) / C::BR, a.B * a.H);
   ScopedKernelTimer timer(FAM == FAM_Q ? KERNEL_BWD_Q : (FAM == FAM_K ? KERNEL_BWD_K : KERNEL_BWD_V), stream);
-  kern<<<grid, 320, smem, stream>>>(rm[0], rm[1], rm[2], rm[3], cm[0], cm[1], cm[2], cm[3], p);
+  kern<<<grid, 352, smem, stream>>>(rm[0], rm[1], rm[2], rm[3], cm[0], cm[1], cm[2], cm[3], p);
   return cudaGetLastError() == cudaSuccess ? JVPFA_OK : JVPFA_ERR_LAUNCH;
 }
 

@@ -86,7 +86,7 @@ struct FwdCfg {
   static constexpr int TMEM_T = D;
   static constexpr int TMEM_S = 2 * D;  // buffer b at TMEM_S + 128*b; tS 64 columns further
   static constexpr int TMEM_COLS = 512;
-  static constexpr int NBAR = 4 + 4 * STAGES + 4;
+  static constexpr int NBAR = 4 + 4 * STAGES + 4 + 2;
   static constexpr size_t smem_bytes() { return 2 * TILE_Q + STAGES * STAGE + 2 * 2 * 128 * 4 + (NBAR + 2) * 8; }
 };
 
@@ -96,7 +96,7 @@ struct FwdCfg {
 // PAD: the tensors' head dimension is smaller than D (columns beyond it are zero-filled by TMA); the K steps and
 // output columns that would only see zeros are then skipped at run time.
 template <int D, bool DUAL, bool BF16, bool PAD>
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(352, 1)
 fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmTQ,
                  const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmTK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmTV,
@@ -123,6 +123,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint64_t* v_full = k_full + ST;
   uint64_t* k_empty = v_full + ST;
   uint64_t* v_empty = k_empty + ST;
+  uint64_t* s_free = v_empty + ST;   // [2]: the PV products that read score buffer b have completed
   uint32_t& tmem_base_s = *reinterpret_cast<uint32_t*>(bars + C::NBAR);
   int& poisoned = *reinterpret_cast<int*>(bars + C::NBAR + 1);
   if ((smem_u32(smem) & 1023u) != 0u) {  // the swizzled layouts need this; never observed otherwise
@@ -154,6 +155,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s_full[i], 1);
       mbar_init(&p_full[i], 256);
+      mbar_init(&s_free[i], 1);
     }
     mbar_init(&o_done, 1);
     mbar_init(&o_final, 1);
@@ -213,8 +215,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
     }
     __syncwarp();
-  } else if (warp == 9) {
-    // ------------------------------------------------------------------ MMA issuer
+  } else if (warp >= 9) {
+    // ------------------------------------------------------------------ MMA issuers: warp 9 scores, warp 10 outputs
     const bool leader = lane == 0;
     if (leader) {
     constexpr uint32_t FMT = BF16 ? FMT_BF16 : FMT_F16;
@@ -231,6 +233,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const uint32_t S_t = tmem + C::TMEM_S + (it & 1) * 128;
       if (leader) JVPFA_FTR(0, it, 0);
       mbar_wait(&k_full[st], ph, w, 20);
+      if (it >= 2) mbar_wait(&s_free[it & 1], ((it >> 1) - 1) & 1, w, 24);
       tc_fence_after_sync();
       if (leader) JVPFA_FTR(0, it, 1);
       const uint64_t dK = desc_kmajor_sw128(smem_u32(sK(st)));
@@ -278,21 +281,29 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           }
         }
         umma_commit(&v_empty[st]);
+        umma_commit(&s_free[it & 1]);
         umma_commit(&o_done);
         if (last) umma_commit(&o_final);
       }
       if (leader) JVPFA_FTR(0, it, 6);
     };
 
-    mbar_wait(&q_full, 0, w, 23);
     int it = 0;
-    for (int j = 0; j < n_kt; ++j) {
-      if (!(tile_bits(j) & kTileAnyKept)) continue;
-      issue_qk(it);
-      if (it > 0) issue_pv(it - 1, false);
-      ++it;
+    if (warp == 9) {
+      mbar_wait(&q_full, 0, w, 23);
+      for (int j = 0; j < n_kt; ++j) {
+        if (!(tile_bits(j) & kTileAnyKept)) continue;
+        issue_qk(it);
+        ++it;
+      }
+    } else {
+      for (int j = 0; j < n_kt; ++j) {
+        if (!(tile_bits(j) & kTileAnyKept)) continue;
+        if (it > 0) issue_pv(it - 1, false);
+        ++it;
+      }
+      if (it > 0) issue_pv(it - 1, true);
     }
-    if (it > 0) issue_pv(it - 1, true);
     }
     __syncwarp();
   } else {
@@ -518,7 +529,7 @@ int launch_one(const jvpfa_fwd_args& a, cudaStream_t stream) {
     return JVPFA_ERR_LAUNCH;
   dim3 grid((a.N + C::BM - 1) / C::BM, a.B * a.H);
   ScopedKernelTimer timer(KERNEL_FWD, stream);
-  kern<<<grid, 320, smem, stream>>>(mQ, mTQ, mK, mTK, mV, mTV, p);
+  kern<<<grid, 352, smem, stream>>>(mQ, mTQ, mK, mTK, mV, mTV, p);
   return cudaGetLastError() == cudaSuccess ? JVPFA_OK : JVPFA_ERR_LAUNCH;
 }
 
