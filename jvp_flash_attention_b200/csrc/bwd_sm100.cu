@@ -96,7 +96,7 @@ struct BwdCfg {
   static constexpr int TMEM_ACC1 = D;
   static constexpr int TMEM_T = 2 * D;                   // score tiles, 64 columns each
   static constexpr int TMEM_COLS = 512;
-  static constexpr int NBAR = 8 + 2 * NA + 2 * NB + 2;
+  static constexpr int NBAR = 8 + 2 * NA + 2 * NB + 4;
   static constexpr size_t smem_bytes() { return NR * TILE_R + (NA + NB) * PAIR + 2 * BC * 16 + (NBAR + 2) * 8; }
 };
 
@@ -148,6 +148,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
   uint64_t* b_full = a_empty + NA;
   uint64_t* b_empty = b_full + NB;
   uint64_t* e_free = b_empty + NB;   // [2] family V: the output products that read score buffer b have completed
+  uint64_t& a_ready = e_free[2];     // families Q, K: A of the current tile is complete (X still accumulating)
+  uint64_t& pt_full = e_free[3];     // families Q, K: dtS of the current tile is in TMEM
   uint32_t& tmem_base_s = *reinterpret_cast<uint32_t*>(bars + C::NBAR);
   int& poisoned = *reinterpret_cast<int*>(bars + C::NBAR + 1);
   if ((smem_u32(smem) & 1023u) != 0u) {  // the swizzled layouts need this; never observed otherwise
@@ -183,6 +185,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
     }
     mbar_init(&ph1_done, 256);
     mbar_init(&xa_full, 1);
+    mbar_init(&a_ready, 1);
+    mbar_init(&pt_full, 256);
     mbar_init(&acc_final, 1);
     for (int i = 0; i < NA; ++i) {
       mbar_init(&a_full[i], 1);
@@ -327,9 +331,11 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
           mma_nt(FAM == FAM_Q ? T2 + 64 : T2, sR(2), sB(buf), idesc_64, 0);   // X = gO V^T (family K: its transpose)
         } else if constexpr (FAM == FAM_Q) {
           mma_nt(T2, sR(3), sB(buf), idesc_128, 0);               // [A | gtO tV^T]
+          if (leader) umma_commit(&a_ready);
           mma_nt(T2 + 64, sR(2), sB(buf), idesc_64, 1);           // X += gO V^T
         } else {
           mma_nt(T2, sR(2), sB(buf), idesc_128, 0);               // [V gO^T | A^T]
+          if (leader) umma_commit(&a_ready);
           mma_nt(T2, sR(3), sB(buf) + C::HALF, idesc_64, 1);      // X^T += tV gtO^T
         }
         if (leader) umma_commit(&xa_full);
@@ -351,6 +357,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
               issue_st(it + 1, (it + 1) & 1);
             } else {
               wait_all(&ph1_done, it & 1, 25);
+              JVPFA_TR(0, it, 5);
               issue_st(it + 1, 0);
             }
           }
@@ -380,17 +387,22 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
             JVPFA_TR(0, it, 3);
           } else {
             const int buf = it % NA;
+            // dtS replaces A and dS replaces X in place (family Q: A first, X second; family K: X first, A second).
+            // dtS only needs A, which the first X/A chain completes, so its two products run before dS exists.
+            const uint32_t E0 = (DUAL && FAM == FAM_Q) ? TS0 + 192 : TS0 + 128;   // dS
+            const uint32_t E1 = (DUAL && FAM == FAM_Q) ? TS0 + 128 : TS0 + 192;   // dtS
+            if constexpr (DUAL) {
+              JVPFA_TR(0, it, 6);
+              wait_all(&pt_full, it & 1, 28);
+              tc_fence_after_sync();
+              JVPFA_TR(0, it, 7);
+              mma_out(tmem + C::TMEM_ACC0, E1, sA(buf) + C::HALF, it > 0);   // dtS c1
+              mma_out(tmem + C::TMEM_ACC1, E1, sA(buf), it > 0);             // dtS c0
+            }
             wait_all(&p_full[0], it & 1, 26);
             tc_fence_after_sync();
             JVPFA_TR(0, it, 2);
-            // dS in the first score tile of the second group, dtS in the second; for family K the
-            // pair product leaves X first and A second, the element-wise code writes them the same way
-            const uint32_t E0 = TS0 + 128, E1 = TS0 + 192;
-            mma_out(tmem + C::TMEM_ACC0, E0, sA(buf), it > 0);               // dS c0 + dtS c1
-            if constexpr (DUAL) {
-              mma_out(tmem + C::TMEM_ACC0, E1, sA(buf) + C::HALF, 1);
-              mma_out(tmem + C::TMEM_ACC1, E1, sA(buf), it > 0);             // dtS c0
-            }
+            mma_out(tmem + C::TMEM_ACC0, E0, sA(buf), DUAL ? 1u : static_cast<uint32_t>(it > 0));   // dS c0
             if (leader) umma_commit(&a_empty[buf]);
             JVPFA_TR(0, it, 3);
             if (has_next) issue_xa(it + 1);
@@ -525,41 +537,75 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
           if constexpr (DUAL) tmem_st_x8(T1 + 8 * hch, e1);
         }
       } else {
-        // ---- phase 2: X, A -> dS = P (X - Delta + ts (A - a) - mu A), dtS = P (A - a)
+        // ---- phase 2: X, A -> dS = P (X - Delta + ts (A - a) - mu A), dtS = P (A - a); both replace their
+        // source in place in this thread's own columns
         const uint32_t T2 = TS0 + 128 + 32 * wg, T3 = T2 + 64;
-        mbar_wait(&xa_full, it & 1, w, 31);
-        tc_fence_after_sync();
-        if (tr) JVPFA_TR(1 + wg, it, 4);
+        if constexpr (DUAL) {
+          const uint32_t TA = (FAM == FAM_Q) ? T2 : T3, TX = (FAM == FAM_Q) ? T3 : T2;
+          // phase 2a, as soon as A is complete: dtS, and everything of dS that does not need X (kept in ts2)
+          mbar_wait(&a_ready, it & 1, w, 33);
+          tc_fence_after_sync();
 #pragma unroll
-        for (int hch = 0; hch < 2; ++hch) {
-          uint32_t x2r[16], x3r[16];
-          if (DUAL || FAM != FAM_Q) tmem_ld_x16(T2 + 16 * hch, x2r);
-          if (DUAL || FAM == FAM_Q) tmem_ld_x16(T3 + 16 * hch, x3r);
-          tmem_wait_ld();
-          uint32_t e0[8], e1[8];
+          for (int hch = 0; hch < 2; ++hch) {
+            uint32_t ar[16];
+            tmem_ld_x16(TA + 16 * hch, ar);
+            tmem_wait_ld();
+            uint32_t e1[8];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int ip = 8 * hch + i;
-            if constexpr (DUAL) {
-              const float2 t2v = make_float2(__uint_as_float(x2r[2 * i]), __uint_as_float(x2r[2 * i + 1]));
-              const float2 t3v = make_float2(__uint_as_float(x3r[2 * i]), __uint_as_float(x3r[2 * i + 1]));
-              const float2 A = (FAM == FAM_Q) ? t2v : t3v;
-              const float2 X = (FAM == FAM_Q) ? t3v : t2v;
+            for (int i = 0; i < 8; ++i) {
+              const int ip = 8 * hch + i;
+              const float2 A = make_float2(__uint_as_float(ar[2 * i]), __uint_as_float(ar[2 * i + 1]));
               const float2 d = __fadd2_rn(A, stat2(3, ip));                       // A - a
-              float2 t = __ffma2_rn(ts2[ip], d, __fadd2_rn(X, stat2(2, ip)));     // X - Delta + ts (A - a)
-              t = __ffma2_rn(stat2(1, ip), A, t);                                 // - mu A
-              const float2 ds = __fmul2_rn(P2[ip], t), dts = __fmul2_rn(P2[ip], d);
-              e0[i] = pack2<BF16>(ds.x, ds.y);
+              float2 t = __ffma2_rn(ts2[ip], d, stat2(2, ip));                    // ts (A - a) - Delta
+              ts2[ip] = __ffma2_rn(stat2(1, ip), A, t);                           // - mu A
+              const float2 dts = __fmul2_rn(P2[ip], d);
               e1[i] = pack2<BF16>(dts.x, dts.y);
-            } else {
-              const float2 X = (FAM == FAM_Q) ? make_float2(__uint_as_float(x3r[2 * i]), __uint_as_float(x3r[2 * i + 1]))
-                                              : make_float2(__uint_as_float(x2r[2 * i]), __uint_as_float(x2r[2 * i + 1]));
+            }
+            tmem_st_x8(TA + 8 * hch, e1);
+          }
+          tmem_wait_st();
+          tc_fence_before_sync();
+          mbar_arrive(&pt_full);
+          if (tr) JVPFA_TR(1 + wg, it, 7);
+          // phase 2b, when X is complete
+          mbar_wait(&xa_full, it & 1, w, 31);
+          tc_fence_after_sync();
+          if (tr) JVPFA_TR(1 + wg, it, 4);
+#pragma unroll
+          for (int hch = 0; hch < 2; ++hch) {
+            uint32_t xr[16];
+            tmem_ld_x16(TX + 16 * hch, xr);
+            tmem_wait_ld();
+            uint32_t e0[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int ip = 8 * hch + i;
+              const float2 X = make_float2(__uint_as_float(xr[2 * i]), __uint_as_float(xr[2 * i + 1]));
+              const float2 ds = __fmul2_rn(P2[ip], __fadd2_rn(X, ts2[ip]));
+              e0[i] = pack2<BF16>(ds.x, ds.y);
+            }
+            tmem_st_x8(TX + 8 * hch, e0);
+          }
+        } else {
+          mbar_wait(&xa_full, it & 1, w, 31);
+          tc_fence_after_sync();
+          if (tr) JVPFA_TR(1 + wg, it, 4);
+          const uint32_t TX = (FAM == FAM_Q) ? T3 : T2;
+#pragma unroll
+          for (int hch = 0; hch < 2; ++hch) {
+            uint32_t xr[16];
+            tmem_ld_x16(TX + 16 * hch, xr);
+            tmem_wait_ld();
+            uint32_t e0[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int ip = 8 * hch + i;
+              const float2 X = make_float2(__uint_as_float(xr[2 * i]), __uint_as_float(xr[2 * i + 1]));
               const float2 ds = __fmul2_rn(P2[ip], __fadd2_rn(X, stat2(2, ip)));  // P (X - Delta)
               e0[i] = pack2<BF16>(ds.x, ds.y);
             }
+            tmem_st_x8(T2 + 8 * hch, e0);
           }
-          tmem_st_x8(T2 + 8 * hch, e0);
-          if constexpr (DUAL) tmem_st_x8(T3 + 8 * hch, e1);
         }
       }
       if (tr) JVPFA_TR(1 + wg, it, 5);
