@@ -96,7 +96,7 @@ struct BwdCfg {
   static constexpr int TMEM_ACC1 = D;
   static constexpr int TMEM_T = 2 * D;                   // score tiles, 64 columns each
   static constexpr int TMEM_COLS = 512;
-  static constexpr int NBAR = 8 + 2 * NA + 2 * NB + 4;
+  static constexpr int NBAR = 8 + 2 * NA + 2 * NB + 8;
   static constexpr size_t smem_bytes() { return NR * TILE_R + (NA + NB) * PAIR + 2 * BC * 16 + (NBAR + 2) * 8; }
 };
 
@@ -150,6 +150,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
   uint64_t* e_free = b_empty + NB;   // [2] family V: the output products that read score buffer b have completed
   uint64_t& a_ready = e_free[2];     // families Q, K: A of the current tile is complete (X still accumulating)
   uint64_t& pt_full = e_free[3];     // families Q, K: dtS of the current tile is in TMEM
+  uint64_t* s_ready = e_free + 4;    // [2] family V: S of score buffer b is complete (tS still accumulating)
+  uint64_t* pp_full = e_free + 6;    // [2] family V: P of score buffer b is in TMEM
   uint32_t& tmem_base_s = *reinterpret_cast<uint32_t*>(bars + C::NBAR);
   int& poisoned = *reinterpret_cast<int*>(bars + C::NBAR + 1);
   if ((smem_u32(smem) & 1023u) != 0u) {  // the swizzled layouts need this; never observed otherwise
@@ -182,6 +184,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
       mbar_init(&st_full[i], 1);
       mbar_init(&p_full[i], 256);
       mbar_init(&e_free[i], 1);
+      mbar_init(&s_ready[i], 1);
+      mbar_init(&pp_full[i], 256);
     }
     mbar_init(&ph1_done, 256);
     mbar_init(&xa_full, 1);
@@ -310,10 +314,13 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
       auto issue_st = [&](int i, int sb) {
         const int buf = i % NA;
         wait_all(&a_full[buf], (i / NA) & 1, 20);
+        // family V: score buffer sb is free once the output products of tile i - 2 have read P, tP from it
+        if constexpr (FAM == FAM_V) if (i >= 2) wait_all(&e_free[sb], ((i - 2) >> 1) & 1, 27);
         tc_fence_after_sync();
         const uint32_t T0 = TS0 + sb * 128;
         if constexpr (DUAL) {
           mma_nt(T0, sR(0), sA(buf), idesc_128, 0);        // [S | R0 c1^T]
+          if constexpr (FAM == FAM_V) if (leader) umma_commit(&s_ready[sb]);
           mma_nt(T0 + 64, sR(1), sA(buf), idesc_64, 1);    // tS += R1 c0^T
         } else {
           mma_nt(T0, sR(0), sA(buf), idesc_64, 0);         // S
@@ -353,7 +360,6 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
           JVPFA_TR(0, it, 0);
           if (jn < j_end) {
             if constexpr (FAM == FAM_V) {
-              if (it >= 1) wait_all(&e_free[(it + 1) & 1], ((it - 1) >> 1) & 1, 27);
               issue_st(it + 1, (it + 1) & 1);
             } else {
               wait_all(&ph1_done, it & 1, 25);
@@ -372,16 +378,22 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
           const bool has_next = jn < j_end;
           if constexpr (FAM == FAM_V) {
             const int buf = it % NB;
-            wait_all(&p_full[it & 1], (it >> 1) & 1, 23);
-            wait_all(&b_full[buf], (it / NB) & 1, 24);
-            tc_fence_after_sync();
-            JVPFA_TR(0, it, 2);
             const uint32_t E0 = TS0 + (it & 1) * 128, E1 = E0 + 64;
-            mma_out(tmem + C::TMEM_ACC0, E0, sB(buf), it > 0);               // dV  += P^T gO + tP^T gtO
+            JVPFA_TR(0, it, 6);
+            wait_all(&b_full[buf], (it / NB) & 1, 24);
             if constexpr (DUAL) {
-              mma_out(tmem + C::TMEM_ACC0, E1, sB(buf) + C::HALF, 1);
+              // P only needs S, which the first score chain completes: its two products run before tP exists
+              wait_all(&pp_full[it & 1], (it >> 1) & 1, 29);
+              tc_fence_after_sync();
+              JVPFA_TR(0, it, 7);
+              mma_out(tmem + C::TMEM_ACC0, E0, sB(buf), it > 0);             // dV  += P^T gO
               mma_out(tmem + C::TMEM_ACC1, E0, sB(buf) + C::HALF, it > 0);   // dtV += P^T gtO
             }
+            wait_all(&p_full[it & 1], (it >> 1) & 1, 23);
+            tc_fence_after_sync();
+            JVPFA_TR(0, it, 2);
+            if constexpr (DUAL) mma_out(tmem + C::TMEM_ACC0, E1, sB(buf) + C::HALF, 1);   // dV += tP^T gtO
+            else mma_out(tmem + C::TMEM_ACC0, E0, sB(buf), it > 0);                         // dV += P^T gO
             if (leader) umma_commit(&b_empty[buf]);
             if (leader) umma_commit(&e_free[it & 1]);
             JVPFA_TR(0, it, 3);
@@ -433,23 +445,32 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
     }
     const float2 c1_2 = make_float2(p.c1, p.c1), s_2 = make_float2(p.s, p.s);
     int it = 0;
-    for (int j = next_active(j_begin); j < j_end; j = next_active(j + 1), ++it) {
+    // families K, V: the statistics of the next column tile are fetched one tile ahead (the load's latency
+    // would otherwise stall all element-wise warps at the top of every tile)
+    auto fetch_stats = [&](int j) -> float4 {
+      // (nothing here may look at the loaded value: that would wait for the load on the spot)
+      float4 sv = make_float4(INFINITY, 0.f, 0.f, 0.f);
+      if (FAM != FAM_Q && tid < C::BC && j < j_end && j * C::BC + tid < N)
+        sv = __ldg(&p.stats[static_cast<size_t>(row_base) + j * C::BC + tid]);
+      return sv;
+    };
+    int j_next = next_active(j_begin);
+    float4 sv_next = fetch_stats(j_next);
+    for (int j = j_next; j < j_end; j = j_next, ++it) {
       const uint8_t bits = tile_bits(j);
       const int c0 = j * C::BC;
       const int cw = c0 + 32 * wg;   // first column of this thread
+      j_next = next_active(j + 1);
       if (FAM != FAM_Q) {
         if (tid < C::BC) {
-          float4 sv = make_float4(INFINITY, 0.f, 0.f, 0.f);
-          if (c0 + tid < N) {
-            sv = p.stats[static_cast<size_t>(row_base) + c0 + tid];
-            if (sv.x == -INFINITY) sv.x = INFINITY;
-          }
-          stats_s[it & 1][0][tid] = -sv.x;
+          const float4 sv = sv_next;
+          stats_s[it & 1][0][tid] = (sv.x == -INFINITY) ? -INFINITY : -sv.x;   // fully excluded query: P = 0
           stats_s[it & 1][1][tid] = -sv.y;
           stats_s[it & 1][2][tid] = -sv.z;
           stats_s[it & 1][3][tid] = -sv.w;
         }
         named_bar_sync(1, 256);
+        sv_next = fetch_stats(j_next);
       }
       // pair of negated statistics for columns (2 i, 2 i + 1) of this thread
       auto stat2 = [&](int field, int i) -> float2 {
@@ -462,7 +483,10 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
       const int sb = (FAM == FAM_V) ? (it & 1) : 0;
       const uint32_t T0 = TS0 + sb * 128 + 32 * wg, T1 = T0 + 64;
       if (tr) JVPFA_TR(1 + wg, it, 0);
-      mbar_wait(&st_full[sb], (FAM == FAM_V) ? ((it >> 1) & 1) : (it & 1), w, 30);
+      // family V, dual: P is computed from S as soon as the first score chain is complete, tP follows with tS
+      constexpr bool EARLY_P = (FAM == FAM_V) && DUAL;
+      if constexpr (EARLY_P) mbar_wait(&s_ready[sb], (it >> 1) & 1, w, 34);
+      else mbar_wait(&st_full[sb], (FAM == FAM_V) ? ((it >> 1) & 1) : (it & 1), w, 30);
       tc_fence_after_sync();
       if (tr) JVPFA_TR(1 + wg, it, 1);
       // ---- phase 1: P and ts of this thread's 32 columns (packed fp32x2 arithmetic: the element-wise
@@ -471,7 +495,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
       {
         uint32_t a0[32], a1[32];
         tmem_ld_x32(T0, a0);
-        if constexpr (DUAL) tmem_ld_x32(T1, a1);
+        if constexpr (DUAL && !EARLY_P) tmem_ld_x32(T1, a1);
         tmem_wait_ld();
         if constexpr (FAM != FAM_V) {
           tc_fence_before_sync();
@@ -485,7 +509,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
           x2[i] = __ffma2_rn(make_float2(__uint_as_float(a0[2 * i]), __uint_as_float(a0[2 * i + 1])), c1_2, stat2(0, i));
-          if constexpr (DUAL) ts2[i] = __fmul2_rn(make_float2(__uint_as_float(a1[2 * i]), __uint_as_float(a1[2 * i + 1])), s_2);
+          if constexpr (DUAL && !EARLY_P) ts2[i] = __fmul2_rn(make_float2(__uint_as_float(a1[2 * i]), __uint_as_float(a1[2 * i + 1])), s_2);
         }
         if (need_causal || need_bound || need_mask) {
 #pragma unroll
@@ -519,7 +543,33 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
         for (int i = 0; i < 16; ++i) P2[i] = make_float2(fast_exp2(x2[i].x), fast_exp2(x2[i].y));
       }
       if (tr) JVPFA_TR(1 + wg, it, 3);
-      if constexpr (FAM == FAM_V) {
+      if constexpr (EARLY_P) {
+        // P back into this thread's own columns of the score buffer, then tP = P (ts - mu) once tS is complete
+        {
+          uint32_t e0[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) e0[i] = pack2<BF16>(P2[i].x, P2[i].y);
+          tmem_st_x16(T0, e0);
+        }
+        tmem_wait_st();
+        tc_fence_before_sync();
+        mbar_arrive(&pp_full[sb]);
+        if (tr) JVPFA_TR(1 + wg, it, 7);
+        mbar_wait(&st_full[sb], (it >> 1) & 1, w, 30);
+        tc_fence_after_sync();
+        if (tr) JVPFA_TR(1 + wg, it, 4);
+        uint32_t a1[32];
+        tmem_ld_x32(T1, a1);
+        tmem_wait_ld();
+        uint32_t e1[16];
+#pragma unroll
+        for (int ip = 0; ip < 16; ++ip) {
+          const float2 ts = __fmul2_rn(make_float2(__uint_as_float(a1[2 * ip]), __uint_as_float(a1[2 * ip + 1])), s_2);
+          const float2 tp = __fmul2_rn(P2[ip], __fadd2_rn(ts, stat2(1, ip)));
+          e1[ip] = pack2<BF16>(tp.x, tp.y);
+        }
+        tmem_st_x16(T1, e1);
+      } else if constexpr (FAM == FAM_V) {
         // P and tP = P (ts - mu) back into this thread's own columns of the score buffer
 #pragma unroll
         for (int hch = 0; hch < 2; ++hch) {
