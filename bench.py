@@ -159,8 +159,11 @@ def run_cuda(args, rank, world, local_rank):
 
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
-    if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
-        os.environ["NCCL_DEBUG"] = "WARN"   # keep NCCL's version banner off stdout: rank 0 prints one JSON line
+    # rank 0 prints exactly one JSON line on stdout: NCCL writes its version banner to file descriptor 1 from native
+    # code, so everything else written to it during the run goes to stderr and the line goes to the saved descriptor
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     w = dict(WORKLOAD)
@@ -324,7 +327,8 @@ def run_cuda(args, rank, world, local_rank):
             "roofline": roofline, "kernels": kernels, "cpu_baseline": cpu_baseline, "e2e": e2e,
             "gpu_launches": 5 * args.steps, "clocks": clocks.summary(),
         }
-        print(json.dumps(line), flush=True)
+        sys.stdout.flush()
+        os.write(json_fd, (json.dumps(line) + "\n").encode())
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

@@ -148,8 +148,10 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
-    if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
-        os.environ["NCCL_DEBUG"] = "WARN"
+    # one JSON line on stdout: NCCL prints its version banner to file descriptor 1 from native code
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
@@ -186,14 +188,14 @@ def main():
         _lib.read_status(dev)
     if rank == 0:
         n_params = sum(p.numel() for p in model.parameters())
-        print(json.dumps({
+        os.write(json_fd, (json.dumps({
             "metric": "DiT JVP training step, samples/s", "value": B * world / (ms * 1e-3), "unit": "samples/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
             "scaling": "weak", "dtype": "bf16", "data": "synthetic", "loss": float(loss),
             "config": {"workload": f"DiT depth={args.depth} hidden={args.hidden} heads={args.heads} "
                                    f"(head dim {args.hidden // args.heads}) tokens={N}, torch.func.jvp + MSE on primal and "
                                    "tangent + backward + NCCL all-reduce + AdamW", "attention": args.attention,
-                       "global_batch": B * world, "parameters": n_params}}), flush=True)
+                       "global_batch": B * world, "parameters": n_params}}) + "\n").encode())
     if world > 1:
         torch.distributed.barrier()
         torch.distributed.destroy_process_group()

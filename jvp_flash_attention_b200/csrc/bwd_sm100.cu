@@ -21,8 +21,10 @@
 // the 64 statistics of the current query tile in shared memory and read them as broadcasts.
 //
 // Roles: warps 0-7 element-wise as two warpgroups that split the 64 columns of every score tile
-// (thread = TMEM lane = one score row, 32 columns), warp 8 TMA producer, warp 9 MMA issuer. Column-side tiles flow through a ring of shared-memory slots in the
-// order in which the MMA issuer releases them (tiles only the score MMAs read come first).
+// (thread = TMEM lane = one score row, 32 columns), warp 8 TMA producer, warps 9 and 10 MMA issuers (9: the
+// score products S, tS; 10: the output products and X, A; two instruction streams keep the tensor pipe fed while
+// one of them waits on a barrier). Column-side tiles flow through a ring of shared-memory slots in the order in
+// which the issuers release them (tiles only the score MMAs read come first).
 #include <type_traits>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
