@@ -6,7 +6,9 @@
 //
 // Forward follows the reference's _attn_fwd / _attn_fwd_inner (jvp_flash_attention/jvp_attention.py:
 // 673-1044, 136-347); backward follows _attn_bwd_dkdv / _attn_bwd_dq (:1426-1574, 1578-1718)
-// extended with the tangent-output terms. Head dimension up to 128.
+// extended with the tangent-output terms. Head dimension up to 256 (above 128 the backward streams its column-side
+// tiles in two 128-wide chunks of the head dimension to stay inside shared memory).
+#include <type_traits>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include "host_common.h"
@@ -18,7 +20,8 @@ namespace {
 constexpr int TB = 32;       // tile edge (rows and columns)
 constexpr int PITCH = 33;    // padded pitch of transposed tiles
 constexpr int NTHREADS = 256;
-constexpr int kMaxD = 128;
+constexpr int kMaxD = 256;
+constexpr int kChunkD = 128;   // widest slice of the head dimension the backward keeps of a column-side tile
 
 enum { FAM_Q = 0, FAM_K = 1, FAM_V = 2 };
 
@@ -32,13 +35,18 @@ template <> __device__ __forceinline__ __half from_f<__half>(float x) { return _
 template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
 
 // dst[d * PITCH + r] = src[(row0 + r) * D + d] for r < TB (zero where row0 + r >= N)
+// transposed tile: dst[d - d0][r] = src[row0 + r][d] for d in [d0, d0 + dn)
+template <typename T>
+__device__ __forceinline__ void load_tile_t(float* dst, const T* src, int row0, int N, int D, int d0, int dn) {
+  for (int idx = threadIdx.x; idx < TB * dn; idx += NTHREADS) {
+    const int r = idx / dn, d = idx - r * dn;
+    const int row = row0 + r;
+    dst[d * PITCH + r] = (row < N) ? to_f<T>(src[static_cast<size_t>(row) * D + d0 + d]) : 0.f;
+  }
+}
 template <typename T>
 __device__ __forceinline__ void load_tile_t(float* dst, const T* src, int row0, int N, int D) {
-  for (int idx = threadIdx.x; idx < TB * D; idx += NTHREADS) {
-    const int r = idx / D, d = idx - r * D;
-    const int row = row0 + r;
-    dst[d * PITCH + r] = (row < N) ? to_f<T>(src[static_cast<size_t>(row) * D + d]) : 0.f;
-  }
+  load_tile_t<T>(dst, src, row0, N, D, 0, D);
 }
 
 struct GenParams {
@@ -67,18 +75,19 @@ __device__ __forceinline__ void score_mac(float (&acc)[2][2], const float* At, c
 
 // out block of this thread: rows ty + 16 i, d-columns tx + 16 j (j < D/16 rounded up);
 // acc[i][j] += sum_c E[row][c] * Ct[dcol][c]
-template <int NJ>
+// Ct holds the head-dimension slice [16 J0, 16 (J0 + NJC)) of the tile, D is the full head dimension
+template <int NJ, int J0 = 0, int NJC = NJ>
 __device__ __forceinline__ void out_mac(float (&acc)[2][NJ], const float* E, const float* Ct, int D, int ty, int tx) {
 #pragma unroll 2
   for (int c = 0; c < TB; ++c) {
     const float e0 = E[ty * PITCH + c], e1 = E[(ty + 16) * PITCH + c];
 #pragma unroll
-    for (int j = 0; j < NJ; ++j) {
+    for (int j = 0; j < NJC; ++j) {
       const int dc = tx + 16 * j;
-      if (dc < D) {
+      if (16 * J0 + dc < D) {
         const float v = Ct[dc * PITCH + c];
-        acc[0][j] = fmaf(e0, v, acc[0][j]);
-        acc[1][j] = fmaf(e1, v, acc[1][j]);
+        acc[0][J0 + j] = fmaf(e0, v, acc[0][J0 + j]);
+        acc[1][J0 + j] = fmaf(e1, v, acc[1][J0 + j]);
       }
     }
   }
@@ -260,15 +269,17 @@ generic_bwd_kernel(const T* __restrict__ r0p, const T* __restrict__ r1p, const T
   extern __shared__ float sm[];
   const int D = p.D, N = p.N;
   const int tile = D * PITCH;
+  constexpr bool CHUNKED = NJ > kChunkD / 16;          // head dimension above 128: column-side tiles in two slices
+  const int ctile = (CHUNKED ? kChunkD : D) * PITCH;
   float* R0 = sm;
   float* R1 = R0 + tile;
   float* R2 = R1 + tile;
   float* R3 = R2 + tile;
   float* C0 = R3 + tile;
-  float* C1 = C0 + tile;
-  float* C2 = C1 + tile;
-  float* C3 = C2 + tile;
-  float* E0 = C3 + tile;
+  float* C1 = C0 + ctile;
+  float* C2 = C1 + ctile;
+  float* C3 = C2 + ctile;
+  float* E0 = C3 + ctile;
   float* E1 = E0 + TB * PITCH;
   float4* st_s = reinterpret_cast<float4*>(E1 + TB * PITCH + 3);  // keep 16-byte alignment below
   st_s = reinterpret_cast<float4*>((reinterpret_cast<uintptr_t>(st_s) + 15) & ~uintptr_t(15));
@@ -300,11 +311,15 @@ generic_bwd_kernel(const T* __restrict__ r0p, const T* __restrict__ r1p, const T
     if (p.mv.kind != JVPFA_MASK_NONE) bits = (FAM == FAM_Q) ? tile32_bits(p.mv, b, h, rt, ct) : tile32_bits(p.mv, b, h, ct, rt);
     if (!(bits & kTileAnyKept)) continue;
     const int c0 = ct * TB;
+    // column-side tiles, head-dimension slice [d0, d0 + dn)
+    auto load_c = [&](int d0, int dn) {
+      load_tile_t<T>(C0, c0p + base, c0, N, D, d0, dn);
+      if (dual) load_tile_t<T>(C1, c1p + base, c0, N, D, d0, dn);
+      load_tile_t<T>(C2, c2p + base, c0, N, D, d0, dn);
+      if (dual) load_tile_t<T>(C3, c3p + base, c0, N, D, d0, dn);
+    };
     __syncthreads();
-    load_tile_t<T>(C0, c0p + base, c0, N, D);
-    if (dual) load_tile_t<T>(C1, c1p + base, c0, N, D);
-    load_tile_t<T>(C2, c2p + base, c0, N, D);
-    if (dual) load_tile_t<T>(C3, c3p + base, c0, N, D);
+    load_c(0, CHUNKED ? kChunkD : D);
     // statistics of the query positions of this tile pair
     if (threadIdx.x < TB) {
       const int qpos = (FAM == FAM_Q ? r0 : c0) + threadIdx.x;
@@ -318,18 +333,30 @@ generic_bwd_kernel(const T* __restrict__ r0p, const T* __restrict__ r1p, const T
     __syncthreads();
     float T0[2][2] = {{0.f, 0.f}, {0.f, 0.f}}, T1[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
     float T2[2][2] = {{0.f, 0.f}, {0.f, 0.f}}, T3[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
-    score_mac(T0, R0, C0, D, ty, tx);
-    if (dual) {
-      score_mac(T1, R1, C0, D, ty, tx);
-      score_mac(T1, R0, C1, D, ty, tx);
-    }
-    if (FAM != FAM_V) {
-      score_mac(T2, R2, C2, D, ty, tx);
+    // score products over the head-dimension slice of length dn that starts at row-side offset ro (floats)
+    auto scores = [&](int ro, int dn) {
+      score_mac(T0, R0 + ro, C0, dn, ty, tx);
       if (dual) {
-        score_mac(T2, R3, C3, D, ty, tx);
-        if (FAM == FAM_Q) score_mac(T3, R3, C2, D, ty, tx);
-        else score_mac(T3, R2, C3, D, ty, tx);
+        score_mac(T1, R1 + ro, C0, dn, ty, tx);
+        score_mac(T1, R0 + ro, C1, dn, ty, tx);
       }
+      if (FAM != FAM_V) {
+        score_mac(T2, R2 + ro, C2, dn, ty, tx);
+        if (dual) {
+          score_mac(T2, R3 + ro, C3, dn, ty, tx);
+          if (FAM == FAM_Q) score_mac(T3, R3 + ro, C2, dn, ty, tx);
+          else score_mac(T3, R2 + ro, C3, dn, ty, tx);
+        }
+      }
+    };
+    if constexpr (CHUNKED) {
+      scores(0, kChunkD);
+      __syncthreads();
+      load_c(kChunkD, D - kChunkD);
+      __syncthreads();
+      scores(kChunkD * PITCH, D - kChunkD);
+    } else {
+      scores(0, D);
     }
     const bool use_mask = p.mv.kind != JVPFA_MASK_NONE && (bits & kTileAnyMasked);
 #pragma unroll
@@ -355,18 +382,32 @@ generic_bwd_kernel(const T* __restrict__ r0p, const T* __restrict__ r1p, const T
         E1[rr * PITCH + cc] = v1;
       }
     __syncthreads();
-    if (FAM == FAM_V) {
-      out_mac<NJ>(acc0, E0, C2, D, ty, tx);
-      if (dual) {
-        out_mac<NJ>(acc0, E1, C3, D, ty, tx);
-        out_mac<NJ>(acc1, E0, C3, D, ty, tx);
+    // output products for the head-dimension columns [16 J0, 16 (J0 + NJC)) held in the column-side tiles
+    auto outputs = [&](auto j0, auto njc) {
+      constexpr int J0 = decltype(j0)::value, NJC = decltype(njc)::value;
+      if (FAM == FAM_V) {
+        out_mac<NJ, J0, NJC>(acc0, E0, C2, D, ty, tx);
+        if (dual) {
+          out_mac<NJ, J0, NJC>(acc0, E1, C3, D, ty, tx);
+          out_mac<NJ, J0, NJC>(acc1, E0, C3, D, ty, tx);
+        }
+      } else {
+        out_mac<NJ, J0, NJC>(acc0, E0, C0, D, ty, tx);
+        if (dual) {
+          out_mac<NJ, J0, NJC>(acc0, E1, C1, D, ty, tx);
+          out_mac<NJ, J0, NJC>(acc1, E1, C0, D, ty, tx);
+        }
       }
+    };
+    if constexpr (CHUNKED) {
+      constexpr int JC = kChunkD / 16;
+      outputs(std::integral_constant<int, JC>{}, std::integral_constant<int, NJ - JC>{});   // second slice is loaded
+      __syncthreads();
+      load_c(0, kChunkD);
+      __syncthreads();
+      outputs(std::integral_constant<int, 0>{}, std::integral_constant<int, JC>{});
     } else {
-      out_mac<NJ>(acc0, E0, C0, D, ty, tx);
-      if (dual) {
-        out_mac<NJ>(acc0, E1, C1, D, ty, tx);
-        out_mac<NJ>(acc1, E1, C0, D, ty, tx);
-      }
+      outputs(std::integral_constant<int, 0>{}, std::integral_constant<int, NJ>{});
     }
   }
 #pragma unroll
@@ -419,7 +460,8 @@ template <typename T>
 int fwd_by_d(const jvpfa_fwd_args& a, cudaStream_t stream) {
   if (a.D <= 32) return fwd_typed<T, 2>(a, stream);
   if (a.D <= 64) return fwd_typed<T, 4>(a, stream);
-  return fwd_typed<T, 8>(a, stream);
+  if (a.D <= 128) return fwd_typed<T, 8>(a, stream);
+  return fwd_typed<T, 16>(a, stream);
 }
 
 template <typename T, int NJ, int FAM>
@@ -443,7 +485,8 @@ int bwd_family(const jvpfa_bwd_args& a, const float4* stats, cudaStream_t stream
     c[0] = cp(a.q); c[1] = cp(a.tq); c[2] = cp(a.go); c[3] = cp(a.gto);
     o0 = static_cast<T*>(a.dv); o1 = static_cast<T*>(a.dtv); p.out_scale = 1.f;
   }
-  const size_t smem = (8 * static_cast<size_t>(a.D) * PITCH + 2 * TB * PITCH + 8) * sizeof(float) + TB * sizeof(float4) + 16;
+  const size_t cD = a.D > kChunkD ? kChunkD : a.D;   // column-side tiles hold at most 128 head-dimension columns
+  const size_t smem = (4 * (static_cast<size_t>(a.D) + cD) * PITCH + 2 * TB * PITCH + 8) * sizeof(float) + TB * sizeof(float4) + 16;
   auto kern = generic_bwd_kernel<T, NJ, FAM>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
     return JVPFA_ERR_LAUNCH;
@@ -476,7 +519,8 @@ template <typename T>
 int bwd_by_d(const jvpfa_bwd_args& a, cudaStream_t stream) {
   if (a.D <= 32) return bwd_typed<T, 2>(a, stream);
   if (a.D <= 64) return bwd_typed<T, 4>(a, stream);
-  return bwd_typed<T, 8>(a, stream);
+  if (a.D <= 128) return bwd_typed<T, 8>(a, stream);
+  return bwd_typed<T, 16>(a, stream);
 }
 
 }  // namespace

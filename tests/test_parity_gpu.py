@@ -156,6 +156,9 @@ def test_golden_reference_interpreter(dev, case):
     (torch.bfloat16, 1, 2, 256, 32, False),    # head dims off the tensor-core path
     (torch.float16, 1, 2, 64, 16, True),
     (torch.bfloat16, 1, 1, 256, 72, False),
+    (torch.float16, 1, 2, 96, 256, True),      # the reference's largest head dimension (CUDA-core kernels)
+    (torch.float32, 1, 2, 80, 256, False),
+    (torch.bfloat16, 1, 1, 64, 160, False),
 ])
 def test_shapes(dev, dtype, B, H, N, D, causal):
     # bf16 keeps 8 bits of mantissa: a gradient of magnitude >= 8 cannot be stored to within 2e-2, and short
