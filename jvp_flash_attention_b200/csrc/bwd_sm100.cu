@@ -276,8 +276,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
     // ------------------------------------------------------------------ MMA issuers: warp 9 the score products S, tS;
     // warp 10 the output products and X, A (two instruction streams keep the tensor pipe fed while one of them waits)
     {
-      // all lanes run the loop so that addresses and descriptors stay warp-uniform; lane 0 issues
-      const bool leader = lane == 0;
+      // all lanes run the loop so that addresses and descriptors stay warp-uniform; the elected lane issues
+      const bool leader = elect_one_sync();
       auto wait_all = [&](uint64_t* bar, uint32_t parity, int site) {
         mbar_wait(bar, parity, w, site);
         __syncwarp();

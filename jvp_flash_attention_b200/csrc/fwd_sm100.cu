@@ -221,8 +221,13 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     __syncwarp();
   } else if (warp >= 9) {
     // ------------------------------------------------------------------ MMA issuers: warp 9 scores, warp 10 outputs
-    const bool leader = lane == 0;
-    if (leader) {
+    // all lanes run the loops (waits included) so that the warp stays converged; the elected lane issues
+    const bool leader = elect_one_sync();
+    auto wait_all = [&](uint64_t* bar, uint32_t parity, int site) {
+      mbar_wait(bar, parity, w, site);
+      __syncwarp();
+    };
+    {
     constexpr uint32_t FMT = BF16 ? FMT_BF16 : FMT_F16;
     const uint32_t idesc_64 = make_idesc(FMT, 128, 64, 0, 0);
     const uint32_t idesc_128 = make_idesc(FMT, 128, 128, 0, 0);
@@ -236,8 +241,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const uint32_t ph = (it / ST) & 1;
       const uint32_t S_t = tmem + C::TMEM_S + (it & 1) * 128;
       if (leader) JVPFA_FTR(0, it, 0);
-      mbar_wait(&k_full[st], ph, w, 20);
-      if (it >= 2) mbar_wait(&s_free[it & 1], ((it >> 1) - 1) & 1, w, 24);
+      wait_all(&k_full[st], ph, 20);
+      if (it >= 2) wait_all(&s_free[it & 1], ((it >> 1) - 1) & 1, 24);
       tc_fence_after_sync();
       if (leader) JVPFA_FTR(0, it, 1);
       const uint64_t dK = desc_kmajor_sw128(smem_u32(sK(st)));
@@ -265,9 +270,9 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const uint32_t P_t = tmem + C::TMEM_S + (it & 1) * 128;
       const uint32_t W_t = P_t + 64;
       if (leader) JVPFA_FTR(0, it, 3);
-      mbar_wait(&p_full[it & 1], (it >> 1) & 1, w, 21);
+      wait_all(&p_full[it & 1], (it >> 1) & 1, 21);
       if (leader) JVPFA_FTR(0, it, 4);
-      mbar_wait(&v_full[st], ph, w, 22);
+      wait_all(&v_full[st], ph, 22);
       tc_fence_after_sync();
       if (leader) JVPFA_FTR(0, it, 5);
       const uint64_t dV0 = desc_mnmajor_sw128(smem_u32(sV(st)), C::BN * 128);
@@ -294,7 +299,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
     int it = 0;
     if (warp == 9) {
-      mbar_wait(&q_full, 0, w, 23);
+      wait_all(&q_full, 0, 23);
       for (int j = 0; j < n_kt; ++j) {
         if (!(tile_bits(j) & kTileAnyKept)) continue;
         issue_qk(it);

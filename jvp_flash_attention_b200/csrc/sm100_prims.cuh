@@ -184,6 +184,21 @@ __host__ __device__ __forceinline__ uint32_t make_idesc(uint32_t ab_fmt, uint32_
   return d;
 }
 
+// One lane of the (converged) warp. The lane that issues tcgen05.mma has to be chosen this way: with the
+// predicate of elect.sync the compiler keeps descriptors and addresses in uniform registers and one thread issues an
+// instruction every 10-12 cycles; behind `lane == 0` the same code needs 45-48 cycles per instruction (measured with
+// N = 16 instructions that leave the tensor pipe idle), which is slower than the pipe executes N <= 64 shapes and
+// leaves no slack for N = 128.
+__device__ __forceinline__ bool elect_one_sync() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "elect.sync _|P, 0xFFFFFFFF;\n\t"
+      "selp.b32 %0, 1, 0, P;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
 // ---------------------------------------------------------------------------------------------
 // MMA issue (one thread), commit to an mbarrier
 // ---------------------------------------------------------------------------------------------
