@@ -278,6 +278,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
     {
       // all lanes run the loop so that addresses and descriptors stay warp-uniform; the elected lane issues
       const bool leader = elect_one_sync();
+      const uint32_t lead = leader ? 1u : 0u;
       auto wait_all = [&](uint64_t* bar, uint32_t parity, int site) {
         mbar_wait(bar, parity, w, site);
         __syncwarp();
@@ -294,23 +295,19 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
       auto mma_nt = [&](uint32_t dst, const uint8_t* rtile, const uint8_t* ctile, uint32_t idesc, uint32_t acc) {
         // descriptors of the later K steps differ from the first only in the 16-byte-unit start address
         const uint64_t da = desc_kmajor_sw128(smem_u32(rtile)), db = desc_kmajor_sw128(smem_u32(ctile));
-        if (leader) {
 #pragma unroll
-          for (int k = 0; k < D / 16; ++k) {
-            const uint64_t o = static_cast<uint64_t>(((k >> 2) * C::SLAB + (k & 3) * 32) >> 4);
-            if (!PAD || k < ksteps) umma_ss(dst, da + o, db + o, idesc, acc | (k > 0));
-          }
+        for (int k = 0; k < D / 16; ++k) {
+          const uint64_t o = static_cast<uint64_t>(((k >> 2) * C::SLAB + (k & 3) * 32) >> 4);
+          if (!PAD || k < ksteps) umma_ss_pred(dst, da + o, db + o, idesc, acc | (k > 0), lead);
         }
       };
       // acc[128 x D] (+)= E[128 x 64] (TMEM, 16-bit, two column groups of 16) * Cc[64 x D]
       auto mma_out = [&](uint32_t accum, uint32_t e, const uint8_t* ctile, uint32_t acc) {
         const uint64_t db = desc_mnmajor_sw128(smem_u32(ctile), C::SLAB);
-        if (leader) {
 #pragma unroll
-          for (int k = 0; k < C::BC / 16; ++k)
-            umma_ts(accum, e + (k & 1) * 8 + (k >> 1) * 32, db + static_cast<uint64_t>((k * 2048) >> 4), idesc_out,
-                    acc | (k > 0));
-        }
+        for (int k = 0; k < C::BC / 16; ++k)
+          umma_ts_pred(accum, e + (k & 1) * 8 + (k >> 1) * 32, db + static_cast<uint64_t>((k * 2048) >> 4), idesc_out,
+                       acc | (k > 0), lead);
       };
       // S, tS of tile i into score buffer sb
       auto issue_st = [&](int i, int sb) {

@@ -235,9 +235,9 @@ def test_error_behaviour_on_gpu(dev):
     with pytest.raises(AssertionError):
         attention(q, q, q, attn_mask=m[:, :, :32])              # wrong shape
     from jvp_flash_attention_b200 import _lib
-    big = torch.randn(1, 1, 64, 256, device=dev, dtype=torch.bfloat16)
+    big = torch.randn(1, 1, 64, 512, device=dev, dtype=torch.bfloat16)
     with pytest.raises(_lib.JvpfaError):
-        attention(big, big, big)                                 # head dim 256: no kernel
+        attention(big, big, big)                                 # head dim 512: no kernel (256 is the largest)
 
 
 # ------------------------------------------------------------------ size-independent properties at full size
