@@ -2,12 +2,13 @@
 // pass, with tcgen05 MMAs accumulating in TMEM and K/tK/V/tV tiles staged by TMA.
 //
 // Replaces the reference's _attn_fwd_tma / _attn_fwd_inner_tma (jvp_flash_attention/jvp_attention.py:
-// 1100-1392, 350-559). Per (128-row query tile, batch*head) one CTA of 11 warps:
+// 1100-1392, 350-559). Per (128-row query tile, batch*head) one CTA of 12 warps:
 //   warps 0-7  two softmax warpgroups that split the 64 columns of every score tile: thread r of a
 //              warpgroup owns score row r (TMEM lane r) and 32 columns; keeps m, l, mu in registers, turns the
 //              score tile S and tangent-score tile tS into 16-bit P and W = P o (s tS) written back to TMEM;
 //              the two halves of a row exchange their maxima (and, at the end, their sums) through shared memory
-//   warp 8     TMA producer (one lane)
+//   warp 8     TMA producer of Q, tQ and the stacked [K; tK] pairs (one lane)
+//   warp 11    TMA producer of the V, tV tiles (one lane)
 //   warp 9     issues the score products (lane 0); owns the TMEM allocation
 //   warp 10    issues the output products (lane 0). tcgen05.mma issue blocks once three to four instructions are
 //              queued, so one issuing thread idles the tensor pipe during each of its barrier waits and commits;
@@ -95,12 +96,12 @@ struct FwdCfg {
 
 // Warps 0-7: two softmax warpgroups that split the 64 columns of every score tile (thread = TMEM lane =
 // one score row, 32 columns; the row maximum and the final row sums are exchanged through shared
-// memory); warp 8: TMA producer (one lane); warps 9, 10: MMA issuers (one lane each: scores / outputs), warp 9 owns the
+// memory); warps 8, 11: TMA producers (one lane each: Q and K pairs / V tiles); warps 9, 10: MMA issuers (one lane each: scores / outputs), warp 9 owns the
 // TMEM allocation.
 // PAD: the tensors' head dimension is smaller than D (columns beyond it are zero-filled by TMA); the K steps and
 // output columns that would only see zeros are then skipped at run time.
 template <int D, bool DUAL, bool BF16, bool PAD>
-__global__ void __launch_bounds__(352, 1)
+__global__ void __launch_bounds__(384, 1)
 fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmTQ,
                  const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmTK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmTV,
@@ -183,8 +184,29 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     return bits;
   };
 
-  if (warp == 8) {
-    // ------------------------------------------------------------------ TMA producer
+  if (warp == 11) {
+    // ------------------------------------------------------------------ TMA producer of the V, tV tiles (a warp of
+    // its own: V slots free up a tile later than K slots, one producer waiting for them would hold the K loads back)
+    if (lane == 0) {
+      int it = 0;
+      for (int j = 0; j < n_kt; ++j) {
+        if (!(tile_bits(j) & kTileAnyKept)) continue;
+        const int st = it % ST;
+        const uint32_t ph = (it / ST) & 1;
+        const int krow = row_base + j * C::BN;
+        mbar_wait(&v_empty[st], ph ^ 1, w, 11);
+        mbar_arrive_expect_tx(&v_full[st], (DUAL ? 2 : 1) * C::TILE_V);
+#pragma unroll
+        for (int sl = 0; sl < SLABS; ++sl) {
+          tma_load_2d(sV(st) + sl * C::HALF, &tmV, &v_full[st], 64 * sl, krow);
+          if constexpr (DUAL) tma_load_2d(sTV(st) + sl * C::HALF, &tmTV, &v_full[st], 64 * sl, krow);
+        }
+        ++it;
+      }
+    }
+    __syncwarp();
+  } else if (warp == 8) {
+    // ------------------------------------------------------------------ TMA producer of Q, tQ and the [K; tK] pairs
     if (lane == 0) {
       tma_prefetch_desc(&tmQ);
       tma_prefetch_desc(&tmK);
@@ -207,13 +229,6 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (int sl = 0; sl < SLABS; ++sl) {
           tma_load_2d(sK(st) + sl * C::SLAB, &tmK, &k_full[st], 64 * sl, krow);
           if constexpr (DUAL) tma_load_2d(sK(st) + sl * C::SLAB + C::HALF, &tmTK, &k_full[st], 64 * sl, krow);
-        }
-        mbar_wait(&v_empty[st], ph ^ 1, w, 11);
-        mbar_arrive_expect_tx(&v_full[st], (DUAL ? 2 : 1) * C::TILE_V);
-#pragma unroll
-        for (int sl = 0; sl < SLABS; ++sl) {
-          tma_load_2d(sV(st) + sl * C::HALF, &tmV, &v_full[st], 64 * sl, krow);
-          if constexpr (DUAL) tma_load_2d(sTV(st) + sl * C::HALF, &tmTV, &v_full[st], 64 * sl, krow);
         }
         ++it;
       }
@@ -538,7 +553,7 @@ int launch_one(const jvpfa_fwd_args& a, cudaStream_t stream) {
     return JVPFA_ERR_LAUNCH;
   dim3 grid((a.N + C::BM - 1) / C::BM, a.B * a.H);
   ScopedKernelTimer timer(KERNEL_FWD, stream);
-  kern<<<grid, 352, smem, stream>>>(mQ, mTQ, mK, mTK, mV, mTV, p);
+  kern<<<grid, 384, smem, stream>>>(mQ, mTQ, mK, mTK, mV, mTV, p);
   return cudaGetLastError() == cudaSuccess ? JVPFA_OK : JVPFA_ERR_LAUNCH;
 }
 
