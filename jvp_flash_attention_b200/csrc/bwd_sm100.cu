@@ -704,43 +704,51 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
 }
 
 // stats[row] = (lse2, mu, Delta, a) with a = rowsum(gtO o O), Delta = rowsum(gO o O) + rowsum(gtO o tO) - a mu.
-// One warp per row; 16-bit inputs. Generalises the reference's _attn_bwd_preprocess
+// Half a warp per row; 16-bit inputs. Generalises the reference's _attn_bwd_preprocess
 // (jvp_attention.py:1395-1422), which computes rowsum(O o dO) only.
 template <bool BF16>
 __global__ void bwd_preprocess_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict__ to,
                                       const uint16_t* __restrict__ go, const uint16_t* __restrict__ gto,
                                       const float* __restrict__ lse2, const float* __restrict__ mu,
                                       float4* __restrict__ stats, int64_t rows, int D) {
-  const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (row >= rows) return;
-  auto cvt = [](uint16_t x) -> float {
-    if constexpr (BF16) return __uint_as_float(static_cast<uint32_t>(x) << 16);
-    else return __half2float(__ushort_as_half(x));
+  // half a warp per row, 16 bytes per lane and tensor in flight
+  const int lane = threadIdx.x & 31, l16 = lane & 15;
+  const int64_t row = (static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5)) * 2 + (lane >> 4);
+  const bool live = row < rows;
+  auto lo = [](uint32_t x) -> float {
+    if constexpr (BF16) return __uint_as_float(x << 16);
+    else return __half2float(__ushort_as_half(static_cast<uint16_t>(x & 0xFFFFu)));
+  };
+  auto hi = [](uint32_t x) -> float {
+    if constexpr (BF16) return __uint_as_float(x & 0xFFFF0000u);
+    else return __half2float(__ushort_as_half(static_cast<uint16_t>(x >> 16)));
   };
   float s_go_o = 0.f, s_gto_to = 0.f, s_gto_o = 0.f;
-  for (int d = lane * 2; d < D; d += 64) {
-    const size_t idx = static_cast<size_t>(row) * D + d;
-    const uint32_t ov = *reinterpret_cast<const uint32_t*>(o + idx);
-    const uint32_t tov = gto ? *reinterpret_cast<const uint32_t*>(to + idx) : 0u;
-    const uint32_t gov = *reinterpret_cast<const uint32_t*>(go + idx);
-    const uint32_t gtov = gto ? *reinterpret_cast<const uint32_t*>(gto + idx) : 0u;
+  if (live) {
+    for (int d = l16 * 8; d < D; d += 128) {
+      const size_t idx = static_cast<size_t>(row) * D + d;
+      const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+      const uint4 ov = *reinterpret_cast<const uint4*>(o + idx);
+      const uint4 gov = *reinterpret_cast<const uint4*>(go + idx);
+      const uint4 tov = gto ? *reinterpret_cast<const uint4*>(to + idx) : z;
+      const uint4 gtov = gto ? *reinterpret_cast<const uint4*>(gto + idx) : z;
+      const uint32_t a0[4] = {ov.x, ov.y, ov.z, ov.w}, a1[4] = {tov.x, tov.y, tov.z, tov.w};
+      const uint32_t a2[4] = {gov.x, gov.y, gov.z, gov.w}, a3[4] = {gtov.x, gtov.y, gtov.z, gtov.w};
 #pragma unroll
-    for (int u = 0; u < 2; ++u) {
-      const float fo = cvt(static_cast<uint16_t>(ov >> (16 * u))), fto = cvt(static_cast<uint16_t>(tov >> (16 * u)));
-      const float fgo = cvt(static_cast<uint16_t>(gov >> (16 * u))), fgto = cvt(static_cast<uint16_t>(gtov >> (16 * u)));
-      s_go_o = fmaf(fgo, fo, s_go_o);
-      s_gto_to = fmaf(fgto, fto, s_gto_to);
-      s_gto_o = fmaf(fgto, fo, s_gto_o);
+      for (int u = 0; u < 4; ++u) {
+        s_go_o = fmaf(lo(a2[u]), lo(a0[u]), s_go_o);     s_go_o = fmaf(hi(a2[u]), hi(a0[u]), s_go_o);
+        s_gto_to = fmaf(lo(a3[u]), lo(a1[u]), s_gto_to); s_gto_to = fmaf(hi(a3[u]), hi(a1[u]), s_gto_to);
+        s_gto_o = fmaf(lo(a3[u]), lo(a0[u]), s_gto_o);   s_gto_o = fmaf(hi(a3[u]), hi(a0[u]), s_gto_o);
+      }
     }
   }
 #pragma unroll
-  for (int off = 16; off > 0; off >>= 1) {
+  for (int off = 8; off > 0; off >>= 1) {
     s_go_o += __shfl_xor_sync(0xFFFFFFFFu, s_go_o, off);
     s_gto_to += __shfl_xor_sync(0xFFFFFFFFu, s_gto_to, off);
     s_gto_o += __shfl_xor_sync(0xFFFFFFFFu, s_gto_o, off);
   }
-  if (lane == 0) {
+  if (l16 == 0 && live) {
     const float m = mu[row];
     stats[row] = make_float4(lse2[row], m, s_go_o + s_gto_to - s_gto_o * m, s_gto_o);
   }
@@ -804,8 +812,8 @@ template <int D, bool BF16>
 int launch_all(const jvpfa_bwd_args& a, cudaStream_t stream) {
   const int64_t rows = static_cast<int64_t>(a.B) * a.H * a.N;
   float4* stats = reinterpret_cast<float4*>(static_cast<uint8_t*>(a.workspace) + kStatusBytes);
-  const int warps_per_block = 8;
-  const unsigned blocks = static_cast<unsigned>((rows + warps_per_block - 1) / warps_per_block);
+  const int warps_per_block = 8;   // two rows per warp
+  const unsigned blocks = static_cast<unsigned>((rows + 2 * warps_per_block - 1) / (2 * warps_per_block));
   {
   ScopedKernelTimer timer(KERNEL_BWD_PREPROCESS, stream);
   bwd_preprocess_kernel<BF16><<<blocks, warps_per_block * 32, 0, stream>>>(
