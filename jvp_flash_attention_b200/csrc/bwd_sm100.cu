@@ -209,10 +209,12 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
     tmem_alloc(&tmem_base_s, C::TMEM_COLS);
     tmem_relinquish();
   }
+  // the TMA producers need the barriers but not the TMEM address: they start loading while TMEM is being allocated
+  const bool producer = (warp == 8);
   tc_fence_before_sync();
-  __syncthreads();
+  if (!producer) named_bar_sync(2, 320);
   tc_fence_after_sync();
-  const uint32_t tmem = tmem_base_s;
+  const uint32_t tmem = producer ? 0u : tmem_base_s;
 
   // summary bits of column tile j against this row tile (64x64 summary entries are indexed [q][k])
   auto tile_bits = [&](int j) -> uint8_t {

@@ -171,10 +171,12 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     tmem_alloc(&tmem_base_s, C::TMEM_COLS);
     tmem_relinquish();
   }
+  // the TMA producers need the barriers but not the TMEM address: they start loading while TMEM is being allocated
+  const bool producer = (warp == 8 || warp == 11);
   tc_fence_before_sync();
-  __syncthreads();
+  if (!producer) named_bar_sync(2, 320);
   tc_fence_after_sync();
-  const uint32_t tmem = tmem_base_s;
+  const uint32_t tmem = producer ? 0u : tmem_base_s;
 
   // Key tile j takes part unless the mask summary says that nothing in it is kept.
   auto tile_bits = [&](int j) -> uint8_t {
