@@ -198,10 +198,16 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const int krow = row_base + j * C::BN;
         mbar_wait(&v_empty[st], ph ^ 1, w, 11);
         mbar_arrive_expect_tx(&v_full[st], (DUAL ? 2 : 1) * C::TILE_V);
+        if constexpr (!PAD && SLABS > 1) {
+          // the slabs of a V tile are consecutive in shared memory: one box per tensor through the 3-D map
+          tma_load_3d(sV(st), &tmV, &v_full[st], 0, krow, 0);
+          if constexpr (DUAL) tma_load_3d(sTV(st), &tmTV, &v_full[st], 0, krow, 0);
+        } else {
 #pragma unroll
-        for (int sl = 0; sl < SLABS; ++sl) {
-          tma_load_2d(sV(st) + sl * C::HALF, &tmV, &v_full[st], 64 * sl, krow);
-          if constexpr (DUAL) tma_load_2d(sTV(st) + sl * C::HALF, &tmTV, &v_full[st], 64 * sl, krow);
+          for (int sl = 0; sl < SLABS; ++sl) {
+            tma_load_2d(sV(st) + sl * C::HALF, &tmV, &v_full[st], 64 * sl, krow);
+            if constexpr (DUAL) tma_load_2d(sTV(st) + sl * C::HALF, &tmTV, &v_full[st], 64 * sl, krow);
+          }
         }
         ++it;
       }
@@ -528,10 +534,10 @@ int launch_one(const jvpfa_fwd_args& a, cudaStream_t stream) {
   const uint64_t rows = static_cast<uint64_t>(a.B) * a.H * a.N;
   CUtensorMap mQ, mTQ, mK, mTK, mV, mTV;
   bool ok = make_tile_map(&mQ, a.q, rows, a.D, C::BM, a.dtype) && make_tile_map(&mK, a.k, rows, a.D, C::BN, a.dtype) &&
-            make_tile_map(&mV, a.v, rows, a.D, C::BN, a.dtype);
+            ((!PAD && D > 64) ? make_slab_map(&mV, a.v, rows, a.D, C::BN, a.dtype) : make_tile_map(&mV, a.v, rows, a.D, C::BN, a.dtype));
   if (DUAL) {
     ok = ok && make_tile_map(&mTQ, a.tq, rows, a.D, C::BM, a.dtype) && make_tile_map(&mTK, a.tk, rows, a.D, C::BN, a.dtype) &&
-         make_tile_map(&mTV, a.tv, rows, a.D, C::BN, a.dtype);
+         ((!PAD && D > 64) ? make_slab_map(&mTV, a.tv, rows, a.D, C::BN, a.dtype) : make_tile_map(&mTV, a.tv, rows, a.D, C::BN, a.dtype));
   } else {
     mTQ = mQ; mTK = mK; mTV = mV;
   }

@@ -36,6 +36,19 @@ bool make_tile_map(CUtensorMap* out, const void* base, uint64_t rows, int D, int
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+bool make_slab_map(CUtensorMap* out, const void* base, uint64_t rows, int D, int box_rows, int dtype) {
+  TensorMapEncodeFn enc = tensor_map_encoder();
+  if (enc == nullptr || base == nullptr || D % 64 != 0) return false;
+  const cuuint64_t dims[3] = {64, rows, static_cast<cuuint64_t>(D / 64)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(D) * 2, 128};
+  const cuuint32_t box[3] = {64, static_cast<cuuint32_t>(box_rows), static_cast<cuuint32_t>(D / 64)};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUtensorMapDataType dt = dtype == JVPFA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  return enc(out, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 uint64_t wait_budget_ns() {
   static uint64_t ns = [] {
     const char* e = std::getenv("JVPFA_WAIT_BUDGET_MS");
