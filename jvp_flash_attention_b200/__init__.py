@@ -3,6 +3,6 @@
 ``from jvp_flash_attention_b200.jvp_attention import JVPAttn, attention`` replaces
 ``from jvp_flash_attention.jvp_attention import JVPAttn, attention``.
 """
-from .jvp_attention import MASK_CONST, MIN_SEQUENCE_LENGTH, JVPAttn, attention  # noqa: F401
+from .jvp_attention import MASK_CONST, MIN_SEQUENCE_LENGTH, JVPAttn, attention, check  # noqa: F401
 
-__all__ = ["JVPAttn", "attention", "MASK_CONST", "MIN_SEQUENCE_LENGTH"]
+__all__ = ["JVPAttn", "attention", "check", "MASK_CONST", "MIN_SEQUENCE_LENGTH"]

@@ -156,28 +156,72 @@ def stream_ptr(device) -> C.c_void_p:
     return C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
 
 
-# Per-device workspace (status word + scratch), grown on demand. Reusing one buffer per device keeps
-# the status word at a stable address; kernels of consecutive calls on one stream are ordered.
+# Workspaces (status word + scratch), one per (device, stream), grown on demand. Kernels of calls that share a
+# workspace must be ordered on one stream (the backward's per-row statistics live in it between its preprocess and
+# family kernels), so every stream gets its own. A buffer that is outgrown is kept alive until the process ends:
+# kernels already enqueued may still use it.
+class _Workspace:
+    def __init__(self, device, nbytes: int):
+        self.buf = torch.zeros(nbytes, dtype=torch.uint8, device=device)
+        self.word = self.buf[:4].view(torch.int32)                       # device status word
+        self.host = torch.zeros(1, dtype=torch.int32).pin_memory()       # its last copy on the host
+        self.retired: list = []
+
+
 _workspaces: dict = {}
 
 
+def _ws_key(device):
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    return index, torch.cuda.current_stream(index).cuda_stream
+
+
+def _raise_timeout(ws: _Workspace, device) -> None:
+    """Error path: waits for the stream, reads and clears the status word, raises."""
+    torch.cuda.current_stream(device).synchronize()
+    detail = int(ws.word.cpu().item())
+    ws.word.zero_()
+    ws.host.zero_()
+    torch.cuda.current_stream(device).synchronize()
+    raise JvpfaError(ERR_DEVICE_TIMEOUT, lib().jvpfa_error_string(ERR_DEVICE_TIMEOUT).decode() + f" (wait id {detail})")
+
+
 def workspace(device, nbytes: int) -> torch.Tensor:
-    key = (device.index if device.index is not None else torch.cuda.current_device())
+    """Workspace of the current stream of ``device`` with at least ``nbytes`` bytes. Before handing it out, looks at
+    the host copy of the status word that the previous call on this stream left (no synchronisation): a device-side
+    wait that gave up in an earlier call raises here."""
+    key = _ws_key(device)
     ws = _workspaces.get(key)
-    if ws is None or ws.numel() < nbytes:
-        ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
-        _workspaces[key] = ws
-    return ws
+    if ws is not None and int(ws.host[0]) != 0:
+        _raise_timeout(ws, device)
+    if ws is None or ws.buf.numel() < nbytes:
+        new = _Workspace(device, max(nbytes, 1 << 20))
+        if ws is not None:
+            new.retired = ws.retired + [ws.buf]
+        _workspaces[key] = ws = new
+    return ws.buf
+
+
+def post_launch(device) -> None:
+    """Enqueues a copy of the status word to pinned host memory behind the kernels just launched."""
+    ws = _workspaces.get(_ws_key(device))
+    if ws is not None:
+        ws.host.copy_(ws.word, non_blocking=True)
 
 
 def read_status(device=None) -> None:
-    """Synchronises the current stream and raises if a device-side wait gave up since the last read."""
+    """Synchronises the device and raises if a device-side wait gave up, on any stream, since the last read."""
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
-    ws = workspace(device, 256)
-    detail = C.c_int32(0)
-    rc = lib().jvpfa_read_status(C.c_void_p(ws.data_ptr()), stream_ptr(device), C.byref(detail))
-    if rc != OK:
-        raise JvpfaError(rc, lib().jvpfa_error_string(rc).decode() + f" (wait id {detail.value})")
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    torch.cuda.synchronize(index)
+    for (dev_i, _), ws in list(_workspaces.items()):
+        if dev_i != index:
+            continue
+        detail = C.c_int32(0)
+        rc = lib().jvpfa_read_status(C.c_void_p(ws.buf.data_ptr()), stream_ptr(device), C.byref(detail))
+        ws.host.zero_()
+        if rc != OK:
+            raise JvpfaError(rc, lib().jvpfa_error_string(rc).decode() + f" (wait id {detail.value})")
 
 
 def mask_summary(mask_c: Mask, mask_tensor, B, H, N):
@@ -213,6 +257,7 @@ def fwd(q, k, v, tq, tk, tv, mask_c: Mask, summary, causal: bool, sm_scale: floa
     ws = workspace(q.device, need)
     a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
     check(lib().jvpfa_fwd(C.byref(a), stream_ptr(q.device)))
+    post_launch(q.device)
     return o, to, lse2, mu
 
 
@@ -240,6 +285,7 @@ def bwd(q, k, v, tq, tk, tv, o, to, lse2, mu, go, gto, mask_c: Mask, summary, ca
     ws = workspace(q.device, need)
     a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
     check(lib().jvpfa_bwd(C.byref(a), stream_ptr(q.device)))
+    post_launch(q.device)
     return tuple(outs)
 
 

@@ -50,6 +50,19 @@ __device__ long long g_bwd_trace[3 * 3 * 64 * 8];  // [family][role][tile][stamp
 #else
 #define JVPFA_TR(role, it, k) do { } while (0)
 #endif
+// Optional per-CTA phase stamps (compile with -DJVPFA_CTA_TRACE): [family][cta][0..7] = clock64 at phase k,
+// [8] = smid, [9] = globaltimer at entry, [10] = column tiles of the CTA.
+#ifdef JVPFA_CTA_TRACE
+#define JVPFA_CTA_MAX 8192
+__device__ long long g_bwd_cta[3 * JVPFA_CTA_MAX * 12];
+#define JVPFA_CS(k)                                                                                   \
+  do {                                                                                                \
+    const int cta_ = blockIdx.y * gridDim.x + blockIdx.x;                                             \
+    if (cta_ < JVPFA_CTA_MAX) g_bwd_cta[(FAM * JVPFA_CTA_MAX + cta_) * 12 + (k)] = clock64();         \
+  } while (0)
+#else
+#define JVPFA_CS(k) do { } while (0)
+#endif
 
 struct BwdKParams {
   int H, N;
@@ -149,11 +162,12 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
   uint64_t* a_empty = a_full + NA;
   uint64_t* b_full = a_empty + NA;
   uint64_t* b_empty = b_full + NB;
-  uint64_t* e_free = b_empty + NB;   // [2] family V: the output products that read score buffer b have completed
+  uint64_t* e_free = b_empty + NB;   // [2] family V: the output products that read P, tP buffer b have completed
   uint64_t& a_ready = e_free[2];     // families Q, K: A of the current tile is complete (X still accumulating)
   uint64_t& pt_full = e_free[3];     // families Q, K: dtS of the current tile is in TMEM
-  uint64_t* s_ready = e_free + 4;    // [2] family V: S of score buffer b is complete (tS still accumulating)
-  uint64_t* pp_full = e_free + 6;    // [2] family V: P of score buffer b is in TMEM
+  uint64_t& sc_free = e_free[5];     // family V: all 256 element-wise threads hold S, tS in registers, the next tile's
+                                     // score products may overwrite them
+  uint64_t* pp_full = e_free + 6;    // [2] family V: P of buffer b is in TMEM
   uint32_t& tmem_base_s = *reinterpret_cast<uint32_t*>(bars + C::NBAR);
   int& poisoned = *reinterpret_cast<int*>(bars + C::NBAR + 1);
   if ((smem_u32(smem) & 1023u) != 0u) {  // the swizzled layouts need this; never observed otherwise
@@ -162,6 +176,18 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
   }
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+#ifdef JVPFA_CTA_TRACE
+  if (tid == 0) {
+    JVPFA_CS(0);
+    const int cta_ = blockIdx.y * gridDim.x + blockIdx.x;
+    if (cta_ < JVPFA_CTA_MAX) {
+      uint32_t smid_;
+      asm volatile("mov.u32 %0, %%smid;" : "=r"(smid_));
+      g_bwd_cta[(FAM * JVPFA_CTA_MAX + cta_) * 12 + 8] = smid_;
+      g_bwd_cta[(FAM * JVPFA_CTA_MAX + cta_) * 12 + 9] = static_cast<long long>(global_timer_ns());
+    }
+  }
+#endif
   const int n_rt = gridDim.x;
   // heavier tiles first under a causal mask: late query tiles, early key tiles
   const int rt = (p.causal && FAM == FAM_Q) ? (n_rt - 1 - static_cast<int>(blockIdx.x)) : blockIdx.x;
@@ -186,10 +212,10 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
       mbar_init(&st_full[i], 1);
       mbar_init(&p_full[i], 256);
       mbar_init(&e_free[i], 1);
-      mbar_init(&s_ready[i], 1);
       mbar_init(&pp_full[i], 256);
     }
     mbar_init(&ph1_done, 256);
+    mbar_init(&sc_free, 256);
     mbar_init(&xa_full, 1);
     mbar_init(&a_ready, 1);
     mbar_init(&pt_full, 256);
@@ -215,6 +241,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
   if (!producer) named_bar_sync(2, 320);
   tc_fence_after_sync();
   const uint32_t tmem = producer ? 0u : tmem_base_s;
+  if (tid == 0) JVPFA_CS(1);
 
   // summary bits of column tile j against this row tile (64x64 summary entries are indexed [q][k])
   auto tile_bits = [&](int j) -> uint8_t {
@@ -308,26 +335,26 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
         const uint64_t db = desc_mnmajor_sw128(smem_u32(ctile), C::SLAB);
 #pragma unroll
         for (int k = 0; k < C::BC / 16; ++k)
-          umma_ts_pred(accum, e + (k & 1) * 8 + (k >> 1) * 32, db + static_cast<uint64_t>((k * 2048) >> 4), idesc_out,
-                       acc | (k > 0), lead);
+          umma_ts_pred(accum, e + (FAM == FAM_V ? k * 8 : (k & 1) * 8 + (k >> 1) * 32),
+                       db + static_cast<uint64_t>((k * 2048) >> 4), idesc_out, acc | (k > 0), lead);
       };
       // S, tS of tile i into score buffer sb
       auto issue_st = [&](int i, int sb) {
         const int buf = i % NA;
         wait_all(&a_full[buf], (i / NA) & 1, 20);
-        // family V: score buffer sb is free once the output products of tile i - 2 have read P, tP from it
-        if constexpr (FAM == FAM_V) if (i >= 2) wait_all(&e_free[sb], ((i - 2) >> 1) & 1, 27);
+        // family V: the one score buffer is free once the element-wise threads hold S, tS of tile i - 1 in registers
+        if constexpr (FAM == FAM_V) if (i >= 1) wait_all(&sc_free, (i - 1) & 1, 27);
         tc_fence_after_sync();
-        const uint32_t T0 = TS0 + sb * 128;
+        const uint32_t T0 = TS0;
         if constexpr (DUAL) {
           mma_nt(T0, sR(0), sA(buf), idesc_128, 0);        // [S | R0 c1^T]
-          if constexpr (FAM == FAM_V) if (leader) umma_commit(&s_ready[sb]);
           mma_nt(T0 + 64, sR(1), sA(buf), idesc_64, 1);    // tS += R1 c0^T
         } else {
           mma_nt(T0, sR(0), sA(buf), idesc_64, 0);         // S
         }
-        if (leader) umma_commit(&st_full[sb]);
+        if (leader) umma_commit(&st_full[0]);
         if constexpr (FAM == FAM_V) if (leader) umma_commit(&a_empty[buf]);
+        (void)sb;
       };
       // X, A of tile i (families Q, K)
       auto issue_xa = [&](int i) {
@@ -379,7 +406,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
           const bool has_next = jn < j_end;
           if constexpr (FAM == FAM_V) {
             const int buf = it % NB;
-            const uint32_t E0 = TS0 + (it & 1) * 128, E1 = E0 + 64;
+            const uint32_t E0 = TS0 + 128 + (it & 1) * 64, E1 = E0 + 32;   // 16-bit P, tP of this tile
             JVPFA_TR(0, it, 6);
             wait_all(&b_full[buf], (it / NB) & 1, 24);
             if constexpr (DUAL) {
@@ -481,26 +508,30 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
         }
         return *reinterpret_cast<const float2*>(&stats_s[it & 1][field][32 * wg + 2 * i]);
       };
-      const int sb = (FAM == FAM_V) ? (it & 1) : 0;
-      const uint32_t T0 = TS0 + sb * 128 + 32 * wg, T1 = T0 + 64;
+      const int sb = (FAM == FAM_V) ? (it & 1) : 0;   // family V: P, tP buffer of this tile
+      const uint32_t T0 = TS0 + 32 * wg, T1 = T0 + 64;
+      const uint32_t EV0 = TS0 + 128 + sb * 64 + 16 * wg, EV1 = EV0 + 32;   // family V: this thread's 16 columns of P, tP
       if (tr) JVPFA_TR(1 + wg, it, 0);
-      // family V, dual: P is computed from S as soon as the first score chain is complete, tP follows with tS
-      constexpr bool EARLY_P = (FAM == FAM_V) && DUAL;
-      if constexpr (EARLY_P) mbar_wait(&s_ready[sb], (it >> 1) & 1, w, 34);
-      else mbar_wait(&st_full[sb], (FAM == FAM_V) ? ((it >> 1) & 1) : (it & 1), w, 30);
+      // family V, dual: P goes back to TMEM first (its two output products start while tP is computed)
+      constexpr bool SPLIT_P = (FAM == FAM_V) && DUAL;
+      mbar_wait(&st_full[0], it & 1, w, 30);
       tc_fence_after_sync();
       if (tr) JVPFA_TR(1 + wg, it, 1);
+      if (tid == 0 && it == 0) JVPFA_CS(2);
       // ---- phase 1: P and ts of this thread's 32 columns (packed fp32x2 arithmetic: the element-wise
       // warps share their schedulers with the MMA-issuing warp, so every instruction saved here counts)
       float2 P2[16], ts2[16];
       {
         uint32_t a0[32], a1[32];
         tmem_ld_x32(T0, a0);
-        if constexpr (DUAL && !EARLY_P) tmem_ld_x32(T1, a1);
+        if constexpr (DUAL) tmem_ld_x32(T1, a1);
         tmem_wait_ld();
         if constexpr (FAM != FAM_V) {
           tc_fence_before_sync();
           mbar_arrive(&ph1_done);   // S, tS are in registers: the next tile's products may overwrite them
+        } else {
+          tc_fence_before_sync();
+          mbar_arrive(&sc_free);    // likewise: family V keeps one score buffer and two buffers of 16-bit P, tP
         }
         if (tr) JVPFA_TR(1 + wg, it, 2);
         const bool need_causal = p.causal && ((FAM == FAM_Q) ? (c0 + C::BC - 1 > r0) : (r0 + C::BR - 1 > c0));
@@ -510,7 +541,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
           x2[i] = __ffma2_rn(make_float2(__uint_as_float(a0[2 * i]), __uint_as_float(a0[2 * i + 1])), c1_2, stat2(0, i));
-          if constexpr (DUAL && !EARLY_P) ts2[i] = __fmul2_rn(make_float2(__uint_as_float(a1[2 * i]), __uint_as_float(a1[2 * i + 1])), s_2);
+          if constexpr (DUAL) ts2[i] = __fmul2_rn(make_float2(__uint_as_float(a1[2 * i]), __uint_as_float(a1[2 * i + 1])), s_2);
         }
         if (need_causal || need_bound || need_mask) {
 #pragma unroll
@@ -544,34 +575,35 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
         for (int i = 0; i < 16; ++i) P2[i] = make_float2(fast_exp2(x2[i].x), fast_exp2(x2[i].y));
       }
       if (tr) JVPFA_TR(1 + wg, it, 3);
-      if constexpr (EARLY_P) {
-        // P back into this thread's own columns of the score buffer, then tP = P (ts - mu) once tS is complete
+      if constexpr (SPLIT_P) {
+        // P into this tile's 16-bit buffer (which the output products of tile it - 2 read), then tP = P (ts - mu)
+        if (it >= 2) {
+          mbar_wait(&e_free[sb], ((it >> 1) - 1) & 1, w, 35);
+          tc_fence_after_sync();
+        }
         {
           uint32_t e0[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) e0[i] = pack2<BF16>(P2[i].x, P2[i].y);
-          tmem_st_x16(T0, e0);
+          tmem_st_x16(EV0, e0);
         }
         tmem_wait_st();
         tc_fence_before_sync();
         mbar_arrive(&pp_full[sb]);
         if (tr) JVPFA_TR(1 + wg, it, 7);
-        mbar_wait(&st_full[sb], (it >> 1) & 1, w, 30);
-        tc_fence_after_sync();
-        if (tr) JVPFA_TR(1 + wg, it, 4);
-        uint32_t a1[32];
-        tmem_ld_x32(T1, a1);
-        tmem_wait_ld();
         uint32_t e1[16];
 #pragma unroll
         for (int ip = 0; ip < 16; ++ip) {
-          const float2 ts = __fmul2_rn(make_float2(__uint_as_float(a1[2 * ip]), __uint_as_float(a1[2 * ip + 1])), s_2);
-          const float2 tp = __fmul2_rn(P2[ip], __fadd2_rn(ts, stat2(1, ip)));
+          const float2 tp = __fmul2_rn(P2[ip], __fadd2_rn(ts2[ip], stat2(1, ip)));
           e1[ip] = pack2<BF16>(tp.x, tp.y);
         }
-        tmem_st_x16(T1, e1);
+        tmem_st_x16(EV1, e1);
       } else if constexpr (FAM == FAM_V) {
-        // P and tP = P (ts - mu) back into this thread's own columns of the score buffer
+        // P (and tP = P (ts - mu)) into this tile's 16-bit buffer, which the output products of tile it - 2 read
+        if (it >= 2) {
+          mbar_wait(&e_free[sb], ((it >> 1) - 1) & 1, w, 35);
+          tc_fence_after_sync();
+        }
 #pragma unroll
         for (int hch = 0; hch < 2; ++hch) {
           uint32_t e0[8], e1[8];
@@ -584,8 +616,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
               e1[i] = pack2<BF16>(tp.x, tp.y);
             }
           }
-          tmem_st_x8(T0 + 8 * hch, e0);
-          if constexpr (DUAL) tmem_st_x8(T1 + 8 * hch, e1);
+          tmem_st_x8(EV0 + 8 * hch, e0);
+          if constexpr (DUAL) tmem_st_x8(EV1 + 8 * hch, e1);
         }
       } else {
         // ---- phase 2: X, A -> dS = P (X - Delta + ts (A - a) - mu A), dtS = P (A - a); both replace their
@@ -666,11 +698,19 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
       if (tr) JVPFA_TR(1 + wg, it, 6);
     }
     // epilogue
+    if (tid == 0) JVPFA_CS(3);
     mbar_wait(&acc_final, 0, w, 32);
     tc_fence_after_sync();
-    const size_t orow = (static_cast<size_t>(row_base) + gr) * p.D;
+    if (tid == 0) JVPFA_CS(4);
+    // Each warpgroup writes half of the head dimension; the rows go through this warp's patch of shared memory (the
+    // first row-side tile is no longer needed: every product has completed) so that the global stores are row segments.
+    constexpr int CH = D / 64;
+    if (it == 0) mbar_wait(&r_full, 0, w, 36);   // nothing was multiplied: the row-side loads may still be in flight
+    uint8_t* patch = sR(0) + warp * (32 * CH * 64);
+    uint32_t q0[CH][16], q1[CH][16];
 #pragma unroll
-    for (int c = wg * (D / 64); c < (wg + 1) * (D / 64); ++c) {
+    for (int cc = 0; cc < CH; ++cc) {
+      const int c = wg * CH + cc;
       uint32_t a0[32], a1[32];
       if (it > 0) {
         tmem_ld_x32(tmem + lane_off + C::TMEM_ACC0 + c * 32, a0);
@@ -680,28 +720,32 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
 #pragma unroll
         for (int i = 0; i < 32; ++i) { a0[i] = 0u; a1[i] = 0u; }
       }
-      if (gr < N) {
-        uint32_t q0[16], q1[16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          q0[i] = pack2<BF16>(__uint_as_float(a0[2 * i]) * p.out_scale, __uint_as_float(a0[2 * i + 1]) * p.out_scale);
-          if constexpr (DUAL)
-            q1[i] = pack2<BF16>(__uint_as_float(a1[2 * i]) * p.out_scale, __uint_as_float(a1[2 * i + 1]) * p.out_scale);
-        }
-        uint4* o0 = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.out0) + orow + c * 32);
-        uint4* o1 = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.out1) + orow + c * 32);
-#pragma unroll
-        for (int v4 = 0; v4 < 4; ++v4) {
-          if (c * 32 + v4 * 8 < p.D) {
-            o0[v4] = make_uint4(q0[4 * v4], q0[4 * v4 + 1], q0[4 * v4 + 2], q0[4 * v4 + 3]);
-            if constexpr (DUAL) o1[v4] = make_uint4(q1[4 * v4], q1[4 * v4 + 1], q1[4 * v4 + 2], q1[4 * v4 + 3]);
-          }
-        }
+      for (int i = 0; i < 16; ++i) {
+        q0[cc][i] = pack2<BF16>(__uint_as_float(a0[2 * i]) * p.out_scale, __uint_as_float(a0[2 * i + 1]) * p.out_scale);
+        if constexpr (DUAL)
+          q1[cc][i] = pack2<BF16>(__uint_as_float(a1[2 * i]) * p.out_scale, __uint_as_float(a1[2 * i + 1]) * p.out_scale);
       }
     }
+    {
+      const int col0 = wg * (D / 2);
+      const int wrow0 = r0 + (warp & 3) * 32;
+      const size_t goff = (static_cast<size_t>(row_base) + wrow0) * p.D + col0;
+      const int rows = N - wrow0, cols = p.D - col0;
+      store_rows_via_smem<CH>(patch, q0, static_cast<uint16_t*>(p.out0) + goff, p.D, rows, cols, lane);
+      if constexpr (DUAL) store_rows_via_smem<CH>(patch, q1, static_cast<uint16_t*>(p.out1) + goff, p.D, rows, cols, lane);
+    }
+    if (tid == 0) JVPFA_CS(5);
   }
   tc_fence_before_sync();
   __syncthreads();
+#ifdef JVPFA_CTA_TRACE
+  if (tid == 0) {
+    JVPFA_CS(6);
+    const int cta_ = blockIdx.y * gridDim.x + blockIdx.x;
+    if (cta_ < JVPFA_CTA_MAX) g_bwd_cta[(FAM * JVPFA_CTA_MAX + cta_) * 12 + 10] = j_end - j_begin;
+  }
+#endif
   if (warp == 9) tmem_dealloc(tmem, C::TMEM_COLS);
 }
 
@@ -841,6 +885,11 @@ int launch_all(const jvpfa_bwd_args& a, cudaStream_t stream) {
 #ifdef JVPFA_TRACE
 extern "C" int jvpfa_bwd_trace_read(long long* host_out) {
   return cudaMemcpyFromSymbol(host_out, g_bwd_trace, sizeof(g_bwd_trace)) == cudaSuccess ? 0 : 1;
+}
+#endif
+#ifdef JVPFA_CTA_TRACE
+extern "C" int jvpfa_bwd_cta_trace_read(long long* host_out) {
+  return cudaMemcpyFromSymbol(host_out, g_bwd_cta, sizeof(g_bwd_cta)) == cudaSuccess ? 0 : 1;
 }
 #endif
 

@@ -12,12 +12,13 @@
 //   warp 9     issues the score products (lane 0); owns the TMEM allocation
 //   warp 10    issues the output products (lane 0). tcgen05.mma issue blocks once three to four instructions are
 //              queued, so one issuing thread idles the tensor pipe during each of its barrier waits and commits;
-//              two instruction streams keep it fed. They hand score buffers to each other through s_free.
+//              two instruction streams keep it fed.
 // Per 64-column key tile: [S | Q tK^T] = Q [K; tK]^T as one N = 128 product against the stacked pair, then
 // tS += tQ K^T (operands in shared memory), then O += P V, T += W V + P tV (P, W read from TMEM; V, tV as
 // MN-major shared-memory operands). Epilogue: O/l, tO = T/l - (mu/l) O/l, lse2 = m + log2 l, mu/l.
-// TMEM columns: O [0,D), T [D,2D), then two score buffers of (S 64 | tS 64) columns; P and W overwrite
-// 16 of the 32 columns of S and tS that their thread has already read.
+// TMEM columns: O [0,D), T [D,2D), one score buffer (S 64 | tS 64), then two buffers of 16-bit (P 32 | W 32). The score
+// buffer is released as soon as every softmax thread holds its part of S, tS in registers, so that the next tile's
+// score products are queued behind the running output products instead of waiting for them to complete.
 #include <type_traits>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -40,6 +41,19 @@ __device__ long long g_fwd_trace[3 * 64 * 8];
   } while (0)
 #else
 #define JVPFA_FTR(role, it, k) do { } while (0)
+#endif
+// Optional per-CTA phase stamps (compile with -DJVPFA_CTA_TRACE): [cta][0..7] = clock64 at phase k, [cta][8] = smid,
+// [cta][9] = globaltimer at entry, [cta][10] = key tiles of the CTA.
+#ifdef JVPFA_CTA_TRACE
+#define JVPFA_CTA_MAX 8192
+__device__ long long g_fwd_cta[JVPFA_CTA_MAX * 12];
+#define JVPFA_CS(k)                                                                                   \
+  do {                                                                                                \
+    const int cta_ = blockIdx.y * gridDim.x + blockIdx.x;                                             \
+    if (cta_ < JVPFA_CTA_MAX) g_fwd_cta[cta_ * 12 + (k)] = clock64();                                 \
+  } while (0)
+#else
+#define JVPFA_CS(k) do { } while (0)
 #endif
 
 struct FwdKParams {
@@ -88,7 +102,8 @@ struct FwdCfg {
   static constexpr int STAGE = PAIR_K + 2 * TILE_V;
   static constexpr int TMEM_O = 0;
   static constexpr int TMEM_T = D;
-  static constexpr int TMEM_S = 2 * D;  // buffer b at TMEM_S + 128*b; tS 64 columns further
+  static constexpr int TMEM_S = 2 * D;        // S 64 columns, tS 64 columns further (one buffer)
+  static constexpr int TMEM_P = 2 * D + 128;  // 16-bit P (32 columns) and W (32 columns further), buffer b at + 64 b
   static constexpr int TMEM_COLS = 512;
   static constexpr int NBAR = 4 + 4 * STAGES + 4 + 2;
   static constexpr size_t smem_bytes() { return 2 * TILE_Q + STAGES * STAGE + 2 * 2 * 128 * 4 + (NBAR + 2) * 8; }
@@ -122,13 +137,14 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint64_t& q_full = bars[0];
   uint64_t& o_done = bars[1];
   uint64_t& o_final = bars[2];
-  uint64_t* s_full = bars + 4;       // [2]
+  uint64_t& s_full = bars[4];        // S, tS of the current tile are complete
+  uint64_t& s_free = bars[5];        // all 256 softmax threads have S, tS in registers: the next tile's products may overwrite them
   uint64_t* p_full = bars + 6;       // [2]
   uint64_t* k_full = bars + 8;
   uint64_t* v_full = k_full + ST;
   uint64_t* k_empty = v_full + ST;
   uint64_t* v_empty = k_empty + ST;
-  uint64_t* s_free = v_empty + ST;   // [2]: the PV products that read score buffer b have completed
+  uint64_t* p_free = v_empty + ST;   // [2]: the PV products that read P, W buffer b have completed
   uint32_t& tmem_base_s = *reinterpret_cast<uint32_t*>(bars + C::NBAR);
   int& poisoned = *reinterpret_cast<int*>(bars + C::NBAR + 1);
   if ((smem_u32(smem) & 1023u) != 0u) {  // the swizzled layouts need this; never observed otherwise
@@ -137,6 +153,18 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   }
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+#ifdef JVPFA_CTA_TRACE
+  if (tid == 0) {
+    JVPFA_CS(0);
+    const int cta_ = blockIdx.y * gridDim.x + blockIdx.x;
+    if (cta_ < JVPFA_CTA_MAX) {
+      uint32_t smid_;
+      asm volatile("mov.u32 %0, %%smid;" : "=r"(smid_));
+      g_fwd_cta[cta_ * 12 + 8] = smid_;
+      g_fwd_cta[cta_ * 12 + 9] = static_cast<long long>(global_timer_ns());
+    }
+  }
+#endif
   const int qt = p.causal ? (static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x)) : blockIdx.x;
   const int bh = blockIdx.y;
   const int b = bh / p.H, h = bh % p.H;
@@ -157,10 +185,11 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_init(&k_empty[i], 1);
       mbar_init(&v_empty[i], 1);
     }
+    mbar_init(&s_full, 1);
+    mbar_init(&s_free, 256);
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&s_full[i], 1);
       mbar_init(&p_full[i], 256);
-      mbar_init(&s_free[i], 1);
+      mbar_init(&p_free[i], 1);
     }
     mbar_init(&o_done, 1);
     mbar_init(&o_final, 1);
@@ -177,6 +206,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   if (!producer) named_bar_sync(2, 320);
   tc_fence_after_sync();
   const uint32_t tmem = producer ? 0u : tmem_base_s;
+  if (tid == 0) JVPFA_CS(1);
 
   // Key tile j takes part unless the mask summary says that nothing in it is kept.
   auto tile_bits = [&](int j) -> uint8_t {
@@ -262,10 +292,10 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     auto issue_qk = [&](int it) {
       const int st = it % ST;
       const uint32_t ph = (it / ST) & 1;
-      const uint32_t S_t = tmem + C::TMEM_S + (it & 1) * 128;
+      const uint32_t S_t = tmem + C::TMEM_S;
       if (leader) JVPFA_FTR(0, it, 0);
       wait_all(&k_full[st], ph, 20);
-      if (it >= 2) wait_all(&s_free[it & 1], ((it >> 1) - 1) & 1, 24);
+      if (it >= 1) wait_all(&s_free, (it - 1) & 1, 24);
       tc_fence_after_sync();
       if (leader) JVPFA_FTR(0, it, 1);
       const uint64_t dK = desc_kmajor_sw128(smem_u32(sK(st)));
@@ -282,7 +312,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             if (!PAD || k < ksteps) umma_ss(S_t + 64, dTQ + o, dK + o, idesc_64, 1);                    // tS += tQ K^T
           }
         }
-        umma_commit(&s_full[it & 1]);
+        umma_commit(&s_full);
         umma_commit(&k_empty[st]);
       }
       if (leader) JVPFA_FTR(0, it, 2);
@@ -290,8 +320,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     auto issue_pv = [&](int it, bool last) {
       const int st = it % ST;
       const uint32_t ph = (it / ST) & 1;
-      const uint32_t P_t = tmem + C::TMEM_S + (it & 1) * 128;
-      const uint32_t W_t = P_t + 64;
+      const uint32_t P_t = tmem + C::TMEM_P + (it & 1) * 64;
+      const uint32_t W_t = P_t + 32;
       if (leader) JVPFA_FTR(0, it, 3);
       wait_all(&p_full[it & 1], (it >> 1) & 1, 21);
       if (leader) JVPFA_FTR(0, it, 4);
@@ -305,7 +335,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
         for (int k = 0; k < C::BN / 16; ++k) {
           const uint64_t ok = static_cast<uint64_t>((k * 2048) >> 4);
-          const uint32_t eo = (k & 1) * 8 + (k >> 1) * 32;
+          const uint32_t eo = k * 8;
           umma_ts(tmem + C::TMEM_O, P_t + eo, dV0 + ok, idesc_pv, acc0 | (k > 0));
           if constexpr (DUAL) {
             umma_ts(tmem + C::TMEM_T, W_t + eo, dV0 + ok, idesc_pv, acc0 | (k > 0));
@@ -313,7 +343,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           }
         }
         umma_commit(&v_empty[st]);
-        umma_commit(&s_free[it & 1]);
+        umma_commit(&p_free[it & 1]);
         umma_commit(&o_done);
         if (last) umma_commit(&o_final);
       }
@@ -352,20 +382,28 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     for (int j = 0; j < n_kt; ++j) {
       const uint8_t bits = tile_bits(j);
       if (!(bits & kTileAnyKept)) continue;
-      const uint32_t S_t = tmem + C::TMEM_S + (it & 1) * 128 + lane_off + 32 * wg;
+      const uint32_t S_t = tmem + C::TMEM_S + lane_off + 32 * wg;
       const uint32_t tS_t = S_t + 64;
+      const uint32_t P_t = tmem + C::TMEM_P + (it & 1) * 64 + lane_off + 16 * wg;   // this thread's 16 columns of P
+      const uint32_t W_t = P_t + 32;
       const bool tr = lane == 0 && (warp & 3) == 0;
       if (tr) JVPFA_FTR(1 + wg, it, 0);
-      mbar_wait(&s_full[it & 1], (it >> 1) & 1, w, 30);
+      mbar_wait(&s_full, it & 1, w, 30);
       tc_fence_after_sync();
+      if (tid == 0 && it == 0) JVPFA_CS(2);
       if (tr) JVPFA_FTR(1 + wg, it, 1);
       // scores of this thread's 32 columns in the log2 domain, two per register pair (packed fp32x2
       // arithmetic: the softmax warps share their schedulers with the MMA-issuing warp)
       float2 x2[16];
+      uint32_t ts[32];
       {
         uint32_t r0[32];
         tmem_ld_x32(S_t, r0);
+        if constexpr (DUAL) tmem_ld_x32(tS_t, ts);
         tmem_wait_ld();
+        // S and tS are in registers: the next tile's score products may overwrite them
+        tc_fence_before_sync();
+        mbar_arrive(&s_free);
 #pragma unroll
         for (int i = 0; i < 16; ++i)
           x2[i] = __fmul2_rn(make_float2(__uint_as_float(r0[2 * i]), __uint_as_float(r0[2 * i + 1])), c1_2);
@@ -433,10 +471,10 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const float2 nm2 = make_float2(-m_eff, -m_eff);
       if (tr) JVPFA_FTR(1 + wg, it, 4);
       {
-        uint32_t ts[32];
-        if constexpr (DUAL) {
-          tmem_ld_x32(tS_t, ts);
-          tmem_wait_ld();
+        // the PV products of tile it - 2 read this P, W buffer
+        if (it >= 2) {
+          mbar_wait(&p_free[it & 1], ((it >> 1) - 1) & 1, w, 33);
+          tc_fence_after_sync();
         }
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
@@ -455,8 +493,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
               wk[i] = pack2<BF16>(ww.x, ww.y);
             }
           }
-          tmem_st_x8(S_t + 8 * c, pk);
-          if constexpr (DUAL) tmem_st_x8(tS_t + 8 * c, wk);
+          tmem_st_x8(P_t + 8 * c, pk);
+          if constexpr (DUAL) tmem_st_x8(W_t + 8 * c, wk);
         }
       }
       if (tr) JVPFA_FTR(1 + wg, it, 5);
@@ -469,6 +507,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     // epilogue: total row sums over both warpgroups, then each warpgroup writes half of the head dimension.
     // o_done flips once per key tile and a parity wait is only meaningful within one phase of the
     // barrier, so the end of the last accumulation has a barrier of its own.
+    if (tid == 0) JVPFA_CS(3);
     float l = l2.x + l2.y, mu = mu2.x + mu2.y;
     named_bar_sync(1, 256);
     xch[0][wg][r] = l;
@@ -480,11 +519,18 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_wait(&o_final, 0, w, 32);
       tc_fence_after_sync();
     }
+    if (tid == 0) JVPFA_CS(4);
     const float linv = (l > 0.f) ? 1.0f / l : 0.f;
     const float mul = mu * linv;
-    const size_t orow = (static_cast<size_t>(row_base) + qi) * p.D;
+    // Each warpgroup writes half of the head dimension; the rows go through this warp's patch of shared memory (the Q
+    // tile is no longer needed: every product that reads it has completed) so that the global stores are row segments.
+    constexpr int CH = D / 64;
+    if (it == 0) mbar_wait(&q_full, 0, w, 34);   // nothing was multiplied: the Q load itself may still be in flight
+    uint8_t* patch = sQ + warp * (32 * CH * 64);
+    uint32_t po[CH][16], pt[CH][16];
 #pragma unroll
-    for (int c = wg * (D / 64); c < (wg + 1) * (D / 64); ++c) {
+    for (int cc = 0; cc < CH; ++cc) {
+      const int c = wg * CH + cc;
       uint32_t ov[32], tv[32];
       if (it > 0) {
         tmem_ld_x32(tmem + lane_off + C::TMEM_O + c * 32, ov);
@@ -494,37 +540,40 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
         for (int i = 0; i < 32; ++i) { ov[i] = 0u; tv[i] = 0u; }
       }
-      uint32_t po[16], pt[16];
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
         const float o0 = __uint_as_float(ov[2 * i]) * linv, o1 = __uint_as_float(ov[2 * i + 1]) * linv;
-        po[i] = pack2<BF16>(o0, o1);
+        po[cc][i] = pack2<BF16>(o0, o1);
         if constexpr (DUAL) {
           const float t0 = __uint_as_float(tv[2 * i]) * linv - mul * o0;
           const float t1 = __uint_as_float(tv[2 * i + 1]) * linv - mul * o1;
-          pt[i] = pack2<BF16>(t0, t1);
+          pt[cc][i] = pack2<BF16>(t0, t1);
         }
       }
-      if (qi < N) {
-        uint4* op = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.o) + orow + c * 32);
-#pragma unroll
-        for (int v4 = 0; v4 < 4; ++v4)
-          if (c * 32 + v4 * 8 < p.D) op[v4] = make_uint4(po[4 * v4], po[4 * v4 + 1], po[4 * v4 + 2], po[4 * v4 + 3]);
-        if constexpr (DUAL) {
-          uint4* tp = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.to) + orow + c * 32);
-#pragma unroll
-          for (int v4 = 0; v4 < 4; ++v4)
-            if (c * 32 + v4 * 8 < p.D) tp[v4] = make_uint4(pt[4 * v4], pt[4 * v4 + 1], pt[4 * v4 + 2], pt[4 * v4 + 3]);
-        }
-      }
+    }
+    {
+      const int col0 = wg * (D / 2);                                   // first column of this warpgroup
+      const int wrow0 = q0 + (warp & 3) * 32;                          // first row of this warp
+      const size_t goff = (static_cast<size_t>(row_base) + wrow0) * p.D + col0;
+      const int rows = N - wrow0, cols = p.D - col0;
+      store_rows_via_smem<CH>(patch, po, static_cast<uint16_t*>(p.o) + goff, p.D, rows, cols, lane);
+      if constexpr (DUAL) store_rows_via_smem<CH>(patch, pt, static_cast<uint16_t*>(p.to) + goff, p.D, rows, cols, lane);
     }
     if (qi < N && wg == 0) {
       p.lse2[static_cast<size_t>(row_base) + qi] = (l > 0.f) ? m_used + log2f(l) : -INFINITY;
       p.mu[static_cast<size_t>(row_base) + qi] = mul;
     }
+    if (tid == 0) JVPFA_CS(5);
   }
   tc_fence_before_sync();
   __syncthreads();
+#ifdef JVPFA_CTA_TRACE
+  if (tid == 0) {
+    JVPFA_CS(6);
+    const int cta_ = blockIdx.y * gridDim.x + blockIdx.x;
+    if (cta_ < JVPFA_CTA_MAX) g_fwd_cta[cta_ * 12 + 10] = n_kt;
+  }
+#endif
   if (warp == 9) tmem_dealloc(tmem, C::TMEM_COLS);
 }
 
@@ -570,6 +619,11 @@ int launch_one(const jvpfa_fwd_args& a, cudaStream_t stream) {
 #ifdef JVPFA_TRACE
 extern "C" int jvpfa_fwd_trace_read(long long* host_out) {
   return cudaMemcpyFromSymbol(host_out, g_fwd_trace, sizeof(g_fwd_trace)) == cudaSuccess ? 0 : 1;
+}
+#endif
+#ifdef JVPFA_CTA_TRACE
+extern "C" int jvpfa_fwd_cta_trace_read(long long* host_out) {
+  return cudaMemcpyFromSymbol(host_out, g_fwd_cta, sizeof(g_fwd_cta)) == cudaSuccess ? 0 : 1;
 }
 #endif
 

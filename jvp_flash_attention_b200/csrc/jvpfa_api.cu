@@ -233,8 +233,15 @@ int jvpfa_bwd(const jvpfa_bwd_args* a, void* stream) {
       if (!aligned16(p)) return JVPFA_ERR_BAD_ARG;
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (sm100_path_supported(a->dtype, a->D, a->N)) return launch_bwd_sm100(*a, s);
-  return launch_bwd_generic(*a, s);
+  // Primal-only call: the tangent-side pointers are documented as ignored, so the kernels never see them (the
+  // preprocess kernels decide by gto whether the tangent terms enter Delta).
+  jvpfa_bwd_args eff = *a;
+  if (!dual) {
+    eff.tk = eff.tv = eff.to = eff.gto = nullptr;
+    eff.dtq = eff.dtk = eff.dtv = nullptr;
+  }
+  if (sm100_path_supported(eff.dtype, eff.D, eff.N)) return launch_bwd_sm100(eff, s);
+  return launch_bwd_generic(eff, s);
 }
 
 int jvpfa_kernel_timing(int enable, float* ms_out, int32_t* launches_out) {

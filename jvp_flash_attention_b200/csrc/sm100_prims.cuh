@@ -303,5 +303,43 @@ __device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
+// ---------------------------------------------------------------------------------------------
+// Epilogue stores. After a 32x32b TMEM load every lane of a warp holds one output row; written as they are, one
+// 16-byte store instruction touches 32 different 128-byte lines and the kernel spends thousands of cycles in the
+// store unit. The rows go through a per-warp shared-memory patch instead, so that each store instruction writes
+// whole row segments: CH * 4 consecutive lanes cover one row's CH * 64 bytes.
+//
+//   patch   this warp's 32 x (CH * 64) bytes of shared memory (16-byte aligned)
+//   packed  this lane's row: CH chunks of 32 sixteen-bit values, two per register
+//   dst     address of the first of the warp's 32 rows at this warp's first column; rows `pitch` elements apart
+//   rows    how many of the 32 rows exist (rows past the end of the sequence are not written)
+//   cols    how many of the CH * 32 columns exist (a multiple of 8; columns past the head dimension are not written)
+// ---------------------------------------------------------------------------------------------
+template <int CH>
+__device__ __forceinline__ void store_rows_via_smem(uint8_t* patch, const uint32_t (&packed)[CH][16], uint16_t* dst,
+                                                    size_t pitch, int rows, int cols, int lane) {
+  constexpr int ROWB = CH * 64;   // bytes per row in the patch
+  constexpr int LPR = CH * 4;     // lanes (16-byte pieces) per row
+  constexpr int RPP = 32 / LPR;   // rows per store instruction
+  auto swz = [](int row) { return CH == 1 ? ((row >> 1) & 3) : (row & (LPR - 1)); };
+  __syncwarp();
+#pragma unroll
+  for (int c = 0; c < CH; ++c)
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      const int pc = c * 4 + v;
+      *reinterpret_cast<uint4*>(patch + lane * ROWB + ((pc ^ swz(lane)) << 4)) =
+          make_uint4(packed[c][4 * v], packed[c][4 * v + 1], packed[c][4 * v + 2], packed[c][4 * v + 3]);
+    }
+  __syncwarp();
+  const int pc = lane % LPR;
+#pragma unroll
+  for (int i = 0; i < LPR; ++i) {
+    const int row = i * RPP + lane / LPR;
+    const uint4 val = *reinterpret_cast<const uint4*>(patch + row * ROWB + ((pc ^ swz(row)) << 4));
+    if (row < rows && pc * 8 < cols) *reinterpret_cast<uint4*>(dst + row * pitch + pc * 8) = val;
+  }
+}
+
 }  // namespace sm100
 }  // namespace jvpfa

@@ -11,6 +11,12 @@ Same public names as the reference module (jvp_flash_attention/jvp_attention.py)
   and may contain ``-inf``; any mask broadcastable to (Z, H, N, N) is accepted without a copy;
 * there is no Triton, no dispatch to another backend and no CPU path: without the CUDA library,
   or on CPU tensors, calls raise.
+
+Failure detection: every device-side wait in the kernels is bounded; one that gives up records a code in a status
+word and the kernel runs to its end. Each call enqueues a copy of that word to pinned host memory behind its
+kernels, and the next call on the same stream (without synchronising) or ``check()`` (which synchronises the
+device) raises ``_lib.JvpfaError`` with status ``ERR_DEVICE_TIMEOUT``; the results of the call that timed out are
+undefined. Errors the reference reports as Python exceptions (jvp_attention.py:2550, 2574, 3111) keep their types.
 """
 from __future__ import annotations
 
@@ -205,3 +211,9 @@ class JVPAttn:
 
 
 attention = JVPAttn.fwd
+
+
+def check(device=None) -> None:
+    """Synchronises ``device`` (default: the current CUDA device) and raises ``_lib.JvpfaError`` if a bounded
+    device-side wait gave up in any call since the last check."""
+    _lib.read_status(device)
