@@ -1,17 +1,17 @@
 #!/usr/bin/env python
 """Benchmark of the JVP attention hot path: dual forward + dual backward, in algorithmic TFLOP/s.
 
-One "step" = one dual forward and one dual backward over one batch of synthetic inputs
-(B=8, H=16, N=4096, D=128, causal; N(0,1) inputs, tangents and upstream gradients) per GPU.
-Algorithmic FLOPs per step = 42 * B * H * N^2 * D / 2 (matmul FLOPs only, causal halved: 12 for the
-dual forward, 30 for the backward; recomputed or padded work is not counted).
+One "step" = one dual forward and one dual backward over the whole problem B=8, H=16, N=4096, D=128, causal
+(N(0,1) inputs, tangents and upstream gradients). Algorithmic FLOPs per step = 42 * B * H * N^2 * D / 2 (matmul
+FLOPs only, causal halved: 12 for the dual forward, 30 for the backward; recomputed or padded work is not counted).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--dtype bf16|fp16] [--impl reference]
 
-N > 1 is launched with torch.distributed.run, one rank per GPU; every rank takes the same per-GPU
-workload (weak scaling, independent (batch, head) units, no collective on the attention path), the
-timed region is bracketed by a barrier and a device synchronize, the device time is reduced with MAX
-over ranks, and rank 0 prints one JSON line.
+N > 1 is launched with torch.distributed.run, one rank per GPU. The 128 (batch, head) units of the one problem are
+independent, so they are sliced over the ranks (16 per GPU at N = 8; strong scaling, no collective on the attention
+path); the timed region is bracketed by a barrier and a device synchronize, the device time is reduced with MAX over
+ranks, `value` = the whole problem's FLOPs over that time, and rank 0 prints one JSON line. The same line carries a
+`weak` record (every rank runs the full problem, as a fixed per-GPU workload) and an `fp16` record.
 
 ``--impl reference`` times the reference's CPU-runnable path (SDPA-MATH + torch.func.jvp + autograd,
 as in the reference's validator) on the host cores for the same metric and configuration, each step
@@ -55,7 +55,7 @@ class ClockSampler:
     """Samples SM clock and throttle reasons through NVML on a background thread."""
 
     def __init__(self, index: int, period_s: float = 0.02):
-        self.index, self.period, self.samples, self.reasons = index, period_s, [], set()
+        self.index, self.period, self.samples, self.reasons, self.power = index, period_s, [], set(), []
         self.max_mhz, self._stop, self._thread, self.ok = None, threading.Event(), None, False
         try:
             import pynvml
@@ -82,6 +82,7 @@ class ClockSampler:
         while not self._stop.is_set():
             try:
                 self.samples.append(int(self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM)))
+                self.power.append(self.nv.nvmlDeviceGetPowerUsage(self.h) / 1000.0)
                 self.reasons |= self._reason_names(int(self.nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)))
             except Exception:
                 pass
@@ -102,7 +103,8 @@ class ClockSampler:
         if not self.ok or not self.samples:
             return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "note": "NVML unavailable"}
         return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
-                "samples": len(self.samples)}
+                "samples": len(self.samples), "power_w_median": statistics.median(self.power) if self.power else None,
+                "power_w_max": max(self.power) if self.power else None}
 
 
 def physical_gpu_index(local: int) -> int:
@@ -118,10 +120,19 @@ def physical_gpu_index(local: int) -> int:
 # ------------------------------------------------------------------------------------------------
 # reference arm: the reference's CPU path on the host cores
 # ------------------------------------------------------------------------------------------------
+def host_threads(requested):
+    """Threads of the CPU arm: all host cores unless told otherwise (torch.distributed.run exports OMP_NUM_THREADS=1,
+    which would otherwise leave the CPU arm on one core)."""
+    n = requested if requested and requested > 0 else (os.cpu_count() or 1)
+    torch.set_num_threads(n)
+    return torch.get_num_threads()
+
+
 def run_reference(args, rank):
     if rank != 0:
         return
     from oracle.jvp_attention_oracle import sdpa_jvp_oracle
+    cores = host_threads(args.ref_threads)
     w = WORKLOAD
     slices = args.ref_slices
     g = torch.Generator().manual_seed(0)
@@ -135,18 +146,137 @@ def run_reference(args, rank):
     dt = time.perf_counter() - t0
     value = (fwd_f + bwd_f) * args.steps / dt / 1e12
     sample = (f"{slices} of {w['B'] * w['H']} (batch, head) slices per step, fp32, SDPA-MATH + torch.func.jvp + autograd "
-              f"(six gradients through both outputs)")
+              f"(six gradients through both outputs), {cores} host threads")
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": f"dual fwd+bwd attention B={w['B']} H={w['H']} N={w['N']} D={w['D']} causal, CPU reference path",
                    "sample": sample},
-        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+# GPU incumbent: the reference's own Triton kernels on this GPU (a child process, so that a failure there cannot
+# take the benchmark down). Reads the copy of the reference package under baseline/_ref.
+# ------------------------------------------------------------------------------------------------
+INCUMBENT_SHAPES = (
+    # name, B, H, N, D, causal          (the reference's published tables use B=2 H=12 N=2048 D=64)
+    ("readme_shape", 2, 12, 2048, 64, False),
+    ("readme_shape_causal", 2, 12, 2048, 64, True),
+    ("headline_shape", 8, 16, 4096, 128, True),
+)
+
+
+def _time_ms(fn, iters, warmup=3):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def run_incumbent_child(args):
+    """Child process: times the reference's dual forward (JVPAttn.fwd_dual under fwAD.dual_level) and its primal-only
+    backward through its stock code path, and this library's kernels on the same shapes; prints one JSON object."""
+    import torch.autograd.forward_ad as fwAD
+    out = {"dtype": args.dtype, "shapes": {}}
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_dir, "jvp_flash_attention")):
+        print(json.dumps({"unavailable": "reference-on-B200: unavailable (no copy of the reference under baseline/_ref)"}))
+        return
+    sys.path.insert(0, ref_dir)
+    try:
+        from jvp_flash_attention.jvp_attention import JVPAttn as RefAttn
+    except Exception as exc:  # noqa: BLE001
+        print(json.dumps({"unavailable": f"reference-on-B200: unavailable (import failed: {type(exc).__name__}: {exc})"[:400]}))
+        return
+    from jvp_flash_attention_b200 import _lib
+    dev = torch.device("cuda", 0)
+    dtype = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[args.dtype]
+    only = set(args.incumbent_shapes.split(",")) if args.incumbent_shapes else None
+    for name, B, H, N, D, causal in INCUMBENT_SHAPES:
+        if only is not None and name not in only:
+            continue
+        rec = {"B": B, "H": H, "N": N, "D": D, "causal": causal}
+        g = torch.Generator(device=dev).manual_seed(7)
+        q, k, v, tq, tk, tv, go = [torch.randn(B, H, N, D, device=dev, dtype=dtype, generator=g) for _ in range(7)]
+        fwd_f, bwd_f = algorithmic_flops(B, H, N, D, causal)
+        iters = 5 if N >= 4096 else 20
+        try:
+            def ref_fwd():
+                with fwAD.dual_level():
+                    o = RefAttn.fwd_dual(fwAD.make_dual(q, tq), fwAD.make_dual(k, tk), fwAD.make_dual(v, tv), causal=causal)
+                    return fwAD.unpack_dual(o)
+            o_ref, to_ref = ref_fwd()
+            torch.cuda.synchronize()
+            rec["ref_dual_fwd_ms"] = _time_ms(ref_fwd, iters)
+            ql, kl, vl = (t.clone().requires_grad_(True) for t in (q, k, v))
+            o2 = RefAttn.fwd(ql, kl, vl, causal=causal)
+
+            def ref_bwd():
+                return torch.autograd.grad(o2, (ql, kl, vl), go, retain_graph=True)
+            g_ref = ref_bwd()
+            torch.cuda.synchronize()
+            rec["ref_primal_bwd_ms"] = _time_ms(ref_bwd, iters)
+        except Exception as exc:  # noqa: BLE001
+            rec["ref_error"] = f"{type(exc).__name__}: {exc}"[:400]
+            out["shapes"][name] = rec
+            continue
+        s = D ** -0.5
+        mask_c = _lib.make_mask(None, B, H, N)
+        o, to, lse2, mu = _lib.fwd(q, k, v, tq, tk, tv, mask_c, None, causal, s)
+        rec["ours_dual_fwd_ms"] = _time_ms(lambda: _lib.fwd(q, k, v, tq, tk, tv, mask_c, None, causal, s), iters)
+        o1, _, lse1, mu1 = _lib.fwd(q, k, v, None, None, None, mask_c, None, causal, s)
+        gours = _lib.bwd(q, k, v, None, None, None, o1, None, lse1, mu1, go, None, mask_c, None, causal, s)
+        rec["ours_primal_bwd_ms"] = _time_ms(
+            lambda: _lib.bwd(q, k, v, None, None, None, o1, None, lse1, mu1, go, None, mask_c, None, causal, s), iters)
+        rec["ours_dual_bwd_ms"] = _time_ms(
+            lambda: _lib.bwd(q, k, v, tq, tk, tv, o, to, lse2, mu, go, go, mask_c, None, causal, s), iters)
+        rec["ref_dual_fwd_tflops"] = fwd_f / rec["ref_dual_fwd_ms"] / 1e9
+        rec["ours_dual_fwd_tflops"] = fwd_f / rec["ours_dual_fwd_ms"] / 1e9
+        rec["fwd_speedup"] = rec["ref_dual_fwd_ms"] / rec["ours_dual_fwd_ms"]
+        rec["primal_bwd_speedup"] = rec["ref_primal_bwd_ms"] / rec["ours_primal_bwd_ms"]
+        # the two implementations against each other (not a parity gate: the reference multiplies P V in TF32)
+        rec["max_abs_diff"] = {"O": float((o.float() - o_ref.float()).abs().max()),
+                               "tO": float((to.float() - to_ref.float()).abs().max()),
+                               "dq": float((gours[0].float() - g_ref[0].float()).abs().max()),
+                               "dk": float((gours[1].float() - g_ref[1].float()).abs().max()),
+                               "dv": float((gours[2].float() - g_ref[2].float()).abs().max())}
+        out["shapes"][name] = rec
+        del q, k, v, tq, tk, tv, go, o, to, o_ref, to_ref
+        torch.cuda.empty_cache()
+    _lib.read_status(dev)
+    out["note"] = ("reference = jvp_flash_attention (Triton) run unmodified from baseline/_ref on this GPU: JVPAttn.fwd_dual "
+                   "under fwAD.dual_level (dual forward) and autograd through JVPAttn.fwd (its backward covers the primal "
+                   "output only); ours = this library on the same tensors, dual forward / primal-only backward / dual backward")
+    print(json.dumps(out))
+
+
+def gpu_incumbent_record(args, timeout_s=420):
+    import subprocess
+    cmd = [sys.executable, os.path.abspath(__file__), "--impl", "gpu-incumbent", "--dtype", args.dtype]
+    try:
+        r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout_s, cwd=ROOT)
+    except subprocess.TimeoutExpired:
+        return {"unavailable": f"reference-on-B200: unavailable (child process did not finish within {timeout_s} s)"}
+    for ln in reversed(r.stdout.strip().splitlines()):
+        if ln.startswith("{"):
+            try:
+                return json.loads(ln)
+            except json.JSONDecodeError:
+                break
+    tail = (r.stderr or r.stdout or "").strip().splitlines()[-1:] or [""]
+    return {"unavailable": f"reference-on-B200: unavailable (child exit code {r.returncode}: {tail[0][:300]})"}
 
 
 # ------------------------------------------------------------------------------------------------
@@ -156,6 +286,7 @@ def run_cuda(args, rank, world, local_rank):
     import torch.distributed as dist
     from jvp_flash_attention_b200 import _lib
     from jvp_flash_attention_b200.jvp_attention import JVPAttn
+    from jvp_flash_attention_b200.sharding import shard_bounds
 
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
@@ -170,17 +301,11 @@ def run_cuda(args, rank, world, local_rank):
     if args.batch:
         w["B"] = args.batch
     B, H, N, D, causal = w["B"], w["H"], w["N"], w["D"], w["causal"]
-    dtype = torch.bfloat16 if args.dtype == "bf16" else torch.float16
+    units = B * H
+    lo, hi = shard_bounds(units, world, rank)          # this rank's slice of the flattened (batch, head) axis
+    U = hi - lo
     s = D ** -0.5
-    g = torch.Generator(device=dev).manual_seed(1234 + rank)
-    q, k, v, tq, tk, tv, gO, gtO = [torch.randn(B, H, N, D, device=dev, dtype=dtype, generator=g) for _ in range(8)]
-    mask_c = _lib.make_mask(None, B, H, N)
-    fwd_f, bwd_f = algorithmic_flops(B, H, N, D, causal)
-    step_f = fwd_f + bwd_f
-
-    def step():
-        o, to, lse2, mu = _lib.fwd(q, k, v, tq, tk, tv, mask_c, None, causal, s)
-        return _lib.bwd(q, k, v, tq, tk, tv, o, to, lse2, mu, gO, gtO, mask_c, None, causal, s)
+    peak_burst, peak_sustained, peak_kind = measured_peaks()
 
     def barrier():
         if world > 1:
@@ -194,58 +319,116 @@ def run_cuda(args, rank, world, local_rank):
             return float(t)
         return ms
 
-    # ---- device-resident timing (the `value`) ----
-    for _ in range(max(args.warmup, 3)):
-        step()
-    barrier()
-    _lib.read_status(dev)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(physical_gpu_index(local_rank)) as clocks:
+    def make_inputs(n_units, dtype, seed):
+        g = torch.Generator(device=dev).manual_seed(seed)
+        return [torch.randn(1, n_units, N, D, device=dev, dtype=dtype, generator=g) for _ in range(8)]
+
+    def timed_steps(ts, steps, warmup, sampler=None):
+        """Device time per step of dual forward + dual backward on resident inputs, MAX over ranks."""
+        q, k, v, tq, tk, tv, gO, gtO = ts
+        n_units = q.shape[1]
+        mask_c = _lib.make_mask(None, 1, n_units, N)
+
+        def step():
+            o, to, lse2, mu = _lib.fwd(q, k, v, tq, tk, tv, mask_c, None, causal, s)
+            return _lib.bwd(q, k, v, tq, tk, tv, o, to, lse2, mu, gO, gtO, mask_c, None, causal, s)
+
+        for _ in range(warmup):
+            step()
+        barrier()
+        _lib.read_status(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if sampler is not None:
+            sampler.__enter__()
         barrier()
         e0.record()
-        for _ in range(args.steps):
+        for _ in range(steps):
             step()
         e1.record()
         barrier()
-    ms_total = max_over_ranks(e0.elapsed_time(e1))
-    _lib.read_status(dev)
-    ms_step = ms_total / args.steps
-    value = step_f * world / (ms_step * 1e-3) / 1e12
+        if sampler is not None:
+            sampler.__exit__(None, None, None)
+        ms = max_over_ranks(e0.elapsed_time(e1)) / steps
+        _lib.read_status(dev)
+        return ms
 
-    # ---- per-kernel durations, same steps, events on the launching stream ----
-    _lib.kernel_timing(True)
+    fwd_f, bwd_f = algorithmic_flops(1, units, N, D, causal)          # the whole problem
+    step_f = fwd_f + bwd_f
+    warmup = max(args.warmup, 3)
+    dtype = torch.bfloat16 if args.dtype == "bf16" else torch.float16
+
+    # ---- device-resident timing of this rank's slice (the `value`) ----
+    ts = make_inputs(U, dtype, 1234 + rank)
+    clocks = ClockSampler(physical_gpu_index(local_rank))
+    ms_step = timed_steps(ts, args.steps, warmup, clocks)
+    value = step_f / (ms_step * 1e-3) / 1e12
+
+    # ---- per-kernel durations of the same steps: caller-owned events recorded between the launches ----
+    q, k, v, tq, tk, tv, gO, gtO = ts
+    mask_c = _lib.make_mask(None, 1, U, N)
+    ev_f = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
+    for e in ev_f + marks:
+        e.record()                                     # creates the underlying CUDA events
+    names = ("fwd", "bwd_preprocess", "bwd_q", "bwd_k", "bwd_v")
+    acc = dict.fromkeys(names, 0.0)
     for _ in range(args.steps):
-        step()
-    torch.cuda.synchronize()
-    kt = _lib.kernel_timing(False)
-    kernels = {name: {"ms_per_launch": (ms / n if n else None), "launches": n} for name, (ms, n) in kt.items()}
-    bwd_names = ("bwd_q", "bwd_k", "bwd_v")
-    bwd_ms = sum(kt[n][0] for n in bwd_names)
-    bwd_launches = sum(kt[n][1] for n in bwd_names)
-    peak_burst, peak_sustained, peak_kind = measured_peaks()
+        ev_f[0].record()
+        o, to, lse2, mu = _lib.fwd(q, k, v, tq, tk, tv, mask_c, None, causal, s)
+        ev_f[1].record()
+        _lib.bwd(q, k, v, tq, tk, tv, o, to, lse2, mu, gO, gtO, mask_c, None, causal, s, marks=marks)
+        torch.cuda.synchronize()
+        acc["fwd"] += ev_f[0].elapsed_time(ev_f[1])
+        for i, nme in enumerate(names[1:]):
+            acc[nme] += marks[i].elapsed_time(marks[i + 1])
+    kernels = {nme: {"ms_per_launch": acc[nme] / args.steps, "launches": args.steps} for nme in names}
+    lfwd_f, lbwd_f = algorithmic_flops(1, U, N, D, causal)            # this rank's slice
+    fam_ms = (acc["bwd_q"] + acc["bwd_k"] + acc["bwd_v"]) / (3.0 * args.steps)
     # dominant kernel: the backward family kernel (one template, three launches per step); algorithmic FLOPs per
-    # launch = a third of the backward's 30*B*H*N^2*D/2
-    ach = (bwd_f / 3.0) / ((bwd_ms / max(bwd_launches, 1)) * 1e-3) / 1e12 if bwd_launches else None
-    roofline = {"bound": "tensor", "kernel": "bwd_sm100_kernel (families Q, K, V)", "achieved": ach, "peak": peak_sustained,
-                "unit": "TFLOP/s", "frac": (ach / peak_sustained if ach else None), "peak_kind": f"{peak_kind} sustained bf16 cuBLAS",
-                # DRAM bytes per backward-family launch: ncu capture of the B=2 case (profiles/bwd_fwd_sm100_full_set_small.md:
-                # 321.9 / 320.9 / 251.3 MB read+write for families Q / K / V), scaled by B/2 -- traffic grows with the
-                # number of (batch, head) units, every unit's tensors are read from HBM once per launch
-                "traffic": (321.9e6 + 320.9e6 + 251.3e6) / 3.0 * (B / 2.0), "traffic_unit": "bytes per launch",
-                "fwd_kernel": {"achieved": fwd_f / (kt["fwd"][0] / max(kt["fwd"][1], 1) * 1e-3) / 1e12 if kt["fwd"][1] else None}}
-    if roofline["fwd_kernel"]["achieved"]:
-        roofline["fwd_kernel"]["frac"] = roofline["fwd_kernel"]["achieved"] / peak_sustained
+    # launch = a third of the backward's 30 * units * N^2 * D / 2
+    ach = (lbwd_f / 3.0) / (fam_ms * 1e-3) / 1e12
+    fwd_ach = lfwd_f / (acc["fwd"] / args.steps * 1e-3) / 1e12
+    roofline = {"bound": "tensor", "kernel": "bwd_sm100_kernel (families Q, K, V)", "achieved": ach, "peak": peak_burst,
+                "unit": "TFLOP/s", "frac": ach / peak_burst, "peak_kind": f"{peak_kind} burst bf16 cuBLAS",
+                "frac_sustained": ach / peak_sustained, "frac_nominal": ach / NOMINAL_DENSE_TFLOPS,
+                "executed_over_algorithmic": 1.6, "achieved_executed": ach * 1.6,
+                # DRAM bytes per backward-family launch from an ncu capture of 32 (batch, head) units (321.9 / 320.9 /
+                # 251.3 MB read+write for families Q / K / V), scaled by the units of this launch: every unit's tensors
+                # are read from HBM once per launch, so the traffic grows in proportion
+                "traffic": (321.9e6 + 320.9e6 + 251.3e6) / 3.0 * (U / 32.0), "traffic_unit": "bytes per launch",
+                "fwd_kernel": {"achieved": fwd_ach, "frac": fwd_ach / peak_burst, "frac_sustained": fwd_ach / peak_sustained}}
 
-    # ---- end to end through the public API with host buffers ----
+    # ---- the other 16-bit type (the headline configuration is stated in fp16, the target line in bf16) ----
+    other = torch.float16 if dtype == torch.bfloat16 else torch.bfloat16
+    other_name = "fp16" if other == torch.float16 else "bf16"
+    del ts, q, k, v, tq, tk, tv, gO, gtO, o, to
+    ts_o = make_inputs(U, other, 4321 + rank)
+    ms_o = timed_steps(ts_o, max(4, args.steps // 2), 3)
+    other_rec = {"value": step_f / (ms_o * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_o, "dtype": other_name}
+    del ts_o
+
+    # ---- weak scaling beside it: every rank runs the full problem (a fixed per-GPU workload) ----
+    weak = None
+    if world > 1 and not args.no_weak:
+        ts_w = make_inputs(units, dtype, 99 + rank)
+        ms_w = timed_steps(ts_w, max(4, args.steps // 2), 3)
+        weak = {"value": step_f * world / (ms_w * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_w,
+                "scaling": "weak", "global_batch": B * world,
+                "note": "every rank runs the full B x H problem; aggregate over ranks"}
+        del ts_w
+
+    # ---- end to end through the public API with host buffers (this rank's slice) ----
     e2e = None
     if not args.no_e2e:
-        host_in = [torch.empty(B, H, N, D, dtype=dtype).pin_memory() for _ in range(8)]
-        for hbuf, src in zip(host_in, (q, k, v, tq, tk, tv, gO, gtO)):
+        ts = make_inputs(U, dtype, 1234 + rank)
+        host_in = [torch.empty(1, U, N, D, dtype=dtype).pin_memory() for _ in range(8)]
+        for hbuf, src in zip(host_in, ts):
             hbuf.copy_(src)
-        host_out = [torch.empty(B, H, N, D, dtype=dtype).pin_memory() for _ in range(8)]
+        del ts
+        host_out = [torch.empty(1, U, N, D, dtype=dtype).pin_memory() for _ in range(8)]
         # Three streams, inputs double-buffered on the device: the copy-in of step i+1 and the copy-out of step
         # i-1 overlap the kernels of step i, as a caller that streams batches through the public API would do.
-        dev_in = [[torch.empty(B, H, N, D, dtype=dtype, device=dev) for _ in range(8)] for _ in range(2)]
+        dev_in = [[torch.empty(1, U, N, D, dtype=dtype, device=dev) for _ in range(8)] for _ in range(2)]
         s_main = torch.cuda.current_stream(dev)
         s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
         ev_in = [torch.cuda.Event() for _ in range(2)]     # inputs of this buffer set have arrived
@@ -280,6 +463,7 @@ def run_cuda(args, rank, world, local_rank):
             e2e_step()
         barrier()
         n_e2e = max(4, args.steps // 2)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(n_e2e):
             e2e_step()
@@ -287,44 +471,58 @@ def run_cuda(args, rank, world, local_rank):
         e1.record()
         barrier()
         ms_e2e = max_over_ranks(e0.elapsed_time(e1)) / n_e2e
-        nbytes = 8 * B * H * N * D * q.element_size()
-        e2e = {"value": step_f * world / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": nbytes,
+        nbytes = 8 * U * N * D * 2
+        e2e = {"value": step_f / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": nbytes,
                "d2h_bytes_per_step": nbytes, "ms_per_step": ms_e2e, "steps": n_e2e,
-               "note": "JVPAttn.dual + autograd.grad; every step copies its 8 input tensors from pinned host memory and "
-                       "O, tO and the six gradients back to pinned host memory inside the timed region; copies run on "
-                       "their own streams and overlap the kernels of the neighbouring steps"}
+               "note": "JVPAttn.dual + autograd.grad on this rank's slice; every step copies its 8 input tensors from "
+                       "pinned host memory and O, tO and the six gradients back to pinned host memory inside the timed "
+                       "region (bytes are per rank); copies run on their own streams and overlap the kernels of the "
+                       "neighbouring steps. The limiter is the host link, not a kernel: all ranks of a node share host "
+                       "memory and PCIe root bandwidth"}
         del host_in, host_out, dev_in
+        _lib.read_status(dev)
 
     # ---- CPU baseline beside it (rank 0, N = 1 only) ----
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu:
         from oracle.jvp_attention_oracle import sdpa_jvp_oracle
+        cores = host_threads(args.ref_threads)
         gcpu = torch.Generator().manual_seed(0)
-        ts = [torch.randn(1, 1, N, D, generator=gcpu) for _ in range(8)]
-        sdpa_jvp_oracle(*ts, causal=causal, dtype=torch.float32)  # warm-up
+        tsc = [torch.randn(1, 1, N, D, generator=gcpu) for _ in range(8)]
+        sdpa_jvp_oracle(*tsc, causal=causal, dtype=torch.float32)  # warm-up
         done, t0 = 0, time.perf_counter()
         while done < 32 and (time.perf_counter() - t0 < 10.0 or done < 2):
-            sdpa_jvp_oracle(*ts, causal=causal, dtype=torch.float32)
+            sdpa_jvp_oracle(*tsc, causal=causal, dtype=torch.float32)
             done += 1
         dt = time.perf_counter() - t0
         f1, b1 = algorithmic_flops(1, 1, N, D, causal)
-        cpu_baseline = {"value": (f1 + b1) * done / dt / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(),
+        cpu_baseline = {"value": (f1 + b1) * done / dt / 1e12, "unit": "TFLOP/s", "cores": cores,
                         "kind": "port", "sample": f"{done} (batch, head) slices of the workload, fp32, SDPA-MATH + "
                         "torch.func.jvp + autograd on the host cores", "seconds": dt}
+
+    # ---- the reference's own GPU kernels on this box (rank 0, N = 1 only) ----
+    incumbent = None
+    if rank == 0 and world == 1 and not args.no_incumbent:
+        torch.cuda.empty_cache()
+        incumbent = gpu_incumbent_record(args)
 
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "warmup": warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": args.dtype, "data": "synthetic",
-            "config": {"workload": f"dual fwd+bwd attention, per GPU B={B} H={H} N={N} D={D} causal {args.dtype}, "
-                                   "fully masked key tiles skipped; batch x head units sharded over GPUs, no collective",
-                       "global_batch": B * world, "l2": "inputs larger than L2 (8 tensors of 134 MB per step)",
-                       "flops_per_step_per_gpu": step_f},
+            "config": {"workload": f"dual fwd+bwd attention, one problem B={B} H={H} N={N} D={D} causal {args.dtype}, "
+                                   f"fully masked key tiles skipped; its {units} (batch, head) units sliced over the "
+                                   f"GPUs ({U} per GPU), no collective",
+                       "global_batch": B, "units_per_gpu": U,
+                       "l2": f"inputs larger than L2 (8 tensors of {U * N * D * 2 / 1e6:.0f} MB per GPU and step)",
+                       "flops_per_step": step_f},
             "per_gpu_tflops": value / world,
             "frac_of_nominal_dense_peak": value / world / NOMINAL_DENSE_TFLOPS,
             "frac_of_measured_peak": value / world / peak_burst,
-            "roofline": roofline, "kernels": kernels, "cpu_baseline": cpu_baseline, "e2e": e2e,
+            "frac_of_measured_sustained_peak": value / world / peak_sustained,
+            "roofline": roofline, "kernels": kernels, other_name: other_rec, "weak": weak,
+            "cpu_baseline": cpu_baseline, "gpu_incumbent": incumbent, "e2e": e2e,
             "gpu_launches": 5 * args.steps, "clocks": clocks.summary(),
         }
         sys.stdout.flush()
@@ -339,12 +537,16 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--dtype", choices=("bf16", "fp16"), default="bf16")
-    ap.add_argument("--impl", choices=("cuda", "reference"), default="cuda")
+    ap.add_argument("--dtype", choices=("bf16", "fp16", "fp32"), default="bf16")
+    ap.add_argument("--impl", choices=("cuda", "reference", "gpu-incumbent"), default="cuda")
     ap.add_argument("--ref-slices", type=int, default=2, help="(batch, head) slices per step of the reference arm")
+    ap.add_argument("--ref-threads", type=int, default=0, help="host threads of the CPU arm (default: all cores)")
     ap.add_argument("--batch", type=int, default=None, help="override B of the workload (small profiler captures only)")
+    ap.add_argument("--incumbent-shapes", default="", help="comma-separated subset of the GPU-incumbent shapes")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-weak", action="store_true")
+    ap.add_argument("--no-incumbent", action="store_true")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -352,6 +554,11 @@ def main():
     if args.impl == "reference":
         run_reference(args, rank)
         return
+    if args.impl == "gpu-incumbent":
+        run_incumbent_child(args)
+        return
+    if args.dtype == "fp32":
+        raise SystemExit("--dtype fp32 is for --impl gpu-incumbent only")
     if world != args.gpus and world == 1 and args.gpus > 1:
         raise SystemExit("launch N > 1 with: python -m torch.distributed.run --nnodes=1 --nproc-per-node N "
                          "--master-addr 127.0.0.1 --master-port P bench.py --gpus N ...")

@@ -113,6 +113,15 @@ int jvpfa_bwd(const jvpfa_bwd_args* args, void* stream);
  * 100 + the id of the wait that gave up). */
 int jvpfa_read_status(void* workspace, void* stream, int32_t* detail);
 
+/* Self-test of the failure-detection path. Launches one tiny kernel on `stream` in which a single thread waits, with
+ * the kernels' own bounded wait, on a barrier that nothing arrives on: after `budget_us` microseconds (1 .. 1000000)
+ * the wait gives up, writes 177 (100 + wait id 77) into the status word at the start of `workspace` and the kernel
+ * returns normally; a second wait in the same kernel takes the short path of an already failed CTA. `out4` (device,
+ * four int32) receives the two wait results (0 = gave up) and their durations in microseconds. Afterwards
+ * jvpfa_read_status reports JVPFA_ERR_DEVICE_TIMEOUT once. Nothing faults, traps or spins without bound. No reference
+ * counterpart (its errors are host-side Python exceptions, jvp_attention.py:2550, 2574, 3111). */
+int jvpfa_selftest_timeout(void* workspace, int32_t budget_us, int32_t* out4, void* stream);
+
 /* Largest problem (B*H*N query rows) the allocation-free backward accepts; its scratch is 256 B + 16 B per row. */
 #define JVPFA_NO_ALLOC_MAX_ROWS 262144
 
@@ -136,13 +145,13 @@ int jvpfa_read_status(void* workspace, void* stream, int32_t* detail);
  * kernels, on `stream`: 0 means no device-side wait gave up. */
 int jvpfa_bwd_noalloc(const jvpfa_bwd_args* args, int32_t* status_word_out, void* stream);
 
-/* Per-kernel timing for benchmarks. Collects what was measured since the last call -- summed
- * milliseconds and launch counts for the five kernel kinds, in the order forward, backward
- * preprocess, backward family Q, K, V (either pointer may be NULL) -- waits for those launches
- * to finish, and then switches measurement on (enable != 0) or off. While on, each launch is
- * bracketed by CUDA events on its stream. Off by default. No reference counterpart (the reference
- * times whole calls with perf_counter, tests/test_jvp_attention.py:116-143). */
-int jvpfa_kernel_timing(int enable, float* ms_out, int32_t* launches_out);
+/* jvpfa_bwd with caller-owned CUDA events recorded between its launches, for benchmarks that want the
+ * duration of each kernel: events[0] is recorded on `stream` before the preprocess kernel, events[1], [2], [3]
+ * before the three main kernels (gradients of the query side, of the key side, of the value side) and events[4]
+ * after the last one. `events` holds five cudaEvent_t created by the caller with timing enabled; n_events must be 5.
+ * The library keeps no state for this. No reference counterpart (the reference times whole calls with perf_counter,
+ * tests/test_jvp_attention.py:116-143). */
+int jvpfa_bwd_marked(const jvpfa_bwd_args* args, void* stream, void* const* events, int32_t n_events);
 
 #ifdef __cplusplus
 }

@@ -30,7 +30,8 @@ EXPORTED_SYMBOLS = (
     "jvpfa_fwd",
     "jvpfa_bwd",
     "jvpfa_read_status",
-    "jvpfa_kernel_timing",
+    "jvpfa_bwd_marked",
+    "jvpfa_selftest_timeout",
     "jvpfa_bwd_noalloc",
 )
 
@@ -110,8 +111,10 @@ def lib():
                 L.jvpfa_bwd.argtypes = [C.POINTER(BwdArgs), C.c_void_p]
                 L.jvpfa_read_status.restype = C.c_int
                 L.jvpfa_read_status.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_int32)]
-                L.jvpfa_kernel_timing.restype = C.c_int
-                L.jvpfa_kernel_timing.argtypes = [C.c_int, C.POINTER(C.c_float), C.POINTER(C.c_int32)]
+                L.jvpfa_selftest_timeout.restype = C.c_int
+                L.jvpfa_selftest_timeout.argtypes = [C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p]
+                L.jvpfa_bwd_marked.restype = C.c_int
+                L.jvpfa_bwd_marked.argtypes = [C.POINTER(BwdArgs), C.c_void_p, C.POINTER(C.c_void_p), C.c_int32]
                 L.jvpfa_bwd_noalloc.restype = C.c_int
                 L.jvpfa_bwd_noalloc.argtypes = [C.POINTER(BwdArgs), C.c_void_p, C.c_void_p]
                 _lib = L
@@ -224,6 +227,18 @@ def read_status(device=None) -> None:
             raise JvpfaError(rc, lib().jvpfa_error_string(rc).decode() + f" (wait id {detail.value})")
 
 
+def selftest_timeout(device, budget_us: int = 2000) -> torch.Tensor:
+    """Runs the library's failure-detection self-test on the current stream of ``device``: a bounded device-side wait
+    that is made to run out. Returns the (4,) int32 device tensor with the two wait results and their durations in
+    microseconds. The status word is then non-zero: the next call on this stream, or ``read_status``, raises."""
+    ws = workspace(device, 256)
+    out = torch.full((4,), -1, dtype=torch.int32, device=device)
+    check(lib().jvpfa_selftest_timeout(C.c_void_p(ws.data_ptr()), int(budget_us), C.c_void_p(out.data_ptr()),
+                                       stream_ptr(device)))
+    post_launch(device)
+    return out
+
+
 def mask_summary(mask_c: Mask, mask_tensor, B, H, N):
     """Runs the tile-summary pre-pass; returns the uint8 tensor (kept alive by the caller)."""
     if mask_c.kind == MASK_NONE:
@@ -261,9 +276,12 @@ def fwd(q, k, v, tq, tk, tv, mask_c: Mask, summary, causal: bool, sm_scale: floa
     return o, to, lse2, mu
 
 
-def bwd(q, k, v, tq, tk, tv, o, to, lse2, mu, go, gto, mask_c: Mask, summary, causal: bool, sm_scale: float):
+def bwd(q, k, v, tq, tk, tv, o, to, lse2, mu, go, gto, mask_c: Mask, summary, causal: bool, sm_scale: float,
+        marks=None):
     """Launches the backward. Dual form: returns (dq, dk, dv, dtq, dtk, dtv). With tq None (primal-only: tk, tv,
-    to, gto are ignored) returns (dq, dk, dv)."""
+    to, gto are ignored) returns (dq, dk, dv). ``marks``: five ``torch.cuda.Event(enable_timing=True)`` that have
+    been recorded once (so that they exist); they are recorded before the preprocess kernel, before each of the three
+    family kernels and after the last one."""
     B, H, N, D = q.shape
     dual = tq is not None
     outs = [torch.empty_like(q) for _ in range(6 if dual else 3)]
@@ -284,18 +302,10 @@ def bwd(q, k, v, tq, tk, tv, o, to, lse2, mu, go, gto, mask_c: Mask, summary, ca
     need = lib().jvpfa_bwd_workspace_bytes(C.byref(a))
     ws = workspace(q.device, need)
     a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
-    check(lib().jvpfa_bwd(C.byref(a), stream_ptr(q.device)))
+    if marks is None:
+        check(lib().jvpfa_bwd(C.byref(a), stream_ptr(q.device)))
+    else:
+        handles = (C.c_void_p * 5)(*[C.c_void_p(e.cuda_event) for e in marks])
+        check(lib().jvpfa_bwd_marked(C.byref(a), stream_ptr(q.device), handles, 5))
     post_launch(q.device)
     return tuple(outs)
-
-
-KERNEL_NAMES = ("fwd", "bwd_preprocess", "bwd_q", "bwd_k", "bwd_v")
-
-
-def kernel_timing(enable: bool):
-    """Collects per-kernel milliseconds and launch counts measured since the last call, then switches
-    the measurement on or off. Returns {name: (total_ms, launches)}."""
-    ms = (C.c_float * 5)()
-    n = (C.c_int32 * 5)()
-    check(lib().jvpfa_kernel_timing(int(enable), ms, n))
-    return {name: (float(ms[i]), int(n[i])) for i, name in enumerate(KERNEL_NAMES)}

@@ -39,30 +39,6 @@ namespace {
 
 enum { FAM_Q = 0, FAM_K = 1, FAM_V = 2 };
 
-// Optional cycle trace of CTA (0,0) for kernel tuning (compile with -DJVPFA_TRACE): role 0 = MMA issuer,
-// 1 / 2 = first lane of element-wise warpgroup 0 / 1; 8 time stamps per tile for the first 64 tiles, per family.
-#ifdef JVPFA_TRACE
-__device__ long long g_bwd_trace[3 * 3 * 64 * 8];  // [family][role][tile][stamp]
-#define JVPFA_TR(role, it, k)                                                                        \
-  do {                                                                                               \
-    if (blockIdx.x == 0 && blockIdx.y == 0 && (it) < 64) g_bwd_trace[((FAM * 3 + (role)) * 64 + (it)) * 8 + (k)] = clock64(); \
-  } while (0)
-#else
-#define JVPFA_TR(role, it, k) do { } while (0)
-#endif
-// Optional per-CTA phase stamps (compile with -DJVPFA_CTA_TRACE): [family][cta][0..7] = clock64 at phase k,
-// [8] = smid, [9] = globaltimer at entry, [10] = column tiles of the CTA.
-#ifdef JVPFA_CTA_TRACE
-#define JVPFA_CTA_MAX 8192
-__device__ long long g_bwd_cta[3 * JVPFA_CTA_MAX * 12];
-#define JVPFA_CS(k)                                                                                   \
-  do {                                                                                                \
-    const int cta_ = blockIdx.y * gridDim.x + blockIdx.x;                                             \
-    if (cta_ < JVPFA_CTA_MAX) g_bwd_cta[(FAM * JVPFA_CTA_MAX + cta_) * 12 + (k)] = clock64();         \
-  } while (0)
-#else
-#define JVPFA_CS(k) do { } while (0)
-#endif
 
 struct BwdKParams {
   int H, N;
@@ -176,18 +152,6 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
   }
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-#ifdef JVPFA_CTA_TRACE
-  if (tid == 0) {
-    JVPFA_CS(0);
-    const int cta_ = blockIdx.y * gridDim.x + blockIdx.x;
-    if (cta_ < JVPFA_CTA_MAX) {
-      uint32_t smid_;
-      asm volatile("mov.u32 %0, %%smid;" : "=r"(smid_));
-      g_bwd_cta[(FAM * JVPFA_CTA_MAX + cta_) * 12 + 8] = smid_;
-      g_bwd_cta[(FAM * JVPFA_CTA_MAX + cta_) * 12 + 9] = static_cast<long long>(global_timer_ns());
-    }
-  }
-#endif
   const int n_rt = gridDim.x;
   // heavier tiles first under a causal mask: late query tiles, early key tiles
   const int rt = (p.causal && FAM == FAM_Q) ? (n_rt - 1 - static_cast<int>(blockIdx.x)) : blockIdx.x;
@@ -241,7 +205,6 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
   if (!producer) named_bar_sync(2, 320);
   tc_fence_after_sync();
   const uint32_t tmem = producer ? 0u : tmem_base_s;
-  if (tid == 0) JVPFA_CS(1);
 
   // summary bits of column tile j against this row tile (64x64 summary entries are indexed [q][k])
   auto tile_bits = [&](int j) -> uint8_t {
@@ -385,17 +348,14 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
         if (j < j_end) issue_st(0, 0);
         for (; j < j_end; ++it) {
           const int jn = next_active(j + 1);
-          JVPFA_TR(0, it, 0);
           if (jn < j_end) {
             if constexpr (FAM == FAM_V) {
               issue_st(it + 1, (it + 1) & 1);
             } else {
               wait_all(&ph1_done, it & 1, 25);
-              JVPFA_TR(0, it, 5);
               issue_st(it + 1, 0);
             }
           }
-          JVPFA_TR(0, it, 1);
           j = jn;
         }
       } else {
@@ -407,24 +367,20 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
           if constexpr (FAM == FAM_V) {
             const int buf = it % NB;
             const uint32_t E0 = TS0 + 128 + (it & 1) * 64, E1 = E0 + 32;   // 16-bit P, tP of this tile
-            JVPFA_TR(0, it, 6);
             wait_all(&b_full[buf], (it / NB) & 1, 24);
             if constexpr (DUAL) {
               // P only needs S, which the first score chain completes: its two products run before tP exists
               wait_all(&pp_full[it & 1], (it >> 1) & 1, 29);
               tc_fence_after_sync();
-              JVPFA_TR(0, it, 7);
               mma_out(tmem + C::TMEM_ACC0, E0, sB(buf), it > 0);             // dV  += P^T gO
               mma_out(tmem + C::TMEM_ACC1, E0, sB(buf) + C::HALF, it > 0);   // dtV += P^T gtO
             }
             wait_all(&p_full[it & 1], (it >> 1) & 1, 23);
             tc_fence_after_sync();
-            JVPFA_TR(0, it, 2);
             if constexpr (DUAL) mma_out(tmem + C::TMEM_ACC0, E1, sB(buf) + C::HALF, 1);   // dV += tP^T gtO
             else mma_out(tmem + C::TMEM_ACC0, E0, sB(buf), it > 0);                         // dV += P^T gO
             if (leader) umma_commit(&b_empty[buf]);
             if (leader) umma_commit(&e_free[it & 1]);
-            JVPFA_TR(0, it, 3);
           } else {
             const int buf = it % NA;
             // dtS replaces A and dS replaces X in place (family Q: A first, X second; family K: X first, A second).
@@ -432,21 +388,16 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
             const uint32_t E0 = (DUAL && FAM == FAM_Q) ? TS0 + 192 : TS0 + 128;   // dS
             const uint32_t E1 = (DUAL && FAM == FAM_Q) ? TS0 + 128 : TS0 + 192;   // dtS
             if constexpr (DUAL) {
-              JVPFA_TR(0, it, 6);
               wait_all(&pt_full, it & 1, 28);
               tc_fence_after_sync();
-              JVPFA_TR(0, it, 7);
               mma_out(tmem + C::TMEM_ACC0, E1, sA(buf) + C::HALF, it > 0);   // dtS c1
               mma_out(tmem + C::TMEM_ACC1, E1, sA(buf), it > 0);             // dtS c0
             }
             wait_all(&p_full[0], it & 1, 26);
             tc_fence_after_sync();
-            JVPFA_TR(0, it, 2);
             mma_out(tmem + C::TMEM_ACC0, E0, sA(buf), DUAL ? 1u : static_cast<uint32_t>(it > 0));   // dS c0
             if (leader) umma_commit(&a_empty[buf]);
-            JVPFA_TR(0, it, 3);
             if (has_next) issue_xa(it + 1);
-            JVPFA_TR(0, it, 4);
           }
           j = jn;
         }
@@ -461,7 +412,6 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
     const int r = (warp & 3) * 32 + lane;
     const int gr = r0 + r;             // global sequence index of this thread's row
     const int gr_c = min(gr, N - 1);
-    const bool tr = (lane == 0 && (warp & 3) == 0);
     const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t TS0 = tmem + C::TMEM_T + lane_off;
     // negated statistics of this thread's query row (family Q): -lse2, -mu, -Delta, -a
@@ -511,13 +461,10 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
       const int sb = (FAM == FAM_V) ? (it & 1) : 0;   // family V: P, tP buffer of this tile
       const uint32_t T0 = TS0 + 32 * wg, T1 = T0 + 64;
       const uint32_t EV0 = TS0 + 128 + sb * 64 + 16 * wg, EV1 = EV0 + 32;   // family V: this thread's 16 columns of P, tP
-      if (tr) JVPFA_TR(1 + wg, it, 0);
       // family V, dual: P goes back to TMEM first (its two output products start while tP is computed)
       constexpr bool SPLIT_P = (FAM == FAM_V) && DUAL;
       mbar_wait(&st_full[0], it & 1, w, 30);
       tc_fence_after_sync();
-      if (tr) JVPFA_TR(1 + wg, it, 1);
-      if (tid == 0 && it == 0) JVPFA_CS(2);
       // ---- phase 1: P and ts of this thread's 32 columns (packed fp32x2 arithmetic: the element-wise
       // warps share their schedulers with the MMA-issuing warp, so every instruction saved here counts)
       float2 P2[16], ts2[16];
@@ -533,7 +480,6 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
           tc_fence_before_sync();
           mbar_arrive(&sc_free);    // likewise: family V keeps one score buffer and two buffers of 16-bit P, tP
         }
-        if (tr) JVPFA_TR(1 + wg, it, 2);
         const bool need_causal = p.causal && ((FAM == FAM_Q) ? (c0 + C::BC - 1 > r0) : (r0 + C::BR - 1 > c0));
         const bool need_bound = (FAM == FAM_Q) && (c0 + C::BC > N);
         const bool need_mask = p.mv.kind != JVPFA_MASK_NONE && (bits & kTileAnyMasked);
@@ -574,7 +520,6 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
 #pragma unroll
         for (int i = 0; i < 16; ++i) P2[i] = make_float2(fast_exp2(x2[i].x), fast_exp2(x2[i].y));
       }
-      if (tr) JVPFA_TR(1 + wg, it, 3);
       if constexpr (SPLIT_P) {
         // P into this tile's 16-bit buffer (which the output products of tile it - 2 read), then tP = P (ts - mu)
         if (it >= 2) {
@@ -590,7 +535,6 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
         tmem_wait_st();
         tc_fence_before_sync();
         mbar_arrive(&pp_full[sb]);
-        if (tr) JVPFA_TR(1 + wg, it, 7);
         uint32_t e1[16];
 #pragma unroll
         for (int ip = 0; ip < 16; ++ip) {
@@ -649,11 +593,9 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
           tmem_wait_st();
           tc_fence_before_sync();
           mbar_arrive(&pt_full);
-          if (tr) JVPFA_TR(1 + wg, it, 7);
           // phase 2b, when X is complete
           mbar_wait(&xa_full, it & 1, w, 31);
           tc_fence_after_sync();
-          if (tr) JVPFA_TR(1 + wg, it, 4);
 #pragma unroll
           for (int hch = 0; hch < 2; ++hch) {
             uint32_t xr[16];
@@ -672,7 +614,6 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
         } else {
           mbar_wait(&xa_full, it & 1, w, 31);
           tc_fence_after_sync();
-          if (tr) JVPFA_TR(1 + wg, it, 4);
           const uint32_t TX = (FAM == FAM_Q) ? T3 : T2;
 #pragma unroll
           for (int hch = 0; hch < 2; ++hch) {
@@ -691,17 +632,13 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
           }
         }
       }
-      if (tr) JVPFA_TR(1 + wg, it, 5);
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive(&p_full[sb]);
-      if (tr) JVPFA_TR(1 + wg, it, 6);
     }
     // epilogue
-    if (tid == 0) JVPFA_CS(3);
     mbar_wait(&acc_final, 0, w, 32);
     tc_fence_after_sync();
-    if (tid == 0) JVPFA_CS(4);
     // Each warpgroup writes half of the head dimension; the rows go through this warp's patch of shared memory (the
     // first row-side tile is no longer needed: every product has completed) so that the global stores are row segments.
     constexpr int CH = D / 64;
@@ -735,17 +672,9 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
       store_rows_via_smem<CH>(patch, q0, static_cast<uint16_t*>(p.out0) + goff, p.D, rows, cols, lane);
       if constexpr (DUAL) store_rows_via_smem<CH>(patch, q1, static_cast<uint16_t*>(p.out1) + goff, p.D, rows, cols, lane);
     }
-    if (tid == 0) JVPFA_CS(5);
   }
   tc_fence_before_sync();
   __syncthreads();
-#ifdef JVPFA_CTA_TRACE
-  if (tid == 0) {
-    JVPFA_CS(6);
-    const int cta_ = blockIdx.y * gridDim.x + blockIdx.x;
-    if (cta_ < JVPFA_CTA_MAX) g_bwd_cta[(FAM * JVPFA_CTA_MAX + cta_) * 12 + 10] = j_end - j_begin;
-  }
-#endif
   if (warp == 9) tmem_dealloc(tmem, C::TMEM_COLS);
 }
 
@@ -849,31 +778,33 @@ int launch_family(const jvpfa_bwd_args& a, const float4* stats, cudaStream_t str
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
     return JVPFA_ERR_LAUNCH;
   dim3 grid((a.N + C::BR - 1) / C::BR, a.B * a.H);
-  ScopedKernelTimer timer(FAM == FAM_Q ? KERNEL_BWD_Q : (FAM == FAM_K ? KERNEL_BWD_K : KERNEL_BWD_V), stream);
   kern<<<grid, 352, smem, stream>>>(rm[0], rm[1], rm[2], rm[3], cm[0], cm[1], cm[2], cm[3], p);
   return cudaGetLastError() == cudaSuccess ? JVPFA_OK : JVPFA_ERR_LAUNCH;
 }
 
 template <int D, bool BF16>
-int launch_all(const jvpfa_bwd_args& a, cudaStream_t stream) {
+int launch_all(const jvpfa_bwd_args& a, cudaStream_t stream, const LaunchMarks& marks) {
   const int64_t rows = static_cast<int64_t>(a.B) * a.H * a.N;
   float4* stats = reinterpret_cast<float4*>(static_cast<uint8_t*>(a.workspace) + kStatusBytes);
   const int warps_per_block = 8;   // two rows per warp
   const unsigned blocks = static_cast<unsigned>((rows + 2 * warps_per_block - 1) / (2 * warps_per_block));
-  {
-  ScopedKernelTimer timer(KERNEL_BWD_PREPROCESS, stream);
+  marks.mark(0);
   bwd_preprocess_kernel<BF16><<<blocks, warps_per_block * 32, 0, stream>>>(
       static_cast<const uint16_t*>(a.o), static_cast<const uint16_t*>(a.to), static_cast<const uint16_t*>(a.go),
       static_cast<const uint16_t*>(a.gto), a.lse2, a.mu, stats, rows, a.D);
-  }
   if (cudaGetLastError() != cudaSuccess) return JVPFA_ERR_LAUNCH;
   auto three = [&](auto pad, auto dual) {
     constexpr bool P = decltype(pad)::value, DU = decltype(dual)::value;
+    marks.mark(1);
     int rc = launch_family<D, FAM_Q, BF16, P, DU>(a, stats, stream);
     if (rc != JVPFA_OK) return rc;
+    marks.mark(2);
     rc = launch_family<D, FAM_K, BF16, P, DU>(a, stats, stream);
     if (rc != JVPFA_OK) return rc;
-    return launch_family<D, FAM_V, BF16, P, DU>(a, stats, stream);
+    marks.mark(3);
+    rc = launch_family<D, FAM_V, BF16, P, DU>(a, stats, stream);
+    marks.mark(4);
+    return rc;
   };
   const bool dual = a.tq != nullptr;
   if (a.D == D) return dual ? three(std::false_type{}, std::true_type{}) : three(std::false_type{}, std::false_type{});
@@ -882,25 +813,15 @@ int launch_all(const jvpfa_bwd_args& a, cudaStream_t stream) {
 
 }  // namespace
 
-#ifdef JVPFA_TRACE
-extern "C" int jvpfa_bwd_trace_read(long long* host_out) {
-  return cudaMemcpyFromSymbol(host_out, g_bwd_trace, sizeof(g_bwd_trace)) == cudaSuccess ? 0 : 1;
-}
-#endif
-#ifdef JVPFA_CTA_TRACE
-extern "C" int jvpfa_bwd_cta_trace_read(long long* host_out) {
-  return cudaMemcpyFromSymbol(host_out, g_bwd_cta, sizeof(g_bwd_cta)) == cudaSuccess ? 0 : 1;
-}
-#endif
 
 size_t bwd_sm100_workspace_bytes(const jvpfa_bwd_args& a) {
   return kStatusBytes + static_cast<size_t>(a.B) * a.H * a.N * sizeof(float4);
 }
 
-int launch_bwd_sm100(const jvpfa_bwd_args& a, cudaStream_t stream) {
+int launch_bwd_sm100(const jvpfa_bwd_args& a, cudaStream_t stream, const LaunchMarks& marks) {
   const bool bf = a.dtype == JVPFA_BF16;
-  if (sm100_padded_dim(a.D) == 64) return bf ? launch_all<64, true>(a, stream) : launch_all<64, false>(a, stream);
-  return bf ? launch_all<128, true>(a, stream) : launch_all<128, false>(a, stream);
+  if (sm100_padded_dim(a.D) == 64) return bf ? launch_all<64, true>(a, stream, marks) : launch_all<64, false>(a, stream, marks);
+  return bf ? launch_all<128, true>(a, stream, marks) : launch_all<128, false>(a, stream, marks);
 }
 
 }  // namespace jvpfa

@@ -31,30 +31,6 @@ using namespace sm100;
 
 namespace {
 
-// Optional cycle trace of CTA (0,0) for kernel tuning (compile with -DJVPFA_TRACE): role 0 = MMA issuer,
-// 1 / 2 = first lane of softmax warpgroup 0 / 1; 8 time stamps per tile for the first 64 tiles.
-#ifdef JVPFA_TRACE
-__device__ long long g_fwd_trace[3 * 64 * 8];
-#define JVPFA_FTR(role, it, k)                                                                       \
-  do {                                                                                               \
-    if (blockIdx.x == 0 && blockIdx.y == 0 && (it) < 64) g_fwd_trace[((role)*64 + (it)) * 8 + (k)] = clock64(); \
-  } while (0)
-#else
-#define JVPFA_FTR(role, it, k) do { } while (0)
-#endif
-// Optional per-CTA phase stamps (compile with -DJVPFA_CTA_TRACE): [cta][0..7] = clock64 at phase k, [cta][8] = smid,
-// [cta][9] = globaltimer at entry, [cta][10] = key tiles of the CTA.
-#ifdef JVPFA_CTA_TRACE
-#define JVPFA_CTA_MAX 8192
-__device__ long long g_fwd_cta[JVPFA_CTA_MAX * 12];
-#define JVPFA_CS(k)                                                                                   \
-  do {                                                                                                \
-    const int cta_ = blockIdx.y * gridDim.x + blockIdx.x;                                             \
-    if (cta_ < JVPFA_CTA_MAX) g_fwd_cta[cta_ * 12 + (k)] = clock64();                                 \
-  } while (0)
-#else
-#define JVPFA_CS(k) do { } while (0)
-#endif
 
 struct FwdKParams {
   int H, N;
@@ -153,18 +129,6 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   }
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-#ifdef JVPFA_CTA_TRACE
-  if (tid == 0) {
-    JVPFA_CS(0);
-    const int cta_ = blockIdx.y * gridDim.x + blockIdx.x;
-    if (cta_ < JVPFA_CTA_MAX) {
-      uint32_t smid_;
-      asm volatile("mov.u32 %0, %%smid;" : "=r"(smid_));
-      g_fwd_cta[cta_ * 12 + 8] = smid_;
-      g_fwd_cta[cta_ * 12 + 9] = static_cast<long long>(global_timer_ns());
-    }
-  }
-#endif
   const int qt = p.causal ? (static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x)) : blockIdx.x;
   const int bh = blockIdx.y;
   const int b = bh / p.H, h = bh % p.H;
@@ -206,7 +170,6 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   if (!producer) named_bar_sync(2, 320);
   tc_fence_after_sync();
   const uint32_t tmem = producer ? 0u : tmem_base_s;
-  if (tid == 0) JVPFA_CS(1);
 
   // Key tile j takes part unless the mask summary says that nothing in it is kept.
   auto tile_bits = [&](int j) -> uint8_t {
@@ -293,11 +256,9 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const int st = it % ST;
       const uint32_t ph = (it / ST) & 1;
       const uint32_t S_t = tmem + C::TMEM_S;
-      if (leader) JVPFA_FTR(0, it, 0);
       wait_all(&k_full[st], ph, 20);
       if (it >= 1) wait_all(&s_free, (it - 1) & 1, 24);
       tc_fence_after_sync();
-      if (leader) JVPFA_FTR(0, it, 1);
       const uint64_t dK = desc_kmajor_sw128(smem_u32(sK(st)));
       if (leader) {
 #pragma unroll
@@ -315,19 +276,15 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         umma_commit(&s_full);
         umma_commit(&k_empty[st]);
       }
-      if (leader) JVPFA_FTR(0, it, 2);
     };
     auto issue_pv = [&](int it, bool last) {
       const int st = it % ST;
       const uint32_t ph = (it / ST) & 1;
       const uint32_t P_t = tmem + C::TMEM_P + (it & 1) * 64;
       const uint32_t W_t = P_t + 32;
-      if (leader) JVPFA_FTR(0, it, 3);
       wait_all(&p_full[it & 1], (it >> 1) & 1, 21);
-      if (leader) JVPFA_FTR(0, it, 4);
       wait_all(&v_full[st], ph, 22);
       tc_fence_after_sync();
-      if (leader) JVPFA_FTR(0, it, 5);
       const uint64_t dV0 = desc_mnmajor_sw128(smem_u32(sV(st)), C::BN * 128);
       const uint64_t dTV0 = desc_mnmajor_sw128(smem_u32(sTV(st)), C::BN * 128);
       const uint32_t acc0 = it > 0;
@@ -347,7 +304,6 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         umma_commit(&o_done);
         if (last) umma_commit(&o_final);
       }
-      if (leader) JVPFA_FTR(0, it, 6);
     };
 
     int it = 0;
@@ -386,12 +342,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const uint32_t tS_t = S_t + 64;
       const uint32_t P_t = tmem + C::TMEM_P + (it & 1) * 64 + lane_off + 16 * wg;   // this thread's 16 columns of P
       const uint32_t W_t = P_t + 32;
-      const bool tr = lane == 0 && (warp & 3) == 0;
-      if (tr) JVPFA_FTR(1 + wg, it, 0);
       mbar_wait(&s_full, it & 1, w, 30);
       tc_fence_after_sync();
-      if (tid == 0 && it == 0) JVPFA_CS(2);
-      if (tr) JVPFA_FTR(1 + wg, it, 1);
       // scores of this thread's 32 columns in the log2 domain, two per register pair (packed fp32x2
       // arithmetic: the softmax warps share their schedulers with the MMA-issuing warp)
       float2 x2[16];
@@ -437,10 +389,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
       for (int i = 1; i < 16; ++i) m_tile = fmaxf(m_tile, fmaxf(x2[i].x, x2[i].y));
       // row maximum over both warpgroups
-      if (tr) JVPFA_FTR(1 + wg, it, 2);
       xch[it & 1][wg][r] = m_tile;
       named_bar_sync(1, 256);
-      if (tr) JVPFA_FTR(1 + wg, it, 3);
       m_tile = fmaxf(m_tile, xch[it & 1][wg ^ 1][r]);
       const float m_new = fmaxf(m_used, m_tile);
       const bool need = m_new > m_used + p.thresh;
@@ -469,7 +419,6 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
       const float m_eff = (m_used == -INFINITY) ? 0.f : m_used;
       const float2 nm2 = make_float2(-m_eff, -m_eff);
-      if (tr) JVPFA_FTR(1 + wg, it, 4);
       {
         // the PV products of tile it - 2 read this P, W buffer
         if (it >= 2) {
@@ -497,17 +446,14 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           if constexpr (DUAL) tmem_st_x8(W_t + 8 * c, wk);
         }
       }
-      if (tr) JVPFA_FTR(1 + wg, it, 5);
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive(&p_full[it & 1]);
-      if (tr) JVPFA_FTR(1 + wg, it, 6);
       ++it;
     }
     // epilogue: total row sums over both warpgroups, then each warpgroup writes half of the head dimension.
     // o_done flips once per key tile and a parity wait is only meaningful within one phase of the
     // barrier, so the end of the last accumulation has a barrier of its own.
-    if (tid == 0) JVPFA_CS(3);
     float l = l2.x + l2.y, mu = mu2.x + mu2.y;
     named_bar_sync(1, 256);
     xch[0][wg][r] = l;
@@ -519,7 +465,6 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_wait(&o_final, 0, w, 32);
       tc_fence_after_sync();
     }
-    if (tid == 0) JVPFA_CS(4);
     const float linv = (l > 0.f) ? 1.0f / l : 0.f;
     const float mul = mu * linv;
     // Each warpgroup writes half of the head dimension; the rows go through this warp's patch of shared memory (the Q
@@ -563,17 +508,9 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       p.lse2[static_cast<size_t>(row_base) + qi] = (l > 0.f) ? m_used + log2f(l) : -INFINITY;
       p.mu[static_cast<size_t>(row_base) + qi] = mul;
     }
-    if (tid == 0) JVPFA_CS(5);
   }
   tc_fence_before_sync();
   __syncthreads();
-#ifdef JVPFA_CTA_TRACE
-  if (tid == 0) {
-    JVPFA_CS(6);
-    const int cta_ = blockIdx.y * gridDim.x + blockIdx.x;
-    if (cta_ < JVPFA_CTA_MAX) g_fwd_cta[cta_ * 12 + 10] = n_kt;
-  }
-#endif
   if (warp == 9) tmem_dealloc(tmem, C::TMEM_COLS);
 }
 
@@ -609,23 +546,12 @@ int launch_one(const jvpfa_fwd_args& a, cudaStream_t stream) {
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
     return JVPFA_ERR_LAUNCH;
   dim3 grid((a.N + C::BM - 1) / C::BM, a.B * a.H);
-  ScopedKernelTimer timer(KERNEL_FWD, stream);
   kern<<<grid, 384, smem, stream>>>(mQ, mTQ, mK, mTK, mV, mTV, p);
   return cudaGetLastError() == cudaSuccess ? JVPFA_OK : JVPFA_ERR_LAUNCH;
 }
 
 }  // namespace
 
-#ifdef JVPFA_TRACE
-extern "C" int jvpfa_fwd_trace_read(long long* host_out) {
-  return cudaMemcpyFromSymbol(host_out, g_fwd_trace, sizeof(g_fwd_trace)) == cudaSuccess ? 0 : 1;
-}
-#endif
-#ifdef JVPFA_CTA_TRACE
-extern "C" int jvpfa_fwd_cta_trace_read(long long* host_out) {
-  return cudaMemcpyFromSymbol(host_out, g_fwd_cta, sizeof(g_fwd_cta)) == cudaSuccess ? 0 : 1;
-}
-#endif
 
 bool sm100_path_supported(int dtype, int D, int N) {
   // head dimensions other than 64 / 128 run on the next wider kernel with zero-filled columns

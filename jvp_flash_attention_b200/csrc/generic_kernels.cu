@@ -446,7 +446,6 @@ int fwd_typed(const jvpfa_fwd_args& a, cudaStream_t stream) {
   auto launch = [&](auto kern) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
       return JVPFA_ERR_LAUNCH;
-    ScopedKernelTimer timer(KERNEL_FWD, stream);
     kern<<<grid, NTHREADS, smem, stream>>>(static_cast<const T*>(a.q), static_cast<const T*>(a.k),
                                            static_cast<const T*>(a.v), static_cast<const T*>(a.tq),
                                            static_cast<const T*>(a.tk), static_cast<const T*>(a.tv),
@@ -491,36 +490,38 @@ int bwd_family(const jvpfa_bwd_args& a, const float4* stats, cudaStream_t stream
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
     return JVPFA_ERR_LAUNCH;
   dim3 grid((a.N + TB - 1) / TB, a.B * a.H);
-  ScopedKernelTimer timer(FAM == FAM_Q ? KERNEL_BWD_Q : (FAM == FAM_K ? KERNEL_BWD_K : KERNEL_BWD_V), stream);
   kern<<<grid, NTHREADS, smem, stream>>>(r[0], r[1], r[2], r[3], c[0], c[1], c[2], c[3], o0, o1, p);
   return cudaGetLastError() == cudaSuccess ? JVPFA_OK : JVPFA_ERR_LAUNCH;
 }
 
 template <typename T, int NJ>
-int bwd_typed(const jvpfa_bwd_args& a, cudaStream_t stream) {
+int bwd_typed(const jvpfa_bwd_args& a, cudaStream_t stream, const LaunchMarks& marks) {
   const int64_t rows = static_cast<int64_t>(a.B) * a.H * a.N;
   float4* stats = reinterpret_cast<float4*>(static_cast<uint8_t*>(a.workspace) + kStatusBytes);
   const unsigned blocks = static_cast<unsigned>((rows + 7) / 8);
-  {
-  ScopedKernelTimer timer(KERNEL_BWD_PREPROCESS, stream);
+  marks.mark(0);
   generic_preprocess_kernel<T><<<blocks, 256, 0, stream>>>(static_cast<const T*>(a.o), static_cast<const T*>(a.to),
                                                          static_cast<const T*>(a.go), static_cast<const T*>(a.gto),
                                                          a.lse2, a.mu, stats, rows, a.D);
-  }
   if (cudaGetLastError() != cudaSuccess) return JVPFA_ERR_LAUNCH;
+  marks.mark(1);
   int rc = bwd_family<T, NJ, FAM_Q>(a, stats, stream);
   if (rc != JVPFA_OK) return rc;
+  marks.mark(2);
   rc = bwd_family<T, NJ, FAM_K>(a, stats, stream);
   if (rc != JVPFA_OK) return rc;
-  return bwd_family<T, NJ, FAM_V>(a, stats, stream);
+  marks.mark(3);
+  rc = bwd_family<T, NJ, FAM_V>(a, stats, stream);
+  marks.mark(4);
+  return rc;
 }
 
 template <typename T>
-int bwd_by_d(const jvpfa_bwd_args& a, cudaStream_t stream) {
-  if (a.D <= 32) return bwd_typed<T, 2>(a, stream);
-  if (a.D <= 64) return bwd_typed<T, 4>(a, stream);
-  if (a.D <= 128) return bwd_typed<T, 8>(a, stream);
-  return bwd_typed<T, 16>(a, stream);
+int bwd_by_d(const jvpfa_bwd_args& a, cudaStream_t stream, const LaunchMarks& marks) {
+  if (a.D <= 32) return bwd_typed<T, 2>(a, stream, marks);
+  if (a.D <= 64) return bwd_typed<T, 4>(a, stream, marks);
+  if (a.D <= 128) return bwd_typed<T, 8>(a, stream, marks);
+  return bwd_typed<T, 16>(a, stream, marks);
 }
 
 }  // namespace
@@ -539,12 +540,12 @@ size_t bwd_generic_workspace_bytes(const jvpfa_bwd_args& a) {
   return kStatusBytes + static_cast<size_t>(a.B) * a.H * a.N * sizeof(float4);
 }
 
-int launch_bwd_generic(const jvpfa_bwd_args& a, cudaStream_t stream) {
+int launch_bwd_generic(const jvpfa_bwd_args& a, cudaStream_t stream, const LaunchMarks& marks) {
   if (a.D > kMaxD) return JVPFA_ERR_UNSUPPORTED;
   switch (a.dtype) {
-    case JVPFA_F32: return bwd_by_d<float>(a, stream);
-    case JVPFA_F16: return bwd_by_d<__half>(a, stream);
-    case JVPFA_BF16: return bwd_by_d<__nv_bfloat16>(a, stream);
+    case JVPFA_F32: return bwd_by_d<float>(a, stream, marks);
+    case JVPFA_F16: return bwd_by_d<__half>(a, stream, marks);
+    case JVPFA_BF16: return bwd_by_d<__nv_bfloat16>(a, stream, marks);
     default: return JVPFA_ERR_UNSUPPORTED;
   }
 }

@@ -35,25 +35,23 @@ inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 // Workspace layout shared by forward and backward: [0,256) status word + padding, then per-call scratch.
 constexpr size_t kStatusBytes = 256;
 
-// Optional per-kernel timing (off by default): when enabled through jvpfa_kernel_timing, every launch
-// is bracketed by CUDA events on its own stream and the durations are summed per kernel kind.
-enum KernelKind { KERNEL_FWD = 0, KERNEL_BWD_PREPROCESS = 1, KERNEL_BWD_Q = 2, KERNEL_BWD_K = 3, KERNEL_BWD_V = 4, KERNEL_KINDS = 5 };
-struct ScopedKernelTimer {
-  ScopedKernelTimer(KernelKind kind, cudaStream_t stream);
-  ~ScopedKernelTimer();
-  KernelKind kind_;
-  cudaStream_t stream_;
-  cudaEvent_t start_ = nullptr;
+// Optional caller-owned events of jvpfa_bwd_marked: mark(i) records event i on the stream when events were given.
+struct LaunchMarks {
+  void* const* events = nullptr;
+  cudaStream_t stream = nullptr;
+  void mark(int i) const {
+    if (events != nullptr) cudaEventRecord(static_cast<cudaEvent_t>(events[i]), stream);
+  }
 };
 
 int launch_fwd_sm100(const jvpfa_fwd_args& a, cudaStream_t stream);
-int launch_bwd_sm100(const jvpfa_bwd_args& a, cudaStream_t stream);
+int launch_bwd_sm100(const jvpfa_bwd_args& a, cudaStream_t stream, const LaunchMarks& marks);
 size_t bwd_sm100_workspace_bytes(const jvpfa_bwd_args& a);
 bool sm100_path_supported(int dtype, int D, int N);
 inline int sm100_padded_dim(int D) { return D <= 64 ? 64 : 128; }
 
 int launch_fwd_generic(const jvpfa_fwd_args& a, cudaStream_t stream);
-int launch_bwd_generic(const jvpfa_bwd_args& a, cudaStream_t stream);
+int launch_bwd_generic(const jvpfa_bwd_args& a, cudaStream_t stream, const LaunchMarks& marks);
 size_t bwd_generic_workspace_bytes(const jvpfa_bwd_args& a);
 
 }  // namespace jvpfa

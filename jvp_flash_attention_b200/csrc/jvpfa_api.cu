@@ -3,10 +3,9 @@
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
-#include <utility>
-#include <vector>
 #include "host_common.h"
 #include "mask_common.cuh"
+#include "sm100_prims.cuh"
 
 namespace jvpfa {
 
@@ -59,34 +58,6 @@ uint64_t wait_budget_ns() {
 }
 
 namespace {
-struct TimingState {
-  std::mutex mu;
-  bool enabled = false;
-  std::vector<std::pair<cudaEvent_t, cudaEvent_t>> pending[KERNEL_KINDS];
-};
-TimingState& timing() {
-  static TimingState t;
-  return t;
-}
-}  // namespace
-
-ScopedKernelTimer::ScopedKernelTimer(KernelKind kind, cudaStream_t stream) : kind_(kind), stream_(stream) {
-  TimingState& t = timing();
-  if (!t.enabled) return;
-  if (cudaEventCreate(&start_) != cudaSuccess) { start_ = nullptr; return; }
-  cudaEventRecord(start_, stream_);
-}
-ScopedKernelTimer::~ScopedKernelTimer() {
-  if (start_ == nullptr) return;
-  cudaEvent_t stop = nullptr;
-  if (cudaEventCreate(&stop) != cudaSuccess) { cudaEventDestroy(start_); return; }
-  cudaEventRecord(stop, stream_);
-  TimingState& t = timing();
-  std::lock_guard<std::mutex> g(t.mu);
-  t.pending[kind_].emplace_back(start_, stop);
-}
-
-namespace {
 
 // One CTA per (plane, 64-row band): thread t scans mask rows and ORs per-64-column-tile bits.
 __global__ void mask_summary_kernel(MaskView mv, int N, int Bm, uint8_t* out) {
@@ -125,6 +96,33 @@ __global__ void mask_summary_kernel(MaskView mv, int N, int Bm, uint8_t* out) {
   for (int i = threadIdx.x; i < mv.n64; i += blockDim.x)
     out[(static_cast<int64_t>(plane) * mv.n64 + qt) * mv.n64 + i] = static_cast<uint8_t>(bits[i]);
   (void)Bm;
+}
+
+// Self-test of the failure-detection path: one thread waits on an mbarrier that nothing ever arrives on. The wait
+// runs out of its budget, records WAIT_TIMEOUT_BASE + 77 in the status word and marks the CTA as poisoned; a second
+// wait then gives up after a few polls. The kernel returns normally. out: [0], [1] = results of the two waits
+// (0 = gave up), [2], [3] = their durations in microseconds.
+__global__ void selftest_timeout_kernel(int* status, uint64_t budget_ns, int* out) {
+  __shared__ uint64_t bar;
+  __shared__ int poisoned;
+  if (threadIdx.x == 0) {
+    poisoned = 0;
+    sm100::mbar_init(&bar, 1);
+    sm100::fence_mbar_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const sm100::WaitCtx w{status, &poisoned, budget_ns};
+    const uint64_t t0 = sm100::global_timer_ns();
+    const bool first = sm100::mbar_wait(&bar, 0, w, 77);
+    const uint64_t t1 = sm100::global_timer_ns();
+    const bool second = sm100::mbar_wait(&bar, 0, w, 78);
+    const uint64_t t2 = sm100::global_timer_ns();
+    out[0] = first ? 1 : 0;
+    out[1] = second ? 1 : 0;
+    out[2] = static_cast<int>((t1 - t0) / 1000);
+    out[3] = static_cast<int>((t2 - t1) / 1000);
+  }
 }
 
 int check_common(int B, int H, int N, int D, int dtype, int causal, const jvpfa_mask& mask, const void* ws, size_t ws_bytes,
@@ -216,7 +214,8 @@ int jvpfa_fwd(const jvpfa_fwd_args* a, void* stream) {
   return launch_fwd_generic(*a, s);
 }
 
-int jvpfa_bwd(const jvpfa_bwd_args* a, void* stream) {
+namespace {
+int bwd_checked(const jvpfa_bwd_args* a, void* stream, void* const* events) {
   if (a == nullptr) return JVPFA_ERR_BAD_ARG;
   int rc = check_common(a->B, a->H, a->N, a->D, a->dtype, a->causal, a->mask, a->workspace, a->workspace_bytes,
                         jvpfa_bwd_workspace_bytes(a));
@@ -240,31 +239,28 @@ int jvpfa_bwd(const jvpfa_bwd_args* a, void* stream) {
     eff.tk = eff.tv = eff.to = eff.gto = nullptr;
     eff.dtq = eff.dtk = eff.dtv = nullptr;
   }
-  if (sm100_path_supported(eff.dtype, eff.D, eff.N)) return launch_bwd_sm100(eff, s);
-  return launch_bwd_generic(eff, s);
+  LaunchMarks marks;
+  marks.events = events;
+  marks.stream = s;
+  if (sm100_path_supported(eff.dtype, eff.D, eff.N)) return launch_bwd_sm100(eff, s, marks);
+  return launch_bwd_generic(eff, s, marks);
+}
+}  // namespace
+
+int jvpfa_bwd(const jvpfa_bwd_args* a, void* stream) { return bwd_checked(a, stream, nullptr); }
+
+int jvpfa_bwd_marked(const jvpfa_bwd_args* a, void* stream, void* const* events, int32_t n_events) {
+  if (events == nullptr || n_events != 5) return JVPFA_ERR_BAD_ARG;
+  for (int i = 0; i < 5; ++i)
+    if (events[i] == nullptr) return JVPFA_ERR_BAD_ARG;
+  return bwd_checked(a, stream, events);
 }
 
-int jvpfa_kernel_timing(int enable, float* ms_out, int32_t* launches_out) {
-  TimingState& t = timing();
-  std::lock_guard<std::mutex> g(t.mu);
-  for (int k = 0; k < KERNEL_KINDS; ++k) {
-    float total = 0.f;
-    int n = 0;
-    for (auto& ev : t.pending[k]) {
-      float ms = 0.f;
-      if (cudaEventSynchronize(ev.second) == cudaSuccess && cudaEventElapsedTime(&ms, ev.first, ev.second) == cudaSuccess) {
-        total += ms;
-        ++n;
-      }
-      cudaEventDestroy(ev.first);
-      cudaEventDestroy(ev.second);
-    }
-    t.pending[k].clear();
-    if (ms_out) ms_out[k] = total;
-    if (launches_out) launches_out[k] = n;
-  }
-  t.enabled = enable != 0;
-  return JVPFA_OK;
+int jvpfa_selftest_timeout(void* workspace, int32_t budget_us, int32_t* out4, void* stream) {
+  if (workspace == nullptr || out4 == nullptr || budget_us <= 0 || budget_us > 1000000) return JVPFA_ERR_BAD_ARG;
+  selftest_timeout_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<int*>(workspace), static_cast<uint64_t>(budget_us) * 1000ull, out4);
+  return cudaGetLastError() == cudaSuccess ? JVPFA_OK : JVPFA_ERR_LAUNCH;
 }
 
 int jvpfa_read_status(void* workspace, void* stream, int32_t* detail) {
