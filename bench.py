@@ -165,10 +165,12 @@ def run_reference(args, rank):
 # take the benchmark down). Reads the copy of the reference package under baseline/_ref.
 # ------------------------------------------------------------------------------------------------
 INCUMBENT_SHAPES = (
-    # name, B, H, N, D, causal          (the reference's published tables use B=2 H=12 N=2048 D=64)
-    ("readme_shape", 2, 12, 2048, 64, False),
-    ("readme_shape_causal", 2, 12, 2048, 64, True),
-    ("headline_shape", 8, 16, 4096, 128, True),
+    # name, dtype (None = the benchmark's), B, H, N, D, causal   (the reference's published tables: B=2 H=12 N=2048 D=64)
+    ("readme_shape_bf16", "bf16", 2, 12, 2048, 64, False),
+    ("readme_shape_fp16", "fp16", 2, 12, 2048, 64, False),
+    ("readme_shape_fp32", "fp32", 2, 12, 2048, 64, False),
+    ("readme_shape_bf16_causal", "bf16", 2, 12, 2048, 64, True),
+    ("headline_shape", None, 8, 16, 4096, 128, True),
 )
 
 
@@ -189,7 +191,7 @@ def run_incumbent_child(args):
     """Child process: times the reference's dual forward (JVPAttn.fwd_dual under fwAD.dual_level) and its primal-only
     backward through its stock code path, and this library's kernels on the same shapes; prints one JSON object."""
     import torch.autograd.forward_ad as fwAD
-    out = {"dtype": args.dtype, "shapes": {}}
+    out = {"shapes": {}}
     ref_dir = os.path.join(ROOT, "baseline", "_ref")
     if not os.path.isdir(os.path.join(ref_dir, "jvp_flash_attention")):
         print(json.dumps({"unavailable": "reference-on-B200: unavailable (no copy of the reference under baseline/_ref)"}))
@@ -202,12 +204,14 @@ def run_incumbent_child(args):
         return
     from jvp_flash_attention_b200 import _lib
     dev = torch.device("cuda", 0)
-    dtype = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[args.dtype]
+    dtypes = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}
     only = set(args.incumbent_shapes.split(",")) if args.incumbent_shapes else None
-    for name, B, H, N, D, causal in INCUMBENT_SHAPES:
+    for name, dt_name, B, H, N, D, causal in INCUMBENT_SHAPES:
         if only is not None and name not in only:
             continue
-        rec = {"B": B, "H": H, "N": N, "D": D, "causal": causal}
+        dt_name = dt_name or args.dtype
+        dtype = dtypes[dt_name]
+        rec = {"B": B, "H": H, "N": N, "D": D, "causal": causal, "dtype": dt_name}
         g = torch.Generator(device=dev).manual_seed(7)
         q, k, v, tq, tk, tv, go = [torch.randn(B, H, N, D, device=dev, dtype=dtype, generator=g) for _ in range(7)]
         fwd_f, bwd_f = algorithmic_flops(B, H, N, D, causal)

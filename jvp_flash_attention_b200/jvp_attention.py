@@ -176,15 +176,15 @@ class JVPAttn:
         if q_t is None and k_t is None and v_t is None:
             return JVPAttn.fwd(q, k, v, attn_mask, dropout_p, causal, sm_scale, warp_specialize, USE_TMA,
                                verify_attn_mask)
-        _validate(q_p, k_p, v_p, attn_mask, dropout_p, causal, verify_attn_mask)
+        if dropout_p != 0.0:
+            raise NotImplementedError("Dropout is not currently supported in JVP attention.")
         q_t = torch.zeros_like(q_p) if q_t is None else q_t
         k_t = torch.zeros_like(k_p) if k_t is None else k_t
         v_t = torch.zeros_like(v_p) if v_t is None else v_t
-        q_p, k_p, v_p, q_t, k_t, v_t = (t.contiguous() for t in (q_p, k_p, v_p, q_t, k_t, v_t))
-        if sm_scale is None:
-            sm_scale = q_p.shape[-1] ** -0.5
-        o, to, _, _, _ = _DualAttention.apply(q_p, k_p, v_p, q_t, k_t, v_t, _mask_for_kernel(attn_mask, q_p),
-                                              bool(causal), float(sm_scale))
+        # ``dual`` validates, and inside torch.compile switches to the opaque operators (the reference routes its
+        # compiled dual call through its custom op in the same place, jvp_attention.py:3014-3041)
+        o, to = JVPAttn.dual(q_p, k_p, v_p, q_t, k_t, v_t, attn_mask=attn_mask, causal=causal, sm_scale=sm_scale,
+                             verify_attn_mask=verify_attn_mask)
         return fwAD.make_dual(o, to)
 
     @staticmethod

@@ -98,12 +98,15 @@ def test_cfg2_bf16_dense(dev, how):
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 def test_cfg3_causal_headline_shape(dev, dtype):
-    """B=8 H=16 N=4096 D=128 causal; first and last (b,h) slice against the oracle."""
+    """B=8 H=16 N=4096 D=128 causal; the first and the last (b,h) slice and two seeded interior ones (units that are
+    scheduled in the middle of the grid) against the oracle."""
     B, H, N, D = 8, 16, 4096, 128
     scale = 1.0
     ts = make_inputs(B, H, N, D, dtype=dtype, seed=42, scale=scale)
     got = _run_cuda(ts, dev, causal=True)
-    slices = [(0, 0), (7, 15)]
+    rng = np.random.default_rng(20261125)
+    interior = [(int(rng.integers(1, B - 1)), int(rng.integers(0, H))) for _ in range(2)]
+    slices = [(0, 0), (7, 15)] + interior
     ref = closed_form_oracle(*ts, causal=True, slices=slices)
     _compare(got, ref, TOL[dtype], slices)
 
@@ -129,6 +132,24 @@ def test_cfg4_masks_fp32(dev, kind):
     slices = [(0, 0), (1, 7)]
     ref = closed_form_oracle(*ts, attn_mask=mask, slices=slices)
     _compare(got, ref, TOL[torch.float32], slices)
+
+
+def test_cfg2_sharded_over_batch_heads(dev):
+    """The multi-GPU split on one GPU: cfg2 (bf16 B=4 H=16 N=2048 D=64) cut into 4 slices of the flattened (batch, head)
+    axis, each slice run through the CUDA path on its own, the results put together again and compared with the oracle
+    (and, bit for bit, with the unsharded run: units are independent)."""
+    from jvp_flash_attention_b200.sharding import shard_bh, shard_bounds
+    B, H, N, D = 4, 16, 2048, 64
+    ts = make_inputs(B, H, N, D, dtype=torch.bfloat16, seed=42, scale=D ** -0.25)
+    world = 4
+    parts = [_run_cuda([shard_bh(t, world, r).contiguous() for t in ts], dev) for r in range(world)]
+    whole = {n: torch.cat([p[n] for p in parts], dim=1).reshape(B, H, N, D) for n in parts[0]}
+    assert [shard_bounds(B * H, world, r) for r in range(world)] == [(0, 16), (16, 32), (32, 48), (48, 64)]
+    slices = [(0, 5), (1, 0), (2, 15), (3, 9)]           # one unit of every shard
+    ref = closed_form_oracle(*ts, slices=slices)
+    _compare(whole, ref, TOL[torch.bfloat16], slices)
+    full = _run_cuda(ts, dev)
+    assert all(torch.equal(whole[n], full[n]) for n in whole)
 
 
 # ------------------------------------------------------------------ golden vectors of the reference's own kernels
@@ -299,5 +320,67 @@ def test_torch_compile_operator(dev):
     o2, t2, g2 = run(torch.compile(fn, fullgraph=True))
     assert torch.equal(o1, o2) and torch.equal(t1, t2)
     assert all(torch.equal(a, b) for a, b in zip(g1, g2))
+    ref = closed_form_oracle(*[t.cpu() for t in ts], causal=True)          # and the compiled results against the oracle
+    got = {"O": o2, "tO": t2, **dict(zip(GRAD_NAMES, g2))}
+    _compare({n: t.double().cpu() for n, t in got.items()}, ref, TOL[torch.bfloat16])
     torch.library.opcheck(torch.ops.jvp_flash_attention_b200.attn_fwd_dual.default,
                           (*ts[:6], None, 0.125, True), test_utils=("test_schema", "test_faketensor"))
+
+
+def test_primal_only_backward_ignores_tangent_side_pointers(dev):
+    """C ABI: with tq == NULL the call is the primal-only backward and tk, tv, to, gto, dtq, dtk, dtv are ignored, even
+    when they point at real buffers: dq, dk, dv are bit-equal to the call that passes NULL for them."""
+    import ctypes as C
+    from jvp_flash_attention_b200 import _lib
+    for dtype, D in ((torch.bfloat16, 128), (torch.float32, 64)):
+        g = torch.Generator(device=dev).manual_seed(3)
+        q, k, v, go, junk = [torch.randn(1, 2, 256, D, device=dev, dtype=dtype, generator=g) for _ in range(5)]
+        s = 1.0 / math.sqrt(D)
+        mask_c = _lib.make_mask(None, 1, 2, 256)
+        o, _, lse2, mu = _lib.fwd(q, k, v, None, None, None, mask_c, None, True, s)
+        want = _lib.bwd(q, k, v, None, None, None, o, None, lse2, mu, go, None, mask_c, None, True, s)
+        outs = [torch.full_like(q, float("nan")) for _ in range(3)]
+        scratch = [torch.zeros_like(q) for _ in range(3)]
+        a = _lib.BwdArgs()
+        a.B, a.H, a.N, a.D = q.shape
+        a.dtype, a.causal, a.sm_scale = _lib.dtype_code(dtype), 1, float(s)
+        a.mask, a.mask_summary = mask_c, None
+        a.q, a.k, a.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
+        a.tq = None
+        a.tk, a.tv, a.to, a.gto = (junk.data_ptr(),) * 4            # real buffers that must not be looked at
+        a.o, a.lse2, a.mu, a.go = o.data_ptr(), lse2.data_ptr(), mu.data_ptr(), go.data_ptr()
+        a.dq, a.dk, a.dv = (t.data_ptr() for t in outs)
+        a.dtq, a.dtk, a.dtv = (t.data_ptr() for t in scratch)
+        ws = _lib.workspace(dev, _lib.lib().jvpfa_bwd_workspace_bytes(C.byref(a)))
+        a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+        _lib.check(_lib.lib().jvpfa_bwd(C.byref(a), _lib.stream_ptr(dev)))
+        torch.cuda.synchronize()
+        _lib.read_status(dev)
+        assert all(torch.equal(x, y) for x, y in zip(outs, want))
+        assert all(float(t.abs().max()) == 0.0 for t in scratch)   # and the tangent-gradient buffers stay untouched
+
+
+@pytest.mark.parametrize("how", ["func_jvp", "dual_level"])
+def test_torch_compile_fwd_dual(dev, how):
+    """``JVPAttn.fwd_dual`` on dual tensors inside a compiled graph (the reference routes this call through its custom
+    operator, jvp_attention.py:3014-3041): outputs and all six gradients against the oracle."""
+    JVPAttn, _ = _api()
+    ts = make_inputs(2, 2, 256, 64, dtype=torch.bfloat16, seed=6, scale=0.5)
+    dts = [t.to(dev) for t in ts]
+
+    def fn(q, k, v, tq, tk, tv, go, gto):
+        if how == "func_jvp":
+            o, to = torch.func.jvp(lambda a, b, c: JVPAttn.fwd_dual(a, b, c, causal=True), (q, k, v), (tq, tk, tv))
+        else:
+            with fwAD.dual_level():
+                out = JVPAttn.fwd_dual(fwAD.make_dual(q, tq), fwAD.make_dual(k, tk), fwAD.make_dual(v, tv), causal=True)
+                o, to = fwAD.unpack_dual(out)
+        return (o * go).sum() + (to * gto).sum(), o, to
+
+    leaves = [t.clone().requires_grad_(True) for t in dts[:6]]
+    loss, o, to = torch.compile(fn, fullgraph=True)(*leaves, dts[6], dts[7])
+    grads = torch.autograd.grad(loss, leaves)
+    torch.cuda.synchronize()
+    ref = closed_form_oracle(*ts, causal=True)
+    got = {"O": o.detach(), "tO": to.detach(), **dict(zip(GRAD_NAMES, grads))}
+    _compare({n: t.double().cpu() for n, t in got.items()}, ref, TOL[torch.bfloat16])
