@@ -370,21 +370,26 @@ def run_cuda(args, rank, world, local_rank):
     # ---- per-kernel durations of the same steps: caller-owned events recorded between the launches ----
     q, k, v, tq, tk, tv, gO, gtO = ts
     mask_c = _lib.make_mask(None, 1, U, N)
-    ev_f = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
-    marks = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
-    for e in ev_f + marks:
-        e.record()                                     # creates the underlying CUDA events
+    # one set of events per step, read after the last step: no synchronisation (and so no idle GPU) between the steps
+    ev_f = [[torch.cuda.Event(enable_timing=True) for _ in range(2)] for _ in range(args.steps)]
+    marks = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(args.steps)]
+    for group in ev_f + marks:
+        for e in group:
+            e.record()                                 # creates the underlying CUDA events
     names = ("fwd", "bwd_preprocess", "bwd_q", "bwd_k", "bwd_v")
     acc = dict.fromkeys(names, 0.0)
-    for _ in range(args.steps):
-        ev_f[0].record()
+    for i in range(args.steps):
+        o = torch.empty_like(q)                        # warm allocator: the forward's outputs come from its cache
+        del o
+        ev_f[i][0].record()
         o, to, lse2, mu = _lib.fwd(q, k, v, tq, tk, tv, mask_c, None, causal, s)
-        ev_f[1].record()
-        _lib.bwd(q, k, v, tq, tk, tv, o, to, lse2, mu, gO, gtO, mask_c, None, causal, s, marks=marks)
-        torch.cuda.synchronize()
-        acc["fwd"] += ev_f[0].elapsed_time(ev_f[1])
-        for i, nme in enumerate(names[1:]):
-            acc[nme] += marks[i].elapsed_time(marks[i + 1])
+        ev_f[i][1].record()
+        _lib.bwd(q, k, v, tq, tk, tv, o, to, lse2, mu, gO, gtO, mask_c, None, causal, s, marks=marks[i])
+    torch.cuda.synchronize()
+    for i in range(args.steps):
+        acc["fwd"] += ev_f[i][0].elapsed_time(ev_f[i][1])
+        for j, nme in enumerate(names[1:]):
+            acc[nme] += marks[i][j].elapsed_time(marks[i][j + 1])
     kernels = {nme: {"ms_per_launch": acc[nme] / args.steps, "launches": args.steps} for nme in names}
     lfwd_f, lbwd_f = algorithmic_flops(1, U, N, D, causal)            # this rank's slice
     fam_ms = (acc["bwd_q"] + acc["bwd_k"] + acc["bwd_v"]) / (3.0 * args.steps)

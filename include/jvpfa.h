@@ -91,8 +91,11 @@ int jvpfa_version(void);
 /* Text for a status code. */
 const char* jvpfa_error_string(int status);
 
-/* Bytes of caller-provided scratch the calls below need (always >= 256: the first 4 bytes hold
- * the device status word that bounded waits write to). */
+/* Bytes of caller-provided scratch the calls below want (always >= 256: the first 4 bytes hold the device status
+ * word that bounded waits write to; it must be zero before the first call). For fp32 inputs with a head dimension
+ * of at most 64 this is the need of the tensor-core path, which keeps bf16 hi/lo splits of its operands in the
+ * workspace (256 bytes per row and tensor); a call that is given less, but at least 256 bytes (forward) or
+ * 256 + 16 bytes per row (backward), runs the same mathematics on the CUDA cores instead. */
 size_t jvpfa_fwd_workspace_bytes(const jvpfa_fwd_args* args);
 size_t jvpfa_bwd_workspace_bytes(const jvpfa_bwd_args* args);
 

@@ -65,7 +65,16 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
   }
 }
 
-template <int D>
+__device__ __forceinline__ uint32_t pack2_residual(float a, float b, uint32_t hi) {
+  return pack2<true>(a - __uint_as_float(hi << 16), b - __uint_as_float(hi & 0xFFFF0000u));
+}
+
+// X3: fp32 inputs on the tensor cores. A pre-pass splits every fp32 operand x into two bf16 numbers hi + lo (x - hi - lo is
+// below 2^-17 |x|) and writes them side by side as one 128-column row [hi(64) | lo(64)], so the tiles have the shared-memory
+// geometry of the D = 128 kernel with the hi part in slab 0 and the lo part in slab 1; every product a b is then accumulated
+// in fp32 as a_hi b_hi + a_lo b_hi + a_hi b_lo (the terms left out are below 2^-16 |a||b|). The accumulators are 64 columns
+// wide, P and W = P o (s tS) go back to TMEM as hi and lo parts, and the outputs are written as fp32.
+template <int D, bool X3 = false>
 struct FwdCfg {
   static constexpr int BM = 128;
   static constexpr int BN = 64;
@@ -76,10 +85,12 @@ struct FwdCfg {
   static constexpr int SLAB = 128 * 128;          // bytes of one 64-column slab of a 128-row tile
   static constexpr int HALF = BN * 128;           // byte offset of tK inside a slab of the pair
   static constexpr int STAGE = PAIR_K + 2 * TILE_V;
+  static constexpr int DV = X3 ? 64 : D;      // columns of the O and T accumulators
   static constexpr int TMEM_O = 0;
-  static constexpr int TMEM_T = D;
-  static constexpr int TMEM_S = 2 * D;        // S 64 columns, tS 64 columns further (one buffer)
-  static constexpr int TMEM_P = 2 * D + 128;  // 16-bit P (32 columns) and W (32 columns further), buffer b at + 64 b
+  static constexpr int TMEM_T = DV;
+  static constexpr int TMEM_S = 2 * DV;       // S 64 columns, tS 64 columns further (one buffer)
+  static constexpr int TMEM_P = 2 * DV + 128; // 16-bit P (32 columns) and W (32 columns further), buffer b at + PBUF b;
+  static constexpr int PBUF = X3 ? 128 : 64;  // X3: P hi, P lo, W hi, W lo, 32 columns each
   static constexpr int TMEM_COLS = 512;
   static constexpr int NBAR = 4 + 4 * STAGES + 4 + 2;
   static constexpr size_t smem_bytes() { return 2 * TILE_Q + STAGES * STAGE + 2 * 2 * 128 * 4 + (NBAR + 2) * 8; }
@@ -91,15 +102,17 @@ struct FwdCfg {
 // TMEM allocation.
 // PAD: the tensors' head dimension is smaller than D (columns beyond it are zero-filled by TMA); the K steps and
 // output columns that would only see zeros are then skipped at run time.
-template <int D, bool DUAL, bool BF16, bool PAD>
+template <int D, bool DUAL, bool BF16, bool PAD, bool X3 = false>
 __global__ void __launch_bounds__(384, 1)
 fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmTQ,
                  const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmTK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmTV,
                  const FwdKParams p) {
-  using C = FwdCfg<D>;
+  using C = FwdCfg<D, X3>;
   constexpr int ST = C::STAGES;
   constexpr int SLABS = D / 64;
+  constexpr int DV = C::DV;
+  static_assert(!X3 || (D == 128 && BF16 && !PAD), "the split-fp32 mode runs on the 128-column geometry in bf16");
 
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* sQ = smem;
@@ -247,7 +260,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     constexpr uint32_t FMT = BF16 ? FMT_BF16 : FMT_F16;
     const uint32_t idesc_64 = make_idesc(FMT, 128, 64, 0, 0);
     const uint32_t idesc_128 = make_idesc(FMT, 128, 128, 0, 0);
-    const int dn = PAD ? ((p.D + 15) & ~15) : D;           // head dimension rounded up to the MMA granularity
+    const int dn = X3 ? 64 : (PAD ? ((p.D + 15) & ~15) : D);   // columns of the output products (head dimension rounded up to the MMA granularity)
     const int ksteps = dn / 16;                            // K steps of the score products that hold data
     const uint32_t idesc_pv = make_idesc(FMT, 128, dn, 0, 1);
     const uint64_t dQ = desc_kmajor_sw128(smem_u32(sQ)), dTQ = desc_kmajor_sw128(smem_u32(sTQ));
@@ -261,16 +274,36 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tc_fence_after_sync();
       const uint64_t dK = desc_kmajor_sw128(smem_u32(sK(st)));
       if (leader) {
+        if constexpr (X3) {
+          // hi hi + lo hi + hi lo: K steps 0-3 of the left (a) and right (b) operand's slab 0 (hi) or slab 1 (lo)
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k) {
-          const uint64_t o = static_cast<uint64_t>(((k >> 2) * C::SLAB + (k & 3) * 32) >> 4);
-          if (!PAD || k < ksteps) umma_ss(S_t, dQ + o, dK + o, DUAL ? idesc_128 : idesc_64, k > 0);   // [S | Q tK^T]
-        }
-        if constexpr (DUAL) {
+          for (int k = 0; k < 12; ++k) {
+            const int a_slab = (k >> 2) == 1, b_slab = (k >> 2) == 2;
+            const uint64_t oa = static_cast<uint64_t>((a_slab * C::SLAB + (k & 3) * 32) >> 4);
+            const uint64_t ob = static_cast<uint64_t>((b_slab * C::SLAB + (k & 3) * 32) >> 4);
+            umma_ss(S_t, dQ + oa, dK + ob, DUAL ? idesc_128 : idesc_64, k > 0);                        // [S | Q tK^T]
+          }
+          if constexpr (DUAL) {
+#pragma unroll
+            for (int k = 0; k < 12; ++k) {
+              const int a_slab = (k >> 2) == 1, b_slab = (k >> 2) == 2;
+              const uint64_t oa = static_cast<uint64_t>((a_slab * C::SLAB + (k & 3) * 32) >> 4);
+              const uint64_t ob = static_cast<uint64_t>((b_slab * C::SLAB + (k & 3) * 32) >> 4);
+              umma_ss(S_t + 64, dTQ + oa, dK + ob, idesc_64, 1);                                        // tS += tQ K^T
+            }
+          }
+        } else {
 #pragma unroll
           for (int k = 0; k < D / 16; ++k) {
             const uint64_t o = static_cast<uint64_t>(((k >> 2) * C::SLAB + (k & 3) * 32) >> 4);
-            if (!PAD || k < ksteps) umma_ss(S_t + 64, dTQ + o, dK + o, idesc_64, 1);                    // tS += tQ K^T
+            if (!PAD || k < ksteps) umma_ss(S_t, dQ + o, dK + o, DUAL ? idesc_128 : idesc_64, k > 0);   // [S | Q tK^T]
+          }
+          if constexpr (DUAL) {
+#pragma unroll
+            for (int k = 0; k < D / 16; ++k) {
+              const uint64_t o = static_cast<uint64_t>(((k >> 2) * C::SLAB + (k & 3) * 32) >> 4);
+              if (!PAD || k < ksteps) umma_ss(S_t + 64, dTQ + o, dK + o, idesc_64, 1);                    // tS += tQ K^T
+            }
           }
         }
         umma_commit(&s_full);
@@ -280,8 +313,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     auto issue_pv = [&](int it, bool last) {
       const int st = it % ST;
       const uint32_t ph = (it / ST) & 1;
-      const uint32_t P_t = tmem + C::TMEM_P + (it & 1) * 64;
-      const uint32_t W_t = P_t + 32;
+      const uint32_t P_t = tmem + C::TMEM_P + (it & 1) * C::PBUF;
+      const uint32_t W_t = P_t + (X3 ? 64 : 32);
       wait_all(&p_full[it & 1], (it >> 1) & 1, 21);
       wait_all(&v_full[st], ph, 22);
       tc_fence_after_sync();
@@ -293,10 +326,26 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (int k = 0; k < C::BN / 16; ++k) {
           const uint64_t ok = static_cast<uint64_t>((k * 2048) >> 4);
           const uint32_t eo = k * 8;
-          umma_ts(tmem + C::TMEM_O, P_t + eo, dV0 + ok, idesc_pv, acc0 | (k > 0));
-          if constexpr (DUAL) {
-            umma_ts(tmem + C::TMEM_T, W_t + eo, dV0 + ok, idesc_pv, acc0 | (k > 0));
-            umma_ts(tmem + C::TMEM_T, P_t + eo, dTV0 + ok, idesc_pv, 1);
+          if constexpr (X3) {
+            // the lo part of an operand in TMEM sits 32 columns after its hi part, the lo slab of V, tV one slab further
+            const uint64_t lo = static_cast<uint64_t>(C::HALF >> 4);
+            umma_ts(tmem + C::TMEM_O, P_t + eo, dV0 + ok, idesc_pv, acc0 | (k > 0));
+            umma_ts(tmem + C::TMEM_O, P_t + 32 + eo, dV0 + ok, idesc_pv, 1);
+            umma_ts(tmem + C::TMEM_O, P_t + eo, dV0 + lo + ok, idesc_pv, 1);
+            if constexpr (DUAL) {
+              umma_ts(tmem + C::TMEM_T, W_t + eo, dV0 + ok, idesc_pv, acc0 | (k > 0));
+              umma_ts(tmem + C::TMEM_T, W_t + 32 + eo, dV0 + ok, idesc_pv, 1);
+              umma_ts(tmem + C::TMEM_T, W_t + eo, dV0 + lo + ok, idesc_pv, 1);
+              umma_ts(tmem + C::TMEM_T, P_t + eo, dTV0 + ok, idesc_pv, 1);
+              umma_ts(tmem + C::TMEM_T, P_t + 32 + eo, dTV0 + ok, idesc_pv, 1);
+              umma_ts(tmem + C::TMEM_T, P_t + eo, dTV0 + lo + ok, idesc_pv, 1);
+            }
+          } else {
+            umma_ts(tmem + C::TMEM_O, P_t + eo, dV0 + ok, idesc_pv, acc0 | (k > 0));
+            if constexpr (DUAL) {
+              umma_ts(tmem + C::TMEM_T, W_t + eo, dV0 + ok, idesc_pv, acc0 | (k > 0));
+              umma_ts(tmem + C::TMEM_T, P_t + eo, dTV0 + ok, idesc_pv, 1);
+            }
           }
         }
         umma_commit(&v_empty[st]);
@@ -340,8 +389,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (!(bits & kTileAnyKept)) continue;
       const uint32_t S_t = tmem + C::TMEM_S + lane_off + 32 * wg;
       const uint32_t tS_t = S_t + 64;
-      const uint32_t P_t = tmem + C::TMEM_P + (it & 1) * 64 + lane_off + 16 * wg;   // this thread's 16 columns of P
-      const uint32_t W_t = P_t + 32;
+      const uint32_t P_t = tmem + C::TMEM_P + (it & 1) * C::PBUF + lane_off + 16 * wg;   // this thread's 16 columns of P
+      const uint32_t W_t = P_t + (X3 ? 64 : 32);
       mbar_wait(&s_full, it & 1, w, 30);
       tc_fence_after_sync();
       // scores of this thread's 32 columns in the log2 domain, two per register pair (packed fp32x2
@@ -403,7 +452,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           if (DUAL || wg == 0) {
             const uint32_t base = tmem + lane_off + (wg == 0 ? C::TMEM_O : C::TMEM_T);
 #pragma unroll
-            for (int c = 0; c < D / 32; ++c) {
+            for (int c = 0; c < DV / 32; ++c) {
               uint32_t a[32];
               tmem_ld_x32(base + c * 32, a);
               tmem_wait_ld();
@@ -427,7 +476,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
-          uint32_t pk[8], wk[8];
+          uint32_t pk[8], wk[8], pkl[8], wkl[8];
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             const int ip = 8 * c + i;
@@ -435,15 +484,21 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             const float2 pp = make_float2(fast_exp2(e.x), fast_exp2(e.y));
             l2 = __fadd2_rn(l2, pp);
             pk[i] = pack2<BF16>(pp.x, pp.y);
+            if constexpr (X3) pkl[i] = pack2_residual(pp.x, pp.y, pk[i]);
             if constexpr (DUAL) {
               const float2 tsv = __fmul2_rn(make_float2(__uint_as_float(ts[2 * ip]), __uint_as_float(ts[2 * ip + 1])), s_2);
               const float2 ww = __fmul2_rn(pp, tsv);
               mu2 = __fadd2_rn(mu2, ww);
               wk[i] = pack2<BF16>(ww.x, ww.y);
+              if constexpr (X3) wkl[i] = pack2_residual(ww.x, ww.y, wk[i]);
             }
           }
           tmem_st_x8(P_t + 8 * c, pk);
-          if constexpr (DUAL) tmem_st_x8(W_t + 8 * c, wk);
+          if constexpr (X3) tmem_st_x8(P_t + 32 + 8 * c, pkl);
+          if constexpr (DUAL) {
+            tmem_st_x8(W_t + 8 * c, wk);
+            if constexpr (X3) tmem_st_x8(W_t + 32 + 8 * c, wkl);
+          }
         }
       }
       tmem_wait_st();
@@ -469,34 +524,64 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const float mul = mu * linv;
     // Each warpgroup writes half of the head dimension; the rows go through this warp's patch of shared memory (the Q
     // tile is no longer needed: every product that reads it has completed) so that the global stores are row segments.
-    constexpr int CH = D / 64;
     if (it == 0) mbar_wait(&q_full, 0, w, 34);   // nothing was multiplied: the Q load itself may still be in flight
-    uint8_t* patch = sQ + warp * (32 * CH * 64);
-    uint32_t po[CH][16], pt[CH][16];
+    if constexpr (X3) {
+      // fp32 outputs: this warpgroup's 32 columns are 128 bytes per row
+      uint8_t* patch = sQ + warp * (32 * 128);
+      uint32_t po[2][16], pt[2][16];
+      {
+        uint32_t ov[32], tv[32];
+        if (it > 0) {
+          tmem_ld_x32(tmem + lane_off + C::TMEM_O + wg * 32, ov);
+          if constexpr (DUAL) tmem_ld_x32(tmem + lane_off + C::TMEM_T + wg * 32, tv);
+          tmem_wait_ld();
+        } else {
 #pragma unroll
-    for (int cc = 0; cc < CH; ++cc) {
-      const int c = wg * CH + cc;
-      uint32_t ov[32], tv[32];
-      if (it > 0) {
-        tmem_ld_x32(tmem + lane_off + C::TMEM_O + c * 32, ov);
-        if constexpr (DUAL) tmem_ld_x32(tmem + lane_off + C::TMEM_T + c * 32, tv);
-        tmem_wait_ld();
-      } else {
+          for (int i = 0; i < 32; ++i) { ov[i] = 0u; tv[i] = 0u; }
+        }
 #pragma unroll
-        for (int i = 0; i < 32; ++i) { ov[i] = 0u; tv[i] = 0u; }
-      }
-#pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const float o0 = __uint_as_float(ov[2 * i]) * linv, o1 = __uint_as_float(ov[2 * i + 1]) * linv;
-        po[cc][i] = pack2<BF16>(o0, o1);
-        if constexpr (DUAL) {
-          const float t0 = __uint_as_float(tv[2 * i]) * linv - mul * o0;
-          const float t1 = __uint_as_float(tv[2 * i + 1]) * linv - mul * o1;
-          pt[cc][i] = pack2<BF16>(t0, t1);
+        for (int i = 0; i < 32; ++i) {
+          const float o = __uint_as_float(ov[i]) * linv;
+          po[i >> 4][i & 15] = __float_as_uint(o);
+          if constexpr (DUAL) pt[i >> 4][i & 15] = __float_as_uint(__uint_as_float(tv[i]) * linv - mul * o);
         }
       }
-    }
-    {
+      const int col0 = wg * 32;
+      const int wrow0 = q0 + (warp & 3) * 32;
+      const size_t goff = (static_cast<size_t>(row_base) + wrow0) * p.D + col0;      // in fp32 elements
+      const int rows = N - wrow0, cols16 = 2 * (p.D - col0);                          // columns in 16-bit units
+      store_rows_via_smem<2>(patch, po, reinterpret_cast<uint16_t*>(static_cast<float*>(p.o) + goff), 2 * static_cast<size_t>(p.D),
+                             rows, cols16, lane);
+      if constexpr (DUAL)
+        store_rows_via_smem<2>(patch, pt, reinterpret_cast<uint16_t*>(static_cast<float*>(p.to) + goff),
+                               2 * static_cast<size_t>(p.D), rows, cols16, lane);
+    } else {
+      constexpr int CH = D / 64;
+      uint8_t* patch = sQ + warp * (32 * CH * 64);
+      uint32_t po[CH][16], pt[CH][16];
+#pragma unroll
+      for (int cc = 0; cc < CH; ++cc) {
+        const int c = wg * CH + cc;
+        uint32_t ov[32], tv[32];
+        if (it > 0) {
+          tmem_ld_x32(tmem + lane_off + C::TMEM_O + c * 32, ov);
+          if constexpr (DUAL) tmem_ld_x32(tmem + lane_off + C::TMEM_T + c * 32, tv);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) { ov[i] = 0u; tv[i] = 0u; }
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float o0 = __uint_as_float(ov[2 * i]) * linv, o1 = __uint_as_float(ov[2 * i + 1]) * linv;
+          po[cc][i] = pack2<BF16>(o0, o1);
+          if constexpr (DUAL) {
+            const float t0 = __uint_as_float(tv[2 * i]) * linv - mul * o0;
+            const float t1 = __uint_as_float(tv[2 * i + 1]) * linv - mul * o1;
+            pt[cc][i] = pack2<BF16>(t0, t1);
+          }
+        }
+      }
       const int col0 = wg * (D / 2);                                   // first column of this warpgroup
       const int wrow0 = q0 + (warp & 3) * 32;                          // first row of this warp
       const size_t goff = (static_cast<size_t>(row_base) + wrow0) * p.D + col0;
@@ -550,8 +635,65 @@ int launch_one(const jvpfa_fwd_args& a, cudaStream_t stream) {
   return cudaGetLastError() == cudaSuccess ? JVPFA_OK : JVPFA_ERR_LAUNCH;
 }
 
+// fp32 inputs: split pre-pass into the workspace, then the 128-column kernel in its split mode on the split tensors.
+template <bool DUAL>
+int launch_split(const jvpfa_fwd_args& a, cudaStream_t stream) {
+  using C = FwdCfg<128, true>;
+  const int64_t rows = static_cast<int64_t>(a.B) * a.H * a.N;
+  const int n_t = DUAL ? 6 : 3;
+  const void* src[6] = {a.q, a.k, a.v, a.tq, a.tk, a.tv};
+  uint16_t* dst[6];
+  uint8_t* base = static_cast<uint8_t*>(a.workspace) + kStatusBytes;
+  for (int i = 0; i < n_t; ++i) dst[i] = reinterpret_cast<uint16_t*>(base + static_cast<size_t>(i) * rows * kSplitRowBytes);
+  int rc = launch_split_fp32(src, dst, n_t, rows, a.D, stream);
+  if (rc != JVPFA_OK) return rc;
+  CUtensorMap mQ, mTQ, mK, mTK, mV, mTV;
+  const uint64_t urows = static_cast<uint64_t>(rows);
+  bool ok = make_tile_map(&mQ, dst[0], urows, 128, C::BM, JVPFA_BF16) && make_tile_map(&mK, dst[1], urows, 128, C::BN, JVPFA_BF16) &&
+            make_slab_map(&mV, dst[2], urows, 128, C::BN, JVPFA_BF16);
+  if (DUAL) {
+    ok = ok && make_tile_map(&mTQ, dst[3], urows, 128, C::BM, JVPFA_BF16) && make_tile_map(&mTK, dst[4], urows, 128, C::BN, JVPFA_BF16) &&
+         make_slab_map(&mTV, dst[5], urows, 128, C::BN, JVPFA_BF16);
+  } else {
+    mTQ = mQ; mTK = mK; mTV = mV;
+  }
+  if (!ok) return JVPFA_ERR_LAUNCH;
+  FwdKParams p{};
+  p.H = a.H; p.N = a.N; p.D = a.D; p.causal = a.causal;
+  p.s = a.sm_scale;
+  p.c1 = a.sm_scale * 1.4426950408889634f;
+  p.thresh = 8.0f;
+  p.mv.ptr = a.mask.ptr; p.mv.summary = a.mask_summary;
+  p.mv.s0 = a.mask.stride[0]; p.mv.s1 = a.mask.stride[1]; p.mv.s2 = a.mask.stride[2]; p.mv.s3 = a.mask.stride[3];
+  p.mv.kind = a.mask.kind; p.mv.dtype = a.mask.dtype;
+  p.mv.n64 = (a.N + 63) / 64;
+  p.mv.Hm = a.mask.stride[1] == 0 ? 1 : a.H;
+  p.o = a.o; p.to = a.to; p.lse2 = a.lse2; p.mu = a.mu;
+  p.status = static_cast<int*>(a.workspace);
+  p.budget_ns = wait_budget_ns();
+  auto kern = fwd_sm100_kernel<128, DUAL, true, false, true>;
+  const size_t smem = C::smem_bytes();
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
+    return JVPFA_ERR_LAUNCH;
+  dim3 grid((a.N + C::BM - 1) / C::BM, a.B * a.H);
+  kern<<<grid, 384, smem, stream>>>(mQ, mTQ, mK, mTK, mV, mTV, p);
+  return cudaGetLastError() == cudaSuccess ? JVPFA_OK : JVPFA_ERR_LAUNCH;
+}
+
 }  // namespace
 
+bool sm100_split_path_supported(int dtype, int D, int N) {
+  return dtype == JVPFA_F32 && D >= 8 && D <= 64 && (D % 8) == 0 && N >= 1;
+}
+
+size_t fwd_sm100_split_workspace_bytes(const jvpfa_fwd_args& a) {
+  const size_t rows = static_cast<size_t>(a.B) * a.H * a.N;
+  return kStatusBytes + (a.tq != nullptr ? 6 : 3) * rows * kSplitRowBytes;
+}
+
+int launch_fwd_sm100_split(const jvpfa_fwd_args& a, cudaStream_t stream) {
+  return a.tq != nullptr ? launch_split<true>(a, stream) : launch_split<false>(a, stream);
+}
 
 bool sm100_path_supported(int dtype, int D, int N) {
   // head dimensions other than 64 / 128 run on the next wider kernel with zero-filled columns

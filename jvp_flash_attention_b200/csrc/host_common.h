@@ -44,6 +44,17 @@ struct LaunchMarks {
   }
 };
 
+// fp32 inputs on the tensor cores (head dimension <= 64, a multiple of 8): every operand is split into bf16 hi + lo parts
+// by a pre-pass into the workspace and every product runs as three bf16 products accumulated in fp32.
+constexpr int kSplitMaxTensors = 8;
+constexpr size_t kSplitRowBytes = 256;   // one split row: 64 hi + 64 lo bf16 numbers
+int launch_split_fp32(const void* const* src, uint16_t* const* dst, int n_tensors, int64_t rows, int D, cudaStream_t stream);
+bool sm100_split_path_supported(int dtype, int D, int N);
+size_t fwd_sm100_split_workspace_bytes(const jvpfa_fwd_args& a);
+size_t bwd_sm100_split_workspace_bytes(const jvpfa_bwd_args& a);
+int launch_fwd_sm100_split(const jvpfa_fwd_args& a, cudaStream_t stream);
+int launch_bwd_sm100_split(const jvpfa_bwd_args& a, cudaStream_t stream, const LaunchMarks& marks);
+
 int launch_fwd_sm100(const jvpfa_fwd_args& a, cudaStream_t stream);
 int launch_bwd_sm100(const jvpfa_bwd_args& a, cudaStream_t stream, const LaunchMarks& marks);
 size_t bwd_sm100_workspace_bytes(const jvpfa_bwd_args& a);

@@ -166,8 +166,8 @@ const char* jvpfa_error_string(int status) {
   }
 }
 
-size_t jvpfa_fwd_workspace_bytes(const jvpfa_fwd_args* args) {
-  (void)args;
+size_t jvpfa_fwd_workspace_bytes(const jvpfa_fwd_args* a) {
+  if (a != nullptr && sm100_split_path_supported(a->dtype, a->D, a->N)) return fwd_sm100_split_workspace_bytes(*a);
   return kStatusBytes;
 }
 
@@ -199,8 +199,7 @@ int jvpfa_mask_summary(const jvpfa_mask* mask, int32_t B, int32_t H, int32_t N, 
 
 int jvpfa_fwd(const jvpfa_fwd_args* a, void* stream) {
   if (a == nullptr) return JVPFA_ERR_BAD_ARG;
-  int rc = check_common(a->B, a->H, a->N, a->D, a->dtype, a->causal, a->mask, a->workspace, a->workspace_bytes,
-                        jvpfa_fwd_workspace_bytes(a));
+  int rc = check_common(a->B, a->H, a->N, a->D, a->dtype, a->causal, a->mask, a->workspace, a->workspace_bytes, kStatusBytes);
   if (rc != JVPFA_OK) return rc;
   if (!a->q || !a->k || !a->v || !a->o || !a->lse2 || !a->mu) return JVPFA_ERR_BAD_ARG;
   const bool dual = a->tq != nullptr;
@@ -211,6 +210,9 @@ int jvpfa_fwd(const jvpfa_fwd_args* a, void* stream) {
     return JVPFA_ERR_BAD_ARG;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (sm100_path_supported(a->dtype, a->D, a->N)) return launch_fwd_sm100(*a, s);
+  // fp32: the tensor-core path when the workspace has room for the split operands, else the CUDA-core kernels
+  if (sm100_split_path_supported(a->dtype, a->D, a->N) && a->workspace_bytes >= fwd_sm100_split_workspace_bytes(*a))
+    return launch_fwd_sm100_split(*a, s);
   return launch_fwd_generic(*a, s);
 }
 

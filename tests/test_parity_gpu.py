@@ -58,8 +58,11 @@ def _run_cuda(ts, dev, attn_mask=None, causal=False, sm_scale=None, how="dual_le
     return {n: t.double().cpu() for n, t in out.items()}
 
 
-def _compare(got, ref, tol, slices=None, names=("O", "tO") + GRAD_NAMES):
-    worst = {}
+def _compare(got, ref, tol, slices=None, names=("O", "tO") + GRAD_NAMES, ulp_dtype=None):
+    """Max abs error of every tensor against the oracle, at most ``tol``. ``ulp_dtype``: where an oracle value is so
+    large that the output type cannot store it to within ``tol`` (its spacing there exceeds ``tol``), one unit of that
+    spacing is allowed instead -- for bf16 that is every element of magnitude 8 or more (spacing 0.0625)."""
+    worst, bad = {}, {}
     for n in names:
         r = ref[n]
         r = torch.from_numpy(r) if isinstance(r, np.ndarray) else r
@@ -67,9 +70,18 @@ def _compare(got, ref, tol, slices=None, names=("O", "tO") + GRAD_NAMES):
         if slices is not None:
             g = torch.stack([g[b, h] for b, h in slices])
         assert torch.isfinite(g).all(), f"{n} has non-finite values"
-        worst[n] = float((g - r).abs().max())
-    bad = {n: e for n, e in worst.items() if not e <= tol}
-    assert not bad, f"max abs error over tolerance {tol}: {bad} (all: {worst})"
+        err = (g - r).abs()
+        allowed = torch.full_like(err, tol)
+        if ulp_dtype is not None:
+            mant = 7 if ulp_dtype == torch.bfloat16 else 10
+            spacing = torch.exp2(torch.floor(torch.log2(r.abs().clamp_min(1e-30))) - mant)
+            allowed = torch.maximum(allowed, spacing)
+        worst[n] = float(err.max())
+        over = err > allowed
+        if bool(over.any()):
+            i = int(torch.argmax(err - allowed))
+            bad[n] = (float(err.flatten()[i]), float(r.flatten()[i]))
+    assert not bad, f"max abs error over tolerance {tol}: (error, oracle value) {bad} (all: {worst})"
     return worst
 
 
@@ -108,7 +120,8 @@ def test_cfg3_causal_headline_shape(dev, dtype):
     interior = [(int(rng.integers(1, B - 1)), int(rng.integers(0, H))) for _ in range(2)]
     slices = [(0, 0), (7, 15)] + interior
     ref = closed_form_oracle(*ts, causal=True, slices=slices)
-    _compare(got, ref, TOL[dtype], slices)
+    # N(0,1) inputs at this length give gradients of magnitude 8 and more, which bf16 stores in steps of 0.0625
+    _compare(got, ref, TOL[dtype], slices, ulp_dtype=dtype)
 
 
 @pytest.mark.parametrize("kind", ["bool", "block_sparse", "additive"])
