@@ -72,7 +72,16 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
   }
 }
 
-template <int D, int FAM>
+// The residual of a pair after its bf16 rounding `hi`, as bf16 again (the lo part of the hi/lo split).
+__device__ __forceinline__ uint32_t pack2_residual(float a, float b, uint32_t hi) {
+  return pack2<true>(a - __uint_as_float(hi << 16), b - __uint_as_float(hi & 0xFFFF0000u));
+}
+
+// SPLIT: fp32 inputs on the tensor cores. The operands arrive as rows of 128 bf16 numbers [hi(64) | lo(64)] written by the
+// split pre-pass, so the tiles have the geometry of the D = 128 kernel with the hi parts in slab 0 and the lo parts in
+// slab 1; every product a b is accumulated as a_hi b_hi + a_lo b_hi + a_hi b_lo. Accumulators are 64 columns wide, the
+// element-wise warps write hi and lo parts of their 16-bit operands, and the gradients are written as fp32.
+template <int D, int FAM, bool SPLIT = false>
 struct BwdCfg {
   static constexpr int BR = 128;                         // rows per CTA
   static constexpr int BC = 64;                          // columns per streamed tile
@@ -83,9 +92,12 @@ struct BwdCfg {
   static constexpr int PAIR = 2 * BC * D * 2;            // two stacked 64-row tiles = one 128-row operand
   static constexpr int SLAB = 128 * 128;                 // bytes of one 64-column slab of a 128-row tile
   static constexpr int HALF = BC * 128;                  // byte offset of the second tile inside a slab
+  static constexpr int DV = SPLIT ? 64 : D;                 // columns of an accumulator
   static constexpr int TMEM_ACC0 = 0;
-  static constexpr int TMEM_ACC1 = D;
-  static constexpr int TMEM_T = 2 * D;                   // score tiles, 64 columns each
+  static constexpr int TMEM_ACC1 = DV;
+  static constexpr int TMEM_T = 2 * DV;                  // score tiles, 64 columns each
+  static constexpr int EBUF = SPLIT ? 128 : 64;             // family V: columns of one buffer of 16-bit P, tP (SPLIT: hi and lo parts)
+  static constexpr int ELO = SPLIT ? (FAM == FAM_V ? 32 : 16) : 0;   // columns from the hi part of an operand to its lo part
   static constexpr int TMEM_COLS = 512;
   static constexpr int NBAR = 8 + 2 * NA + 2 * NB + 8;
   static constexpr size_t smem_bytes() { return NR * TILE_R + (NA + NB) * PAIR + 2 * BC * 16 + (NBAR + 2) * 8; }
@@ -107,16 +119,18 @@ struct BwdCfg {
 // output columns that would only see zeros are then skipped at run time.
 // DUAL = false: primal-only backward (no tangents, no gradient through a tangent output): S and X = gO V^T only,
 // dS = P (X - Delta); dQ = s dS K, dK = s dS^T Q, dV = P^T gO. Tangent tiles are neither loaded nor multiplied.
-template <int D, int FAM, bool BF16, bool PAD, bool DUAL>
+template <int D, int FAM, bool BF16, bool PAD, bool DUAL, bool SPLIT = false>
 __global__ void __launch_bounds__(352, 1)
 bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant__ CUtensorMap rm1,
                  const __grid_constant__ CUtensorMap rm2, const __grid_constant__ CUtensorMap rm3,
                  const __grid_constant__ CUtensorMap cm0, const __grid_constant__ CUtensorMap cm1,
                  const __grid_constant__ CUtensorMap cm2, const __grid_constant__ CUtensorMap cm3,
                  const BwdKParams p) {
-  using C = BwdCfg<D, FAM>;
+  using C = BwdCfg<D, FAM, SPLIT>;
   constexpr int NA = C::NA, NB = C::NB;
   constexpr int SLABS = D / 64;
+  constexpr int DV = C::DV;
+  static_assert(!SPLIT || (D == 128 && BF16 && !PAD), "the split-fp32 mode runs on the 128-column geometry in bf16");
 
   // Everything lives in dynamic shared memory so that the 128-byte-swizzled tiles can start at its
   // 1024-byte-aligned base without alignment slack: tiles, then statistics, then barriers.
@@ -278,7 +292,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
       constexpr uint32_t FMT = BF16 ? FMT_BF16 : FMT_F16;
       const uint32_t idesc_64 = make_idesc(FMT, 128, 64, 0, 0);
       const uint32_t idesc_128 = make_idesc(FMT, 128, 128, 0, 0);
-      const int dn = PAD ? ((p.D + 15) & ~15) : D;   // head dimension rounded up to the MMA granularity
+      const int dn = SPLIT ? 64 : (PAD ? ((p.D + 15) & ~15) : D);   // columns of the output products (head dimension rounded up)
       const int ksteps = dn / 16;                     // K steps of the score products that hold data
       const uint32_t idesc_out = make_idesc(FMT, 128, dn, 0, 1);
       const uint32_t TS0 = tmem + C::TMEM_T;
@@ -287,19 +301,36 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
       auto mma_nt = [&](uint32_t dst, const uint8_t* rtile, const uint8_t* ctile, uint32_t idesc, uint32_t acc) {
         // descriptors of the later K steps differ from the first only in the 16-byte-unit start address
         const uint64_t da = desc_kmajor_sw128(smem_u32(rtile)), db = desc_kmajor_sw128(smem_u32(ctile));
+        if constexpr (SPLIT) {
+          // hi hi + lo hi + hi lo: K steps 0-3 of slab 0 (hi) or slab 1 (lo) of the two operands
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k) {
-          const uint64_t o = static_cast<uint64_t>(((k >> 2) * C::SLAB + (k & 3) * 32) >> 4);
-          if (!PAD || k < ksteps) umma_ss_pred(dst, da + o, db + o, idesc, acc | (k > 0), lead);
+          for (int k = 0; k < 12; ++k) {
+            const int a_slab = (k >> 2) == 1, b_slab = (k >> 2) == 2;
+            const uint64_t oa = static_cast<uint64_t>((a_slab * C::SLAB + (k & 3) * 32) >> 4);
+            const uint64_t ob = static_cast<uint64_t>((b_slab * C::SLAB + (k & 3) * 32) >> 4);
+            umma_ss_pred(dst, da + oa, db + ob, idesc, acc | (k > 0), lead);
+          }
+        } else {
+#pragma unroll
+          for (int k = 0; k < D / 16; ++k) {
+            const uint64_t o = static_cast<uint64_t>(((k >> 2) * C::SLAB + (k & 3) * 32) >> 4);
+            if (!PAD || k < ksteps) umma_ss_pred(dst, da + o, db + o, idesc, acc | (k > 0), lead);
+          }
         }
       };
       // acc[128 x D] (+)= E[128 x 64] (TMEM, 16-bit, two column groups of 16) * Cc[64 x D]
       auto mma_out = [&](uint32_t accum, uint32_t e, const uint8_t* ctile, uint32_t acc) {
         const uint64_t db = desc_mnmajor_sw128(smem_u32(ctile), C::SLAB);
 #pragma unroll
-        for (int k = 0; k < C::BC / 16; ++k)
-          umma_ts_pred(accum, e + (FAM == FAM_V ? k * 8 : (k & 1) * 8 + (k >> 1) * 32),
-                       db + static_cast<uint64_t>((k * 2048) >> 4), idesc_out, acc | (k > 0), lead);
+        for (int k = 0; k < C::BC / 16; ++k) {
+          const uint32_t ek = e + (FAM == FAM_V ? k * 8 : (k & 1) * 8 + (k >> 1) * 32);
+          const uint64_t dk = db + static_cast<uint64_t>((k * 2048) >> 4);
+          umma_ts_pred(accum, ek, dk, idesc_out, acc | (k > 0), lead);                                        // hi hi
+          if constexpr (SPLIT) {
+            umma_ts_pred(accum, ek + C::ELO, dk, idesc_out, 1, lead);                                         // lo hi
+            umma_ts_pred(accum, ek, dk + static_cast<uint64_t>(C::SLAB >> 4), idesc_out, 1, lead);            // hi lo
+          }
+        }
       };
       // S, tS of tile i into score buffer sb
       auto issue_st = [&](int i, int sb) {
@@ -366,7 +397,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
           const bool has_next = jn < j_end;
           if constexpr (FAM == FAM_V) {
             const int buf = it % NB;
-            const uint32_t E0 = TS0 + 128 + (it & 1) * 64, E1 = E0 + 32;   // 16-bit P, tP of this tile
+            const uint32_t E0 = TS0 + 128 + (it & 1) * C::EBUF, E1 = E0 + C::EBUF / 2;   // 16-bit P, tP of this tile
             wait_all(&b_full[buf], (it / NB) & 1, 24);
             if constexpr (DUAL) {
               // P only needs S, which the first score chain completes: its two products run before tP exists
@@ -460,7 +491,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
       };
       const int sb = (FAM == FAM_V) ? (it & 1) : 0;   // family V: P, tP buffer of this tile
       const uint32_t T0 = TS0 + 32 * wg, T1 = T0 + 64;
-      const uint32_t EV0 = TS0 + 128 + sb * 64 + 16 * wg, EV1 = EV0 + 32;   // family V: this thread's 16 columns of P, tP
+      const uint32_t EV0 = TS0 + 128 + sb * C::EBUF + 16 * wg, EV1 = EV0 + C::EBUF / 2;   // family V: this thread's 16 columns of P, tP
       // family V, dual: P goes back to TMEM first (its two output products start while tP is computed)
       constexpr bool SPLIT_P = (FAM == FAM_V) && DUAL;
       mbar_wait(&st_full[0], it & 1, w, 30);
@@ -531,17 +562,25 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
 #pragma unroll
           for (int i = 0; i < 16; ++i) e0[i] = pack2<BF16>(P2[i].x, P2[i].y);
           tmem_st_x16(EV0, e0);
+          if constexpr (SPLIT) {
+            uint32_t l0[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) l0[i] = pack2_residual(P2[i].x, P2[i].y, e0[i]);
+            tmem_st_x16(EV0 + C::ELO, l0);
+          }
         }
         tmem_wait_st();
         tc_fence_before_sync();
         mbar_arrive(&pp_full[sb]);
-        uint32_t e1[16];
+        uint32_t e1[16], l1[16];
 #pragma unroll
         for (int ip = 0; ip < 16; ++ip) {
           const float2 tp = __fmul2_rn(P2[ip], __fadd2_rn(ts2[ip], stat2(1, ip)));
           e1[ip] = pack2<BF16>(tp.x, tp.y);
+          if constexpr (SPLIT) l1[ip] = pack2_residual(tp.x, tp.y, e1[ip]);
         }
         tmem_st_x16(EV1, e1);
+        if constexpr (SPLIT) tmem_st_x16(EV1 + C::ELO, l1);
       } else if constexpr (FAM == FAM_V) {
         // P (and tP = P (ts - mu)) into this tile's 16-bit buffer, which the output products of tile it - 2 read
         if (it >= 2) {
@@ -550,17 +589,19 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
         }
 #pragma unroll
         for (int hch = 0; hch < 2; ++hch) {
-          uint32_t e0[8], e1[8];
+          uint32_t e0[8], e1[8], l0[8];
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             const int ip = 8 * hch + i;
             e0[i] = pack2<BF16>(P2[ip].x, P2[ip].y);
+            if constexpr (SPLIT) l0[i] = pack2_residual(P2[ip].x, P2[ip].y, e0[i]);
             if constexpr (DUAL) {
               const float2 tp = __fmul2_rn(P2[ip], __fadd2_rn(ts2[ip], stat2(1, ip)));
               e1[i] = pack2<BF16>(tp.x, tp.y);
             }
           }
           tmem_st_x8(EV0 + 8 * hch, e0);
+          if constexpr (SPLIT) tmem_st_x8(EV0 + C::ELO + 8 * hch, l0);
           if constexpr (DUAL) tmem_st_x8(EV1 + 8 * hch, e1);
         }
       } else {
@@ -572,23 +613,33 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
           // phase 2a, as soon as A is complete: dtS, and everything of dS that does not need X (kept in ts2)
           mbar_wait(&a_ready, it & 1, w, 33);
           tc_fence_after_sync();
+          // (split mode: the lo parts go into the upper half of this thread's 32 columns, so all of them are read first)
+          uint32_t ar[2][16];
+          if constexpr (SPLIT) {
+            tmem_ld_x16(TA, ar[0]);
+            tmem_ld_x16(TA + 16, ar[1]);
+            tmem_wait_ld();
+          }
 #pragma unroll
           for (int hch = 0; hch < 2; ++hch) {
-            uint32_t ar[16];
-            tmem_ld_x16(TA + 16 * hch, ar);
-            tmem_wait_ld();
-            uint32_t e1[8];
+            if constexpr (!SPLIT) {
+              tmem_ld_x16(TA + 16 * hch, ar[hch]);
+              tmem_wait_ld();
+            }
+            uint32_t e1[8], l1[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
               const int ip = 8 * hch + i;
-              const float2 A = make_float2(__uint_as_float(ar[2 * i]), __uint_as_float(ar[2 * i + 1]));
+              const float2 A = make_float2(__uint_as_float(ar[hch][2 * i]), __uint_as_float(ar[hch][2 * i + 1]));
               const float2 d = __fadd2_rn(A, stat2(3, ip));                       // A - a
               float2 t = __ffma2_rn(ts2[ip], d, stat2(2, ip));                    // ts (A - a) - Delta
               ts2[ip] = __ffma2_rn(stat2(1, ip), A, t);                           // - mu A
               const float2 dts = __fmul2_rn(P2[ip], d);
               e1[i] = pack2<BF16>(dts.x, dts.y);
+              if constexpr (SPLIT) l1[i] = pack2_residual(dts.x, dts.y, e1[i]);
             }
             tmem_st_x8(TA + 8 * hch, e1);
+            if constexpr (SPLIT) tmem_st_x8(TA + C::ELO + 8 * hch, l1);
           }
           tmem_wait_st();
           tc_fence_before_sync();
@@ -596,39 +647,57 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
           // phase 2b, when X is complete
           mbar_wait(&xa_full, it & 1, w, 31);
           tc_fence_after_sync();
+          uint32_t xr[2][16];
+          if constexpr (SPLIT) {
+            tmem_ld_x16(TX, xr[0]);
+            tmem_ld_x16(TX + 16, xr[1]);
+            tmem_wait_ld();
+          }
 #pragma unroll
           for (int hch = 0; hch < 2; ++hch) {
-            uint32_t xr[16];
-            tmem_ld_x16(TX + 16 * hch, xr);
-            tmem_wait_ld();
-            uint32_t e0[8];
+            if constexpr (!SPLIT) {
+              tmem_ld_x16(TX + 16 * hch, xr[hch]);
+              tmem_wait_ld();
+            }
+            uint32_t e0[8], l0[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
               const int ip = 8 * hch + i;
-              const float2 X = make_float2(__uint_as_float(xr[2 * i]), __uint_as_float(xr[2 * i + 1]));
+              const float2 X = make_float2(__uint_as_float(xr[hch][2 * i]), __uint_as_float(xr[hch][2 * i + 1]));
               const float2 ds = __fmul2_rn(P2[ip], __fadd2_rn(X, ts2[ip]));
               e0[i] = pack2<BF16>(ds.x, ds.y);
+              if constexpr (SPLIT) l0[i] = pack2_residual(ds.x, ds.y, e0[i]);
             }
             tmem_st_x8(TX + 8 * hch, e0);
+            if constexpr (SPLIT) tmem_st_x8(TX + C::ELO + 8 * hch, l0);
           }
         } else {
           mbar_wait(&xa_full, it & 1, w, 31);
           tc_fence_after_sync();
           const uint32_t TX = (FAM == FAM_Q) ? T3 : T2;
+          uint32_t xr[2][16];
+          if constexpr (SPLIT) {
+            tmem_ld_x16(TX, xr[0]);
+            tmem_ld_x16(TX + 16, xr[1]);
+            tmem_wait_ld();
+          }
 #pragma unroll
           for (int hch = 0; hch < 2; ++hch) {
-            uint32_t xr[16];
-            tmem_ld_x16(TX + 16 * hch, xr);
-            tmem_wait_ld();
-            uint32_t e0[8];
+            if constexpr (!SPLIT) {
+              tmem_ld_x16(TX + 16 * hch, xr[hch]);
+              tmem_wait_ld();
+            }
+            uint32_t e0[8], l0[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
               const int ip = 8 * hch + i;
-              const float2 X = make_float2(__uint_as_float(xr[2 * i]), __uint_as_float(xr[2 * i + 1]));
+              const float2 X = make_float2(__uint_as_float(xr[hch][2 * i]), __uint_as_float(xr[hch][2 * i + 1]));
               const float2 ds = __fmul2_rn(P2[ip], __fadd2_rn(X, stat2(2, ip)));  // P (X - Delta)
               e0[i] = pack2<BF16>(ds.x, ds.y);
+              if constexpr (SPLIT) l0[i] = pack2_residual(ds.x, ds.y, e0[i]);
             }
             tmem_st_x8(T2 + 8 * hch, e0);
+            if constexpr (SPLIT) tmem_st_x8(T2 + C::ELO + 8 * hch, l0);
           }
         }
       }
@@ -641,30 +710,59 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
     tc_fence_after_sync();
     // Each warpgroup writes half of the head dimension; the rows go through this warp's patch of shared memory (the
     // first row-side tile is no longer needed: every product has completed) so that the global stores are row segments.
-    constexpr int CH = D / 64;
     if (it == 0) mbar_wait(&r_full, 0, w, 36);   // nothing was multiplied: the row-side loads may still be in flight
-    uint8_t* patch = sR(0) + warp * (32 * CH * 64);
-    uint32_t q0[CH][16], q1[CH][16];
+    if constexpr (SPLIT) {
+      // fp32 outputs: this warpgroup's 32 columns are 128 bytes per row
+      uint8_t* patch = sR(0) + warp * (32 * 128);
+      uint32_t q0[2][16], q1[2][16];
+      {
+        uint32_t a0[32], a1[32];
+        if (it > 0) {
+          tmem_ld_x32(tmem + lane_off + C::TMEM_ACC0 + wg * 32, a0);
+          if constexpr (DUAL) tmem_ld_x32(tmem + lane_off + C::TMEM_ACC1 + wg * 32, a1);
+          tmem_wait_ld();
+        } else {
 #pragma unroll
-    for (int cc = 0; cc < CH; ++cc) {
-      const int c = wg * CH + cc;
-      uint32_t a0[32], a1[32];
-      if (it > 0) {
-        tmem_ld_x32(tmem + lane_off + C::TMEM_ACC0 + c * 32, a0);
-        if constexpr (DUAL) tmem_ld_x32(tmem + lane_off + C::TMEM_ACC1 + c * 32, a1);
-        tmem_wait_ld();
-      } else {
+          for (int i = 0; i < 32; ++i) { a0[i] = 0u; a1[i] = 0u; }
+        }
 #pragma unroll
-        for (int i = 0; i < 32; ++i) { a0[i] = 0u; a1[i] = 0u; }
+        for (int i = 0; i < 32; ++i) {
+          q0[i >> 4][i & 15] = __float_as_uint(__uint_as_float(a0[i]) * p.out_scale);
+          if constexpr (DUAL) q1[i >> 4][i & 15] = __float_as_uint(__uint_as_float(a1[i]) * p.out_scale);
+        }
       }
+      const int col0 = wg * 32;
+      const int wrow0 = r0 + (warp & 3) * 32;
+      const size_t goff = (static_cast<size_t>(row_base) + wrow0) * p.D + col0;      // in fp32 elements
+      const int rows = N - wrow0, cols16 = 2 * (p.D - col0);                          // columns in 16-bit units
+      store_rows_via_smem<2>(patch, q0, reinterpret_cast<uint16_t*>(static_cast<float*>(p.out0) + goff),
+                             2 * static_cast<size_t>(p.D), rows, cols16, lane);
+      if constexpr (DUAL)
+        store_rows_via_smem<2>(patch, q1, reinterpret_cast<uint16_t*>(static_cast<float*>(p.out1) + goff),
+                               2 * static_cast<size_t>(p.D), rows, cols16, lane);
+    } else {
+      constexpr int CH = D / 64;
+      uint8_t* patch = sR(0) + warp * (32 * CH * 64);
+      uint32_t q0[CH][16], q1[CH][16];
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        q0[cc][i] = pack2<BF16>(__uint_as_float(a0[2 * i]) * p.out_scale, __uint_as_float(a0[2 * i + 1]) * p.out_scale);
-        if constexpr (DUAL)
-          q1[cc][i] = pack2<BF16>(__uint_as_float(a1[2 * i]) * p.out_scale, __uint_as_float(a1[2 * i + 1]) * p.out_scale);
+      for (int cc = 0; cc < CH; ++cc) {
+        const int c = wg * CH + cc;
+        uint32_t a0[32], a1[32];
+        if (it > 0) {
+          tmem_ld_x32(tmem + lane_off + C::TMEM_ACC0 + c * 32, a0);
+          if constexpr (DUAL) tmem_ld_x32(tmem + lane_off + C::TMEM_ACC1 + c * 32, a1);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) { a0[i] = 0u; a1[i] = 0u; }
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          q0[cc][i] = pack2<BF16>(__uint_as_float(a0[2 * i]) * p.out_scale, __uint_as_float(a0[2 * i + 1]) * p.out_scale);
+          if constexpr (DUAL)
+            q1[cc][i] = pack2<BF16>(__uint_as_float(a1[2 * i]) * p.out_scale, __uint_as_float(a1[2 * i + 1]) * p.out_scale);
+        }
       }
-    }
-    {
       const int col0 = wg * (D / 2);
       const int wrow0 = r0 + (warp & 3) * 32;
       const size_t goff = (static_cast<size_t>(row_base) + wrow0) * p.D + col0;
@@ -729,9 +827,43 @@ __global__ void bwd_preprocess_kernel(const uint16_t* __restrict__ o, const uint
   }
 }
 
-template <int D, int FAM, bool BF16, bool PAD, bool DUAL>
-int launch_family(const jvpfa_bwd_args& a, const float4* stats, cudaStream_t stream) {
-  using C = BwdCfg<D, FAM>;
+// The same statistics from fp32 tensors (head dimension <= 64): half a warp per row, one float4 per lane and tensor.
+__global__ void bwd_preprocess_f32_kernel(const float* __restrict__ o, const float* __restrict__ to,
+                                          const float* __restrict__ go, const float* __restrict__ gto,
+                                          const float* __restrict__ lse2, const float* __restrict__ mu,
+                                          float4* __restrict__ stats, int64_t rows, int D) {
+  const int lane = threadIdx.x & 31, l16 = lane & 15;
+  const int64_t row = (static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5)) * 2 + (lane >> 4);
+  const bool live = row < rows;
+  float s_go_o = 0.f, s_gto_to = 0.f, s_gto_o = 0.f;
+  if (live && l16 * 4 < D) {
+    const size_t idx = static_cast<size_t>(row) * D + l16 * 4;
+    const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4 ov = *reinterpret_cast<const float4*>(o + idx);
+    const float4 gov = *reinterpret_cast<const float4*>(go + idx);
+    const float4 tov = gto ? *reinterpret_cast<const float4*>(to + idx) : z;
+    const float4 gtov = gto ? *reinterpret_cast<const float4*>(gto + idx) : z;
+    s_go_o = gov.x * ov.x + gov.y * ov.y + gov.z * ov.z + gov.w * ov.w;
+    s_gto_to = gtov.x * tov.x + gtov.y * tov.y + gtov.z * tov.z + gtov.w * tov.w;
+    s_gto_o = gtov.x * ov.x + gtov.y * ov.y + gtov.z * ov.z + gtov.w * ov.w;
+  }
+#pragma unroll
+  for (int off = 8; off > 0; off >>= 1) {
+    s_go_o += __shfl_xor_sync(0xFFFFFFFFu, s_go_o, off);
+    s_gto_to += __shfl_xor_sync(0xFFFFFFFFu, s_gto_to, off);
+    s_gto_o += __shfl_xor_sync(0xFFFFFFFFu, s_gto_o, off);
+  }
+  if (l16 == 0 && live) {
+    const float m = mu[row];
+    stats[row] = make_float4(lse2[row], m, s_go_o + s_gto_to - s_gto_o * m, s_gto_o);
+  }
+}
+
+// `a` holds the operands the tensor maps are built on: in the split-fp32 mode (SPLIT) the bf16 hi/lo tensors of the
+// pre-pass with 128 columns, and `real_D` is the head dimension of the outputs.
+template <int D, int FAM, bool BF16, bool PAD, bool DUAL, bool SPLIT = false>
+int launch_family(const jvpfa_bwd_args& a, const float4* stats, cudaStream_t stream, int real_D = 0) {
+  using C = BwdCfg<D, FAM, SPLIT>;
   const uint64_t rows = static_cast<uint64_t>(a.B) * a.H * a.N;
   const void* rsrc[4];
   const void* csrc[4];
@@ -760,7 +892,7 @@ int launch_family(const jvpfa_bwd_args& a, const float4* stats, cudaStream_t str
     if (!make_tile_map(&cm[i], csrc[i], rows, a.D, C::BC, a.dtype)) return JVPFA_ERR_LAUNCH;
   }
   BwdKParams p{};
-  p.H = a.H; p.N = a.N; p.D = a.D; p.causal = a.causal;
+  p.H = a.H; p.N = a.N; p.D = SPLIT ? real_D : a.D; p.causal = a.causal;
   p.s = a.sm_scale;
   p.c1 = a.sm_scale * 1.4426950408889634f;
   p.out_scale = out_scale;
@@ -773,7 +905,7 @@ int launch_family(const jvpfa_bwd_args& a, const float4* stats, cudaStream_t str
   p.out0 = out0; p.out1 = out1;
   p.status = static_cast<int*>(a.workspace);
   p.budget_ns = wait_budget_ns();
-  auto kern = bwd_sm100_kernel<D, FAM, BF16, PAD, DUAL>;
+  auto kern = bwd_sm100_kernel<D, FAM, BF16, PAD, DUAL, SPLIT>;
   const size_t smem = C::smem_bytes();
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
     return JVPFA_ERR_LAUNCH;
@@ -811,8 +943,55 @@ int launch_all(const jvpfa_bwd_args& a, cudaStream_t stream, const LaunchMarks& 
   return dual ? three(std::true_type{}, std::true_type{}) : three(std::true_type{}, std::false_type{});
 }
 
+// fp32 inputs: statistics from the fp32 tensors, split pre-pass of the eight (primal-only: four) MMA operands into the
+// workspace, then the three family kernels in their split mode on the split tensors. Workspace: status block, statistics,
+// split tensors.
+template <bool DUAL>
+int launch_split(const jvpfa_bwd_args& a, cudaStream_t stream, const LaunchMarks& marks) {
+  const int64_t rows = static_cast<int64_t>(a.B) * a.H * a.N;
+  uint8_t* ws = static_cast<uint8_t*>(a.workspace);
+  float4* stats = reinterpret_cast<float4*>(ws + kStatusBytes);
+  uint8_t* base = ws + kStatusBytes + align_up(static_cast<size_t>(rows) * sizeof(float4), 256);
+  const int n_t = DUAL ? 8 : 4;
+  const void* src[8] = {a.q, a.k, a.v, a.go, a.tq, a.tk, a.tv, a.gto};
+  uint16_t* dst[8];
+  for (int i = 0; i < n_t; ++i) dst[i] = reinterpret_cast<uint16_t*>(base + static_cast<size_t>(i) * rows * kSplitRowBytes);
+  marks.mark(0);
+  const int warps_per_block = 8;   // two rows per warp
+  const unsigned blocks = static_cast<unsigned>((rows + 2 * warps_per_block - 1) / (2 * warps_per_block));
+  bwd_preprocess_f32_kernel<<<blocks, warps_per_block * 32, 0, stream>>>(
+      static_cast<const float*>(a.o), static_cast<const float*>(a.to), static_cast<const float*>(a.go),
+      static_cast<const float*>(a.gto), a.lse2, a.mu, stats, rows, a.D);
+  if (cudaGetLastError() != cudaSuccess) return JVPFA_ERR_LAUNCH;
+  int rc = launch_split_fp32(src, dst, n_t, rows, a.D, stream);
+  if (rc != JVPFA_OK) return rc;
+  jvpfa_bwd_args m = a;      // what the tensor maps are built on
+  m.D = 128;
+  m.dtype = JVPFA_BF16;
+  m.q = dst[0]; m.k = dst[1]; m.v = dst[2]; m.go = dst[3];
+  if (DUAL) { m.tq = dst[4]; m.tk = dst[5]; m.tv = dst[6]; m.gto = dst[7]; }
+  marks.mark(1);
+  rc = launch_family<128, FAM_Q, true, false, DUAL, true>(m, stats, stream, a.D);
+  if (rc != JVPFA_OK) return rc;
+  marks.mark(2);
+  rc = launch_family<128, FAM_K, true, false, DUAL, true>(m, stats, stream, a.D);
+  if (rc != JVPFA_OK) return rc;
+  marks.mark(3);
+  rc = launch_family<128, FAM_V, true, false, DUAL, true>(m, stats, stream, a.D);
+  marks.mark(4);
+  return rc;
+}
+
 }  // namespace
 
+size_t bwd_sm100_split_workspace_bytes(const jvpfa_bwd_args& a) {
+  const size_t rows = static_cast<size_t>(a.B) * a.H * a.N;
+  return kStatusBytes + align_up(rows * sizeof(float4), 256) + (a.tq != nullptr ? 8 : 4) * rows * kSplitRowBytes;
+}
+
+int launch_bwd_sm100_split(const jvpfa_bwd_args& a, cudaStream_t stream, const LaunchMarks& marks) {
+  return a.tq != nullptr ? launch_split<true>(a, stream, marks) : launch_split<false>(a, stream, marks);
+}
 
 size_t bwd_sm100_workspace_bytes(const jvpfa_bwd_args& a) {
   return kStatusBytes + static_cast<size_t>(a.B) * a.H * a.N * sizeof(float4);

@@ -69,12 +69,13 @@ __device__ __forceinline__ uint32_t pack2_residual(float a, float b, uint32_t hi
   return pack2<true>(a - __uint_as_float(hi << 16), b - __uint_as_float(hi & 0xFFFF0000u));
 }
 
-// X3: fp32 inputs on the tensor cores. A pre-pass splits every fp32 operand x into two bf16 numbers hi + lo (x - hi - lo is
-// below 2^-17 |x|) and writes them side by side as one 128-column row [hi(64) | lo(64)], so the tiles have the shared-memory
-// geometry of the D = 128 kernel with the hi part in slab 0 and the lo part in slab 1; every product a b is then accumulated
-// in fp32 as a_hi b_hi + a_lo b_hi + a_hi b_lo (the terms left out are below 2^-16 |a||b|). The accumulators are 64 columns
-// wide, P and W = P o (s tS) go back to TMEM as hi and lo parts, and the outputs are written as fp32.
-template <int D, bool X3 = false>
+// SPLIT: fp32 inputs on the tensor cores. A pre-pass splits every fp32 operand x into two bf16 numbers hi + lo (x - hi - lo
+// is below 2^-18 |x|) and writes them side by side as one 128-column row [hi(64) | lo(64)], so the tiles have the
+// shared-memory geometry of the D = 128 kernel with the hi part in slab 0 and the lo part in slab 1; every product a b is
+// then accumulated in fp32 as a_hi b_hi + a_lo b_hi + a_hi b_lo (what is left out is of the order 2^-18 |a||b|; an fp16 lo
+// part would carry three more bits, but one product cannot take an fp16 operand against a bf16 one). The accumulators are 64
+// columns wide, P and W = P o (s tS) go back to TMEM as hi and lo parts, and the outputs are written as fp32.
+template <int D, bool SPLIT = false>
 struct FwdCfg {
   static constexpr int BM = 128;
   static constexpr int BN = 64;
@@ -85,12 +86,12 @@ struct FwdCfg {
   static constexpr int SLAB = 128 * 128;          // bytes of one 64-column slab of a 128-row tile
   static constexpr int HALF = BN * 128;           // byte offset of tK inside a slab of the pair
   static constexpr int STAGE = PAIR_K + 2 * TILE_V;
-  static constexpr int DV = X3 ? 64 : D;      // columns of the O and T accumulators
+  static constexpr int DV = SPLIT ? 64 : D;      // columns of the O and T accumulators
   static constexpr int TMEM_O = 0;
   static constexpr int TMEM_T = DV;
   static constexpr int TMEM_S = 2 * DV;       // S 64 columns, tS 64 columns further (one buffer)
   static constexpr int TMEM_P = 2 * DV + 128; // 16-bit P (32 columns) and W (32 columns further), buffer b at + PBUF b;
-  static constexpr int PBUF = X3 ? 128 : 64;  // X3: P hi, P lo, W hi, W lo, 32 columns each
+  static constexpr int PBUF = SPLIT ? 128 : 64;  // SPLIT: P hi, P lo, W hi, W lo, 32 columns each
   static constexpr int TMEM_COLS = 512;
   static constexpr int NBAR = 4 + 4 * STAGES + 4 + 2;
   static constexpr size_t smem_bytes() { return 2 * TILE_Q + STAGES * STAGE + 2 * 2 * 128 * 4 + (NBAR + 2) * 8; }
@@ -102,17 +103,17 @@ struct FwdCfg {
 // TMEM allocation.
 // PAD: the tensors' head dimension is smaller than D (columns beyond it are zero-filled by TMA); the K steps and
 // output columns that would only see zeros are then skipped at run time.
-template <int D, bool DUAL, bool BF16, bool PAD, bool X3 = false>
+template <int D, bool DUAL, bool BF16, bool PAD, bool SPLIT = false>
 __global__ void __launch_bounds__(384, 1)
 fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmTQ,
                  const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmTK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmTV,
                  const FwdKParams p) {
-  using C = FwdCfg<D, X3>;
+  using C = FwdCfg<D, SPLIT>;
   constexpr int ST = C::STAGES;
   constexpr int SLABS = D / 64;
   constexpr int DV = C::DV;
-  static_assert(!X3 || (D == 128 && BF16 && !PAD), "the split-fp32 mode runs on the 128-column geometry in bf16");
+  static_assert(!SPLIT || (D == 128 && BF16 && !PAD), "the split-fp32 mode runs on the 128-column geometry in bf16");
 
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* sQ = smem;
@@ -260,7 +261,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     constexpr uint32_t FMT = BF16 ? FMT_BF16 : FMT_F16;
     const uint32_t idesc_64 = make_idesc(FMT, 128, 64, 0, 0);
     const uint32_t idesc_128 = make_idesc(FMT, 128, 128, 0, 0);
-    const int dn = X3 ? 64 : (PAD ? ((p.D + 15) & ~15) : D);   // columns of the output products (head dimension rounded up to the MMA granularity)
+    const int dn = SPLIT ? 64 : (PAD ? ((p.D + 15) & ~15) : D);   // columns of the output products (head dimension rounded up to the MMA granularity)
     const int ksteps = dn / 16;                            // K steps of the score products that hold data
     const uint32_t idesc_pv = make_idesc(FMT, 128, dn, 0, 1);
     const uint64_t dQ = desc_kmajor_sw128(smem_u32(sQ)), dTQ = desc_kmajor_sw128(smem_u32(sTQ));
@@ -274,7 +275,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tc_fence_after_sync();
       const uint64_t dK = desc_kmajor_sw128(smem_u32(sK(st)));
       if (leader) {
-        if constexpr (X3) {
+        if constexpr (SPLIT) {
           // hi hi + lo hi + hi lo: K steps 0-3 of the left (a) and right (b) operand's slab 0 (hi) or slab 1 (lo)
 #pragma unroll
           for (int k = 0; k < 12; ++k) {
@@ -314,7 +315,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const int st = it % ST;
       const uint32_t ph = (it / ST) & 1;
       const uint32_t P_t = tmem + C::TMEM_P + (it & 1) * C::PBUF;
-      const uint32_t W_t = P_t + (X3 ? 64 : 32);
+      const uint32_t W_t = P_t + (SPLIT ? 64 : 32);
       wait_all(&p_full[it & 1], (it >> 1) & 1, 21);
       wait_all(&v_full[st], ph, 22);
       tc_fence_after_sync();
@@ -326,19 +327,19 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (int k = 0; k < C::BN / 16; ++k) {
           const uint64_t ok = static_cast<uint64_t>((k * 2048) >> 4);
           const uint32_t eo = k * 8;
-          if constexpr (X3) {
+          if constexpr (SPLIT) {
             // the lo part of an operand in TMEM sits 32 columns after its hi part, the lo slab of V, tV one slab further
             const uint64_t lo = static_cast<uint64_t>(C::HALF >> 4);
-            umma_ts(tmem + C::TMEM_O, P_t + eo, dV0 + ok, idesc_pv, acc0 | (k > 0));
-            umma_ts(tmem + C::TMEM_O, P_t + 32 + eo, dV0 + ok, idesc_pv, 1);
-            umma_ts(tmem + C::TMEM_O, P_t + eo, dV0 + lo + ok, idesc_pv, 1);
+            // acc += e_hi c_hi + e_lo c_hi + e_hi c_lo
+            auto three = [&](uint32_t accum, uint32_t e, uint64_t c, uint32_t first_acc) {
+              umma_ts(accum, e, c, idesc_pv, first_acc);
+              umma_ts(accum, e + 32, c, idesc_pv, 1);
+              umma_ts(accum, e, c + lo, idesc_pv, 1);
+            };
+            three(tmem + C::TMEM_O, P_t + eo, dV0 + ok, acc0 | (k > 0));
             if constexpr (DUAL) {
-              umma_ts(tmem + C::TMEM_T, W_t + eo, dV0 + ok, idesc_pv, acc0 | (k > 0));
-              umma_ts(tmem + C::TMEM_T, W_t + 32 + eo, dV0 + ok, idesc_pv, 1);
-              umma_ts(tmem + C::TMEM_T, W_t + eo, dV0 + lo + ok, idesc_pv, 1);
-              umma_ts(tmem + C::TMEM_T, P_t + eo, dTV0 + ok, idesc_pv, 1);
-              umma_ts(tmem + C::TMEM_T, P_t + 32 + eo, dTV0 + ok, idesc_pv, 1);
-              umma_ts(tmem + C::TMEM_T, P_t + eo, dTV0 + lo + ok, idesc_pv, 1);
+              three(tmem + C::TMEM_T, W_t + eo, dV0 + ok, acc0 | (k > 0));
+              three(tmem + C::TMEM_T, P_t + eo, dTV0 + ok, 1);
             }
           } else {
             umma_ts(tmem + C::TMEM_O, P_t + eo, dV0 + ok, idesc_pv, acc0 | (k > 0));
@@ -390,7 +391,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const uint32_t S_t = tmem + C::TMEM_S + lane_off + 32 * wg;
       const uint32_t tS_t = S_t + 64;
       const uint32_t P_t = tmem + C::TMEM_P + (it & 1) * C::PBUF + lane_off + 16 * wg;   // this thread's 16 columns of P
-      const uint32_t W_t = P_t + (X3 ? 64 : 32);
+      const uint32_t W_t = P_t + (SPLIT ? 64 : 32);
       mbar_wait(&s_full, it & 1, w, 30);
       tc_fence_after_sync();
       // scores of this thread's 32 columns in the log2 domain, two per register pair (packed fp32x2
@@ -484,20 +485,20 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             const float2 pp = make_float2(fast_exp2(e.x), fast_exp2(e.y));
             l2 = __fadd2_rn(l2, pp);
             pk[i] = pack2<BF16>(pp.x, pp.y);
-            if constexpr (X3) pkl[i] = pack2_residual(pp.x, pp.y, pk[i]);
+            if constexpr (SPLIT) pkl[i] = pack2_residual(pp.x, pp.y, pk[i]);
             if constexpr (DUAL) {
               const float2 tsv = __fmul2_rn(make_float2(__uint_as_float(ts[2 * ip]), __uint_as_float(ts[2 * ip + 1])), s_2);
               const float2 ww = __fmul2_rn(pp, tsv);
               mu2 = __fadd2_rn(mu2, ww);
               wk[i] = pack2<BF16>(ww.x, ww.y);
-              if constexpr (X3) wkl[i] = pack2_residual(ww.x, ww.y, wk[i]);
+              if constexpr (SPLIT) wkl[i] = pack2_residual(ww.x, ww.y, wk[i]);
             }
           }
           tmem_st_x8(P_t + 8 * c, pk);
-          if constexpr (X3) tmem_st_x8(P_t + 32 + 8 * c, pkl);
+          if constexpr (SPLIT) tmem_st_x8(P_t + 32 + 8 * c, pkl);
           if constexpr (DUAL) {
             tmem_st_x8(W_t + 8 * c, wk);
-            if constexpr (X3) tmem_st_x8(W_t + 32 + 8 * c, wkl);
+            if constexpr (SPLIT) tmem_st_x8(W_t + 32 + 8 * c, wkl);
           }
         }
       }
@@ -525,7 +526,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     // Each warpgroup writes half of the head dimension; the rows go through this warp's patch of shared memory (the Q
     // tile is no longer needed: every product that reads it has completed) so that the global stores are row segments.
     if (it == 0) mbar_wait(&q_full, 0, w, 34);   // nothing was multiplied: the Q load itself may still be in flight
-    if constexpr (X3) {
+    if constexpr (SPLIT) {
       // fp32 outputs: this warpgroup's 32 columns are 128 bytes per row
       uint8_t* patch = sQ + warp * (32 * 128);
       uint32_t po[2][16], pt[2][16];

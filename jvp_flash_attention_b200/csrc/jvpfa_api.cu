@@ -174,6 +174,7 @@ size_t jvpfa_fwd_workspace_bytes(const jvpfa_fwd_args* a) {
 size_t jvpfa_bwd_workspace_bytes(const jvpfa_bwd_args* a) {
   if (a == nullptr) return kStatusBytes;
   if (sm100_path_supported(a->dtype, a->D, a->N)) return bwd_sm100_workspace_bytes(*a);
+  if (sm100_split_path_supported(a->dtype, a->D, a->N)) return bwd_sm100_split_workspace_bytes(*a);
   return bwd_generic_workspace_bytes(*a);
 }
 
@@ -219,8 +220,9 @@ int jvpfa_fwd(const jvpfa_fwd_args* a, void* stream) {
 namespace {
 int bwd_checked(const jvpfa_bwd_args* a, void* stream, void* const* events) {
   if (a == nullptr) return JVPFA_ERR_BAD_ARG;
+  // smallest workspace any path takes: the status block and one float4 of statistics per row
   int rc = check_common(a->B, a->H, a->N, a->D, a->dtype, a->causal, a->mask, a->workspace, a->workspace_bytes,
-                        jvpfa_bwd_workspace_bytes(a));
+                        sm100_path_supported(a->dtype, a->D, a->N) ? bwd_sm100_workspace_bytes(*a) : bwd_generic_workspace_bytes(*a));
   if (rc != JVPFA_OK) return rc;
   if (!a->q || !a->k || !a->v || !a->o || !a->lse2 || !a->mu || !a->go || !a->dq || !a->dk || !a->dv) return JVPFA_ERR_BAD_ARG;
   const bool dual = a->tq != nullptr;   // tq == NULL: primal-only backward, the tangent-side pointers are ignored
@@ -245,6 +247,9 @@ int bwd_checked(const jvpfa_bwd_args* a, void* stream, void* const* events) {
   marks.events = events;
   marks.stream = s;
   if (sm100_path_supported(eff.dtype, eff.D, eff.N)) return launch_bwd_sm100(eff, s, marks);
+  // fp32: the tensor-core path when the workspace has room for the split operands, else the CUDA-core kernels
+  if (sm100_split_path_supported(eff.dtype, eff.D, eff.N) && eff.workspace_bytes >= bwd_sm100_split_workspace_bytes(eff))
+    return launch_bwd_sm100_split(eff, s, marks);
   return launch_bwd_generic(eff, s, marks);
 }
 }  // namespace

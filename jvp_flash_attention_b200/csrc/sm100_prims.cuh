@@ -170,7 +170,8 @@ __device__ __forceinline__ uint64_t desc_mnmajor_sw128(uint32_t smem_addr, uint3
 
 enum : uint32_t { FMT_F16 = 0, FMT_BF16 = 1 };
 
-// Instruction descriptor for kind::f16 with fp32 accumulation.
+// Instruction descriptor for kind::f16 with fp32 accumulation (both operands in the same 16-bit format: the hardware
+// does not take an fp16 operand against a bf16 one).
 __host__ __device__ __forceinline__ uint32_t make_idesc(uint32_t ab_fmt, uint32_t M, uint32_t N, uint32_t a_mn_major,
                                                         uint32_t b_mn_major) {
   uint32_t d = 0;

@@ -1,5 +1,6 @@
 // Pre-pass of the fp32 tensor-core path: every fp32 row of up to 64 columns becomes one row of 128 bf16 numbers
-// [hi(64) | lo(64)] with x = hi + lo + r, |r| <= 2^-17 |x|; columns at or beyond the head dimension are zero. The
+// [hi(64) | lo(64)], hi = x rounded to bf16, lo = x - hi rounded to bf16, so that x = hi + lo + r with |r| <= 2^-18 |x|
+// (bf16 keeps the range of fp32, so nothing overflows or is flushed); columns at or beyond the head dimension are zero. The
 // tensor-core kernels then see tiles with the shared-memory geometry of a 128-column 16-bit tensor whose first slab
 // holds the hi parts and whose second slab holds the lo parts. HBM-bound: 4 D bytes read and 256 bytes written per row.
 #include <cuda_bf16.h>
