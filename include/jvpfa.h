@@ -2,8 +2,9 @@
  * jvpfa.h -- C ABI of the B200 (sm_100a) JVP flash-attention library (libjvpfa.so).
  *
  * The entry points below are what a binding of the reference's attention path would call in
- * place of its Triton launches. All tensors are caller-owned device memory; (B,H,N,D) tensors are
- * contiguous row-major exactly as the reference requires (jvp_flash_attention/jvp_attention.py:2950,
+ * place of its Triton launches. All tensors are caller-owned device memory. Outputs are (B,H,N,D)
+ * contiguous row-major, as the reference makes them; inputs may be strided views (see jvpfa_strides),
+ * where the reference copies every non-contiguous input first (jvp_flash_attention/jvp_attention.py:2950,
  * 3007, 3107-3127). Every call is asynchronous on the given CUDA stream and returns a status code;
  * nothing here allocates device memory unless a comment on the entry point says otherwise.
  */
@@ -44,6 +45,16 @@ typedef struct jvpfa_mask {
   int64_t stride[4];
 } jvpfa_mask;
 
+/* Element strides of a (B,H,N,D) input tensor along B, H and N; the D axis must be contiguous. All zero means the
+ * contiguous layout (H*N*D, N*D, D). A strided input (for instance q = qkv.permute(2,0,3,1,4)[0] of a fused projection,
+ * or an upstream gradient that is a transposed view) is read in place by the tensor-core kernels when every stride
+ * is a multiple of 16 bytes and the pointer is 16-byte aligned; otherwise, and for the shapes that run on the
+ * CUDA-core kernels (head dimension above 128 or not a multiple of 8; fp32 above 64), the call returns
+ * JVPFA_ERR_UNSUPPORTED and the caller copies the tensor first. */
+typedef struct jvpfa_strides {
+  int64_t b, h, n;
+} jvpfa_strides;
+
 /* Dual forward. Replaces the launch of _attn_fwd_tma / _attn_fwd in JVPAttn.forward
  * (jvp_attention.py:2773, 2807). Outputs: o, to (same dtype as q), lse2 and mu ((B,H,N) fp32:
  * base-2 log-sum-exp of the scaled, masked scores -- the reference's M, jvp_attention.py:2594 --
@@ -61,6 +72,7 @@ typedef struct jvpfa_fwd_args {
   float *lse2, *mu;
   void* workspace;
   size_t workspace_bytes;
+  jvpfa_strides q_strides, k_strides, v_strides, tq_strides, tk_strides, tv_strides;
 } jvpfa_fwd_args;
 
 /* Dual backward: gradients of sum(o*go)+sum(to*gto) for all six inputs. Replaces
@@ -84,10 +96,11 @@ typedef struct jvpfa_bwd_args {
   void *dq, *dk, *dv, *dtq, *dtk, *dtv;
   void* workspace;
   size_t workspace_bytes;
+  jvpfa_strides q_strides, k_strides, v_strides, tq_strides, tk_strides, tv_strides, go_strides, gto_strides;
 } jvpfa_bwd_args;
 
 /* Library version (major*10000 + minor*100 + patch). */
-int jvpfa_version(void);
+int jvpfa_version(void);   /* 200: the args structs carry input strides */
 /* Text for a status code. */
 const char* jvpfa_error_string(int status);
 

@@ -40,6 +40,10 @@ class Mask(C.Structure):
     _fields_ = [("ptr", C.c_void_p), ("kind", C.c_int32), ("dtype", C.c_int32), ("stride", C.c_int64 * 4)]
 
 
+class Strides(C.Structure):
+    _fields_ = [("b", C.c_int64), ("h", C.c_int64), ("n", C.c_int64)]
+
+
 class FwdArgs(C.Structure):
     _fields_ = [
         ("B", C.c_int32), ("H", C.c_int32), ("N", C.c_int32), ("D", C.c_int32),
@@ -49,6 +53,8 @@ class FwdArgs(C.Structure):
         ("tq", C.c_void_p), ("tk", C.c_void_p), ("tv", C.c_void_p),
         ("o", C.c_void_p), ("to", C.c_void_p), ("lse2", C.c_void_p), ("mu", C.c_void_p),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("q_strides", Strides), ("k_strides", Strides), ("v_strides", Strides),
+        ("tq_strides", Strides), ("tk_strides", Strides), ("tv_strides", Strides),
     ]
 
 
@@ -64,6 +70,9 @@ class BwdArgs(C.Structure):
         ("dq", C.c_void_p), ("dk", C.c_void_p), ("dv", C.c_void_p),
         ("dtq", C.c_void_p), ("dtk", C.c_void_p), ("dtv", C.c_void_p),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("q_strides", Strides), ("k_strides", Strides), ("v_strides", Strides),
+        ("tq_strides", Strides), ("tk_strides", Strides), ("tv_strides", Strides),
+        ("go_strides", Strides), ("gto_strides", Strides),
     ]
 
 
@@ -135,6 +144,45 @@ def dtype_code(dt: torch.dtype) -> int:
 
 def _ptr(t):
     return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def tensor_core_path(dtype: torch.dtype, D: int) -> bool:
+    """Whether (dtype, head dimension) runs on the tensor-core kernels, which read strided inputs in place."""
+    if dtype in (torch.float16, torch.bfloat16):
+        return 8 <= D <= 128 and D % 8 == 0
+    return dtype == torch.float32 and 8 <= D <= 64 and D % 8 == 0
+
+
+def readable_in_place(t: torch.Tensor) -> bool:
+    """A (B,H,N,D) input the tensor-core kernels can read as it is: last axis contiguous, every other stride (of an
+    axis longer than 1) positive and a multiple of 16 bytes, 16-byte aligned storage."""
+    if t.stride(-1) != 1 or t.data_ptr() % 16 != 0:
+        return False
+    es = t.element_size()
+    for dim in range(3):
+        if t.shape[dim] > 1 and (t.stride(dim) <= 0 or (t.stride(dim) * es) % 16 != 0):
+            return False
+    return (t.stride(2) * es) % 16 == 0 and t.stride(2) > 0
+
+
+def as_input(t):
+    """The tensor itself when the kernels can read it in place, else a contiguous copy (None stays None)."""
+    if t is None or t.is_contiguous():
+        return t
+    if tensor_core_path(t.dtype, t.shape[-1]) and readable_in_place(t):
+        return t
+    return t.contiguous()
+
+
+def _set_strides(field: Strides, t) -> None:
+    if t is None or t.is_contiguous():
+        field.b = field.h = field.n = 0
+        return
+    B, H, N, _ = t.shape
+    # an axis of length 1 may carry any stride: give it the contiguous one
+    field.n = t.stride(2) if N > 1 else t.shape[3]
+    field.h = t.stride(1) if H > 1 else N * t.shape[3]
+    field.b = t.stride(0) if B > 1 else H * N * t.shape[3]
 
 
 def make_mask(mask, B, H, N) -> Mask:
@@ -255,8 +303,8 @@ def fwd(q, k, v, tq, tk, tv, mask_c: Mask, summary, causal: bool, sm_scale: floa
     """Launches the dual forward; returns (o, to, lse2, mu). tq/tk/tv None -> primal only (to None)."""
     B, H, N, D = q.shape
     dual = tq is not None
-    o = torch.empty_like(q)
-    to = torch.empty_like(q) if dual else None
+    o = torch.empty(q.shape, dtype=q.dtype, device=q.device)        # outputs are always contiguous
+    to = torch.empty(q.shape, dtype=q.dtype, device=q.device) if dual else None
     lse2 = torch.empty((B, H, N), dtype=torch.float32, device=q.device)
     mu = torch.empty((B, H, N), dtype=torch.float32, device=q.device)
     a = FwdArgs()
@@ -264,8 +312,11 @@ def fwd(q, k, v, tq, tk, tv, mask_c: Mask, summary, causal: bool, sm_scale: floa
     a.dtype, a.causal, a.sm_scale = dtype_code(q.dtype), int(bool(causal)), float(sm_scale)
     a.mask = mask_c
     a.mask_summary = None if summary is None else summary.data_ptr()
+    q, k, v, tq, tk, tv = (as_input(t) for t in (q, k, v, tq, tk, tv))
     a.q, a.k, a.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
     a.tq, a.tk, a.tv = (tq.data_ptr(), tk.data_ptr(), tv.data_ptr()) if dual else (None, None, None)
+    for name, t in (("q", q), ("k", k), ("v", v), ("tq", tq), ("tk", tk), ("tv", tv)):
+        _set_strides(getattr(a, name + "_strides"), t)
     a.o, a.to = o.data_ptr(), (to.data_ptr() if dual else None)
     a.lse2, a.mu = lse2.data_ptr(), mu.data_ptr()
     need = lib().jvpfa_fwd_workspace_bytes(C.byref(a))
@@ -284,7 +335,8 @@ def bwd(q, k, v, tq, tk, tv, o, to, lse2, mu, go, gto, mask_c: Mask, summary, ca
     family kernels and after the last one."""
     B, H, N, D = q.shape
     dual = tq is not None
-    outs = [torch.empty_like(q) for _ in range(6 if dual else 3)]
+    outs = [torch.empty(q.shape, dtype=q.dtype, device=q.device) for _ in range(6 if dual else 3)]
+    q, k, v, tq, tk, tv, go, gto = (as_input(t) for t in (q, k, v, tq, tk, tv, go, gto))
     a = BwdArgs()
     a.B, a.H, a.N, a.D = B, H, N, D
     a.dtype, a.causal, a.sm_scale = dtype_code(q.dtype), int(bool(causal)), float(sm_scale)
@@ -293,6 +345,9 @@ def bwd(q, k, v, tq, tk, tv, o, to, lse2, mu, go, gto, mask_c: Mask, summary, ca
     a.q, a.k, a.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
     a.o, a.lse2, a.mu = o.data_ptr(), lse2.data_ptr(), mu.data_ptr()
     a.go = go.data_ptr()
+    for name, t in (("q", q), ("k", k), ("v", v), ("go", go), ("tq", tq if dual else None), ("tk", tk if dual else None),
+                    ("tv", tv if dual else None), ("gto", gto if dual else None)):
+        _set_strides(getattr(a, name + "_strides"), t)
     a.dq, a.dk, a.dv = (t.data_ptr() for t in outs[:3])
     if dual:
         a.tq, a.tk, a.tv, a.to, a.gto = (t.data_ptr() for t in (tq, tk, tv, to, gto))

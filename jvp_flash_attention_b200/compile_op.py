@@ -20,7 +20,6 @@ from . import _lib
 def attn_fwd_dual(q: Tensor, k: Tensor, v: Tensor, q_t: Tensor, k_t: Tensor, v_t: Tensor, mask: Optional[Tensor],
                   sm_scale: float, causal: bool) -> Tuple[Tensor, Tensor, Tensor, Tensor]:
     B, H, N, D = q.shape
-    q, k, v, q_t, k_t, v_t = (t.contiguous() for t in (q, k, v, q_t, k_t, v_t))
     mask_c = _lib.make_mask(mask, B, H, N)
     summary = _lib.mask_summary(mask_c, mask, B, H, N) if mask is not None else None
     o, o_t, lse2, mu = _lib.fwd(q, k, v, q_t, k_t, v_t, mask_c, summary, causal, sm_scale)
@@ -41,8 +40,8 @@ def attn_bwd_dual(q: Tensor, k: Tensor, v: Tensor, q_t: Tensor, k_t: Tensor, v_t
     B, H, N, D = q.shape
     mask_c = _lib.make_mask(mask, B, H, N)
     summary = _lib.mask_summary(mask_c, mask, B, H, N) if mask is not None else None
-    return _lib.bwd(q.contiguous(), k.contiguous(), v.contiguous(), q_t.contiguous(), k_t.contiguous(), v_t.contiguous(),
-                    o, o_t, lse2, mu, go.contiguous(), go_t.contiguous(), mask_c, summary, causal, sm_scale)
+    return _lib.bwd(q, k, v, q_t, k_t, v_t, o.contiguous(), o_t.contiguous(), lse2, mu, go, go_t, mask_c, summary,
+                    causal, sm_scale)
 
 
 @attn_bwd_dual.register_fake

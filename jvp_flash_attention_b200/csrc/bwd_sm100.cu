@@ -245,24 +245,24 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
       mbar_arrive_expect_tx(&r_full, (DUAL ? C::NR : C::NR / 2) * C::TILE_R);
 #pragma unroll
       for (int sl = 0; sl < SLABS; ++sl) {
-        tma_load_2d(sR(0) + sl * C::SLAB, &rm0, &r_full, 64 * sl, row_base + r0);
-        if constexpr (DUAL) tma_load_2d(sR(1) + sl * C::SLAB, &rm1, &r_full, 64 * sl, row_base + r0);
+        tma_load_tile(sR(0) + sl * C::SLAB, &rm0, &r_full, 64 * sl, r0, h, b);
+        if constexpr (DUAL) tma_load_tile(sR(1) + sl * C::SLAB, &rm1, &r_full, 64 * sl, r0, h, b);
         if constexpr (C::NR == 4) {
-          tma_load_2d(sR(2) + sl * C::SLAB, &rm2, &r_full, 64 * sl, row_base + r0);
-          if constexpr (DUAL) tma_load_2d(sR(3) + sl * C::SLAB, &rm3, &r_full, 64 * sl, row_base + r0);
+          tma_load_tile(sR(2) + sl * C::SLAB, &rm2, &r_full, 64 * sl, r0, h, b);
+          if constexpr (DUAL) tma_load_tile(sR(3) + sl * C::SLAB, &rm3, &r_full, 64 * sl, r0, h, b);
         }
       }
       int it = 0;
       for (int j = next_active(j_begin); j < j_end; j = next_active(j + 1), ++it) {
-        const int crow = row_base + j * C::BC;
+        const int crow = j * C::BC;   // first row of the column tile inside its (batch, head) unit
         {
           const int buf = it % NA;
           mbar_wait(&a_empty[buf], ((it / NA) & 1) ^ 1, w, 10);
           mbar_arrive_expect_tx(&a_full[buf], DUAL ? C::PAIR : C::PAIR / 2);
 #pragma unroll
           for (int sl = 0; sl < SLABS; ++sl) {
-            tma_load_2d(sA(buf) + sl * C::SLAB, &cm0, &a_full[buf], 64 * sl, crow);
-            if constexpr (DUAL) tma_load_2d(sA(buf) + sl * C::SLAB + C::HALF, &cm1, &a_full[buf], 64 * sl, crow);
+            tma_load_tile(sA(buf) + sl * C::SLAB, &cm0, &a_full[buf], 64 * sl, crow, h, b);
+            if constexpr (DUAL) tma_load_tile(sA(buf) + sl * C::SLAB + C::HALF, &cm1, &a_full[buf], 64 * sl, crow, h, b);
           }
         }
         {
@@ -271,8 +271,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
           mbar_arrive_expect_tx(&b_full[buf], DUAL ? C::PAIR : C::PAIR / 2);
 #pragma unroll
           for (int sl = 0; sl < SLABS; ++sl) {
-            tma_load_2d(sB(buf) + sl * C::SLAB, &cm2, &b_full[buf], 64 * sl, crow);
-            if constexpr (DUAL) tma_load_2d(sB(buf) + sl * C::SLAB + C::HALF, &cm3, &b_full[buf], 64 * sl, crow);
+            tma_load_tile(sB(buf) + sl * C::SLAB, &cm2, &b_full[buf], 64 * sl, crow, h, b);
+            if constexpr (DUAL) tma_load_tile(sB(buf) + sl * C::SLAB + C::HALF, &cm3, &b_full[buf], 64 * sl, crow, h, b);
           }
         }
       }
@@ -776,6 +776,16 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
   if (warp == 9) tmem_dealloc(tmem, C::TMEM_COLS);
 }
 
+// Where the rows of the upstream gradients start: go and gto may be strided views, o and to are contiguous.
+struct GradLayout {
+  int H, N;
+  TensorView go, gto;
+  __host__ __device__ int64_t offset(int64_t row, const TensorView& v) const {
+    const int64_t n = row % N, bh = row / N;
+    return (bh / H) * v.sb + (bh % H) * v.sh + n * v.sn;
+  }
+};
+
 // stats[row] = (lse2, mu, Delta, a) with a = rowsum(gtO o O), Delta = rowsum(gO o O) + rowsum(gtO o tO) - a mu.
 // Half a warp per row; 16-bit inputs. Generalises the reference's _attn_bwd_preprocess
 // (jvp_attention.py:1395-1422), which computes rowsum(O o dO) only.
@@ -783,11 +793,12 @@ template <bool BF16>
 __global__ void bwd_preprocess_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict__ to,
                                       const uint16_t* __restrict__ go, const uint16_t* __restrict__ gto,
                                       const float* __restrict__ lse2, const float* __restrict__ mu,
-                                      float4* __restrict__ stats, int64_t rows, int D) {
+                                      float4* __restrict__ stats, int64_t rows, int D, const GradLayout gl) {
   // half a warp per row, 16 bytes per lane and tensor in flight
   const int lane = threadIdx.x & 31, l16 = lane & 15;
   const int64_t row = (static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5)) * 2 + (lane >> 4);
   const bool live = row < rows;
+  const int64_t go_row = live ? gl.offset(row, gl.go) : 0, gto_row = live ? gl.offset(row, gl.gto) : 0;
   auto lo = [](uint32_t x) -> float {
     if constexpr (BF16) return __uint_as_float(x << 16);
     else return __half2float(__ushort_as_half(static_cast<uint16_t>(x & 0xFFFFu)));
@@ -802,9 +813,9 @@ __global__ void bwd_preprocess_kernel(const uint16_t* __restrict__ o, const uint
       const size_t idx = static_cast<size_t>(row) * D + d;
       const uint4 z = make_uint4(0u, 0u, 0u, 0u);
       const uint4 ov = *reinterpret_cast<const uint4*>(o + idx);
-      const uint4 gov = *reinterpret_cast<const uint4*>(go + idx);
+      const uint4 gov = *reinterpret_cast<const uint4*>(go + go_row + d);
       const uint4 tov = gto ? *reinterpret_cast<const uint4*>(to + idx) : z;
-      const uint4 gtov = gto ? *reinterpret_cast<const uint4*>(gto + idx) : z;
+      const uint4 gtov = gto ? *reinterpret_cast<const uint4*>(gto + gto_row + d) : z;
       const uint32_t a0[4] = {ov.x, ov.y, ov.z, ov.w}, a1[4] = {tov.x, tov.y, tov.z, tov.w};
       const uint32_t a2[4] = {gov.x, gov.y, gov.z, gov.w}, a3[4] = {gtov.x, gtov.y, gtov.z, gtov.w};
 #pragma unroll
@@ -831,18 +842,19 @@ __global__ void bwd_preprocess_kernel(const uint16_t* __restrict__ o, const uint
 __global__ void bwd_preprocess_f32_kernel(const float* __restrict__ o, const float* __restrict__ to,
                                           const float* __restrict__ go, const float* __restrict__ gto,
                                           const float* __restrict__ lse2, const float* __restrict__ mu,
-                                          float4* __restrict__ stats, int64_t rows, int D) {
+                                          float4* __restrict__ stats, int64_t rows, int D, const GradLayout gl) {
   const int lane = threadIdx.x & 31, l16 = lane & 15;
   const int64_t row = (static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5)) * 2 + (lane >> 4);
   const bool live = row < rows;
+  const int64_t go_row = live ? gl.offset(row, gl.go) : 0, gto_row = live ? gl.offset(row, gl.gto) : 0;
   float s_go_o = 0.f, s_gto_to = 0.f, s_gto_o = 0.f;
   if (live && l16 * 4 < D) {
     const size_t idx = static_cast<size_t>(row) * D + l16 * 4;
     const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
     const float4 ov = *reinterpret_cast<const float4*>(o + idx);
-    const float4 gov = *reinterpret_cast<const float4*>(go + idx);
+    const float4 gov = *reinterpret_cast<const float4*>(go + go_row + l16 * 4);
     const float4 tov = gto ? *reinterpret_cast<const float4*>(to + idx) : z;
-    const float4 gtov = gto ? *reinterpret_cast<const float4*>(gto + idx) : z;
+    const float4 gtov = gto ? *reinterpret_cast<const float4*>(gto + gto_row + l16 * 4) : z;
     s_go_o = gov.x * ov.x + gov.y * ov.y + gov.z * ov.z + gov.w * ov.w;
     s_gto_to = gtov.x * tov.x + gtov.y * tov.y + gtov.z * tov.z + gtov.w * tov.w;
     s_gto_o = gtov.x * ov.x + gtov.y * ov.y + gtov.z * ov.z + gtov.w * ov.w;
@@ -864,22 +876,25 @@ __global__ void bwd_preprocess_f32_kernel(const float* __restrict__ o, const flo
 template <int D, int FAM, bool BF16, bool PAD, bool DUAL, bool SPLIT = false>
 int launch_family(const jvpfa_bwd_args& a, const float4* stats, cudaStream_t stream, int real_D = 0) {
   using C = BwdCfg<D, FAM, SPLIT>;
-  const uint64_t rows = static_cast<uint64_t>(a.B) * a.H * a.N;
-  const void* rsrc[4];
-  const void* csrc[4];
+  const TensorView vq = make_view(a.q, a.q_strides, a.H, a.N, a.D), vk = make_view(a.k, a.k_strides, a.H, a.N, a.D),
+                   vv = make_view(a.v, a.v_strides, a.H, a.N, a.D), vtq = make_view(a.tq, a.tq_strides, a.H, a.N, a.D),
+                   vtk = make_view(a.tk, a.tk_strides, a.H, a.N, a.D), vtv = make_view(a.tv, a.tv_strides, a.H, a.N, a.D),
+                   vgo = make_view(a.go, a.go_strides, a.H, a.N, a.D), vgto = make_view(a.gto, a.gto_strides, a.H, a.N, a.D);
+  TensorView rsrc[4];
+  TensorView csrc[4];
   void *out0, *out1;
   float out_scale;
   if (FAM == FAM_Q) {
-    rsrc[0] = a.q; rsrc[1] = a.tq; rsrc[2] = a.go; rsrc[3] = a.gto;
-    csrc[0] = a.k; csrc[1] = a.tk; csrc[2] = a.v; csrc[3] = a.tv;
+    rsrc[0] = vq; rsrc[1] = vtq; rsrc[2] = vgo; rsrc[3] = vgto;
+    csrc[0] = vk; csrc[1] = vtk; csrc[2] = vv; csrc[3] = vtv;
     out0 = a.dq; out1 = a.dtq; out_scale = a.sm_scale;
   } else if (FAM == FAM_K) {
-    rsrc[0] = a.k; rsrc[1] = a.tk; rsrc[2] = a.v; rsrc[3] = a.tv;
-    csrc[0] = a.q; csrc[1] = a.tq; csrc[2] = a.go; csrc[3] = a.gto;
+    rsrc[0] = vk; rsrc[1] = vtk; rsrc[2] = vv; rsrc[3] = vtv;
+    csrc[0] = vq; csrc[1] = vtq; csrc[2] = vgo; csrc[3] = vgto;
     out0 = a.dk; out1 = a.dtk; out_scale = a.sm_scale;
   } else {
-    rsrc[0] = a.k; rsrc[1] = a.tk; rsrc[2] = a.k; rsrc[3] = a.tk;
-    csrc[0] = a.q; csrc[1] = a.tq; csrc[2] = a.go; csrc[3] = a.gto;
+    rsrc[0] = vk; rsrc[1] = vtk; rsrc[2] = vk; rsrc[3] = vtk;
+    csrc[0] = vq; csrc[1] = vtq; csrc[2] = vgo; csrc[3] = vgto;
     out0 = a.dv; out1 = a.dtv; out_scale = 1.0f;
   }
   if (!DUAL) {  // tensors that do not exist in the primal-only call: alias the maps to existing ones, they are never used
@@ -888,8 +903,8 @@ int launch_family(const jvpfa_bwd_args& a, const float4* stats, cudaStream_t str
   }
   CUtensorMap rm[4], cm[4];
   for (int i = 0; i < 4; ++i) {
-    if (!make_tile_map(&rm[i], rsrc[i], rows, a.D, C::BR, a.dtype)) return JVPFA_ERR_LAUNCH;
-    if (!make_tile_map(&cm[i], csrc[i], rows, a.D, C::BC, a.dtype)) return JVPFA_ERR_LAUNCH;
+    if (!make_tile_map(&rm[i], rsrc[i], a.B, a.H, a.N, a.D, C::BR, a.dtype)) return JVPFA_ERR_LAUNCH;
+    if (!make_tile_map(&cm[i], csrc[i], a.B, a.H, a.N, a.D, C::BC, a.dtype)) return JVPFA_ERR_LAUNCH;
   }
   BwdKParams p{};
   p.H = a.H; p.N = a.N; p.D = SPLIT ? real_D : a.D; p.causal = a.causal;
@@ -921,9 +936,10 @@ int launch_all(const jvpfa_bwd_args& a, cudaStream_t stream, const LaunchMarks& 
   const int warps_per_block = 8;   // two rows per warp
   const unsigned blocks = static_cast<unsigned>((rows + 2 * warps_per_block - 1) / (2 * warps_per_block));
   marks.mark(0);
+  const GradLayout gl{a.H, a.N, make_view(a.go, a.go_strides, a.H, a.N, a.D), make_view(a.gto, a.gto_strides, a.H, a.N, a.D)};
   bwd_preprocess_kernel<BF16><<<blocks, warps_per_block * 32, 0, stream>>>(
       static_cast<const uint16_t*>(a.o), static_cast<const uint16_t*>(a.to), static_cast<const uint16_t*>(a.go),
-      static_cast<const uint16_t*>(a.gto), a.lse2, a.mu, stats, rows, a.D);
+      static_cast<const uint16_t*>(a.gto), a.lse2, a.mu, stats, rows, a.D, gl);
   if (cudaGetLastError() != cudaSuccess) return JVPFA_ERR_LAUNCH;
   auto three = [&](auto pad, auto dual) {
     constexpr bool P = decltype(pad)::value, DU = decltype(dual)::value;
@@ -959,15 +975,22 @@ int launch_split(const jvpfa_bwd_args& a, cudaStream_t stream, const LaunchMarks
   marks.mark(0);
   const int warps_per_block = 8;   // two rows per warp
   const unsigned blocks = static_cast<unsigned>((rows + 2 * warps_per_block - 1) / (2 * warps_per_block));
+  const GradLayout gl{a.H, a.N, make_view(a.go, a.go_strides, a.H, a.N, a.D), make_view(a.gto, a.gto_strides, a.H, a.N, a.D)};
   bwd_preprocess_f32_kernel<<<blocks, warps_per_block * 32, 0, stream>>>(
       static_cast<const float*>(a.o), static_cast<const float*>(a.to), static_cast<const float*>(a.go),
-      static_cast<const float*>(a.gto), a.lse2, a.mu, stats, rows, a.D);
+      static_cast<const float*>(a.gto), a.lse2, a.mu, stats, rows, a.D, gl);
   if (cudaGetLastError() != cudaSuccess) return JVPFA_ERR_LAUNCH;
-  int rc = launch_split_fp32(src, dst, n_t, rows, a.D, stream);
+  const jvpfa_strides* sst[8] = {&a.q_strides, &a.k_strides, &a.v_strides, &a.go_strides,
+                                 &a.tq_strides, &a.tk_strides, &a.tv_strides, &a.gto_strides};
+  TensorView views[8];
+  for (int i = 0; i < n_t; ++i) views[i] = make_view(src[i], *sst[i], a.H, a.N, a.D);
+  int rc = launch_split_fp32(views, dst, n_t, a.B, a.H, a.N, a.D, stream);
   if (rc != JVPFA_OK) return rc;
-  jvpfa_bwd_args m = a;      // what the tensor maps are built on
+  jvpfa_bwd_args m = a;      // what the tensor maps are built on: the contiguous split tensors
   m.D = 128;
   m.dtype = JVPFA_BF16;
+  const jvpfa_strides none{0, 0, 0};
+  m.q_strides = m.k_strides = m.v_strides = m.tq_strides = m.tk_strides = m.tv_strides = m.go_strides = m.gto_strides = none;
   m.q = dst[0]; m.k = dst[1]; m.v = dst[2]; m.go = dst[3];
   if (DUAL) { m.tq = dst[4]; m.tk = dst[5]; m.tv = dst[6]; m.gto = dst[7]; }
   marks.mark(1);

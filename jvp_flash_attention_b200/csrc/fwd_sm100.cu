@@ -202,18 +202,18 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (!(tile_bits(j) & kTileAnyKept)) continue;
         const int st = it % ST;
         const uint32_t ph = (it / ST) & 1;
-        const int krow = row_base + j * C::BN;
+        const int krow = j * C::BN;   // first key row of the tile inside its (batch, head) unit
         mbar_wait(&v_empty[st], ph ^ 1, w, 11);
         mbar_arrive_expect_tx(&v_full[st], (DUAL ? 2 : 1) * C::TILE_V);
         if constexpr (!PAD && SLABS > 1) {
           // the slabs of a V tile are consecutive in shared memory: one box per tensor through the 3-D map
-          tma_load_3d(sV(st), &tmV, &v_full[st], 0, krow, 0);
-          if constexpr (DUAL) tma_load_3d(sTV(st), &tmTV, &v_full[st], 0, krow, 0);
+          tma_load_slabs(sV(st), &tmV, &v_full[st], krow, h, b);
+          if constexpr (DUAL) tma_load_slabs(sTV(st), &tmTV, &v_full[st], krow, h, b);
         } else {
 #pragma unroll
           for (int sl = 0; sl < SLABS; ++sl) {
-            tma_load_2d(sV(st) + sl * C::HALF, &tmV, &v_full[st], 64 * sl, krow);
-            if constexpr (DUAL) tma_load_2d(sTV(st) + sl * C::HALF, &tmTV, &v_full[st], 64 * sl, krow);
+            tma_load_tile(sV(st) + sl * C::HALF, &tmV, &v_full[st], 64 * sl, krow, h, b);
+            if constexpr (DUAL) tma_load_tile(sTV(st) + sl * C::HALF, &tmTV, &v_full[st], 64 * sl, krow, h, b);
           }
         }
         ++it;
@@ -229,21 +229,21 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_arrive_expect_tx(&q_full, (DUAL ? 2 : 1) * C::TILE_Q);
 #pragma unroll
       for (int sl = 0; sl < SLABS; ++sl) {
-        tma_load_2d(sQ + sl * C::SLAB, &tmQ, &q_full, 64 * sl, row_base + q0);
-        if constexpr (DUAL) tma_load_2d(sTQ + sl * C::SLAB, &tmTQ, &q_full, 64 * sl, row_base + q0);
+        tma_load_tile(sQ + sl * C::SLAB, &tmQ, &q_full, 64 * sl, q0, h, b);
+        if constexpr (DUAL) tma_load_tile(sTQ + sl * C::SLAB, &tmTQ, &q_full, 64 * sl, q0, h, b);
       }
       int it = 0;
       for (int j = 0; j < n_kt; ++j) {
         if (!(tile_bits(j) & kTileAnyKept)) continue;
         const int st = it % ST;
         const uint32_t ph = (it / ST) & 1;
-        const int krow = row_base + j * C::BN;
+        const int krow = j * C::BN;   // first key row of the tile inside its (batch, head) unit
         mbar_wait(&k_empty[st], ph ^ 1, w, 10);
         mbar_arrive_expect_tx(&k_full[st], (DUAL ? 2 : 1) * C::TILE_V);
 #pragma unroll
         for (int sl = 0; sl < SLABS; ++sl) {
-          tma_load_2d(sK(st) + sl * C::SLAB, &tmK, &k_full[st], 64 * sl, krow);
-          if constexpr (DUAL) tma_load_2d(sK(st) + sl * C::SLAB + C::HALF, &tmTK, &k_full[st], 64 * sl, krow);
+          tma_load_tile(sK(st) + sl * C::SLAB, &tmK, &k_full[st], 64 * sl, krow, h, b);
+          if constexpr (DUAL) tma_load_tile(sK(st) + sl * C::SLAB + C::HALF, &tmTK, &k_full[st], 64 * sl, krow, h, b);
         }
         ++it;
       }
@@ -603,13 +603,17 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 template <int D, bool DUAL, bool BF16, bool PAD>
 int launch_one(const jvpfa_fwd_args& a, cudaStream_t stream) {
   using C = FwdCfg<D>;
-  const uint64_t rows = static_cast<uint64_t>(a.B) * a.H * a.N;
   CUtensorMap mQ, mTQ, mK, mTK, mV, mTV;
-  bool ok = make_tile_map(&mQ, a.q, rows, a.D, C::BM, a.dtype) && make_tile_map(&mK, a.k, rows, a.D, C::BN, a.dtype) &&
-            ((!PAD && D > 64) ? make_slab_map(&mV, a.v, rows, a.D, C::BN, a.dtype) : make_tile_map(&mV, a.v, rows, a.D, C::BN, a.dtype));
+  auto tile = [&](CUtensorMap* m, const void* ptr, const jvpfa_strides& st, int box_rows) {
+    return make_tile_map(m, make_view(ptr, st, a.H, a.N, a.D), a.B, a.H, a.N, a.D, box_rows, a.dtype);
+  };
+  auto vmap = [&](CUtensorMap* m, const void* ptr, const jvpfa_strides& st) {
+    return (!PAD && D > 64) ? make_slab_map(m, make_view(ptr, st, a.H, a.N, a.D), a.B, a.H, a.N, a.D, C::BN, a.dtype)
+                            : tile(m, ptr, st, C::BN);
+  };
+  bool ok = tile(&mQ, a.q, a.q_strides, C::BM) && tile(&mK, a.k, a.k_strides, C::BN) && vmap(&mV, a.v, a.v_strides);
   if (DUAL) {
-    ok = ok && make_tile_map(&mTQ, a.tq, rows, a.D, C::BM, a.dtype) && make_tile_map(&mTK, a.tk, rows, a.D, C::BN, a.dtype) &&
-         ((!PAD && D > 64) ? make_slab_map(&mTV, a.tv, rows, a.D, C::BN, a.dtype) : make_tile_map(&mTV, a.tv, rows, a.D, C::BN, a.dtype));
+    ok = ok && tile(&mTQ, a.tq, a.tq_strides, C::BM) && tile(&mTK, a.tk, a.tk_strides, C::BN) && vmap(&mTV, a.tv, a.tv_strides);
   } else {
     mTQ = mQ; mTK = mK; mTV = mV;
   }
@@ -646,15 +650,22 @@ int launch_split(const jvpfa_fwd_args& a, cudaStream_t stream) {
   uint16_t* dst[6];
   uint8_t* base = static_cast<uint8_t*>(a.workspace) + kStatusBytes;
   for (int i = 0; i < n_t; ++i) dst[i] = reinterpret_cast<uint16_t*>(base + static_cast<size_t>(i) * rows * kSplitRowBytes);
-  int rc = launch_split_fp32(src, dst, n_t, rows, a.D, stream);
+  const jvpfa_strides* sst[6] = {&a.q_strides, &a.k_strides, &a.v_strides, &a.tq_strides, &a.tk_strides, &a.tv_strides};
+  TensorView views[6];
+  for (int i = 0; i < n_t; ++i) views[i] = make_view(src[i], *sst[i], a.H, a.N, a.D);
+  int rc = launch_split_fp32(views, dst, n_t, a.B, a.H, a.N, a.D, stream);
   if (rc != JVPFA_OK) return rc;
   CUtensorMap mQ, mTQ, mK, mTK, mV, mTV;
-  const uint64_t urows = static_cast<uint64_t>(rows);
-  bool ok = make_tile_map(&mQ, dst[0], urows, 128, C::BM, JVPFA_BF16) && make_tile_map(&mK, dst[1], urows, 128, C::BN, JVPFA_BF16) &&
-            make_slab_map(&mV, dst[2], urows, 128, C::BN, JVPFA_BF16);
+  const jvpfa_strides none{0, 0, 0};
+  auto tile = [&](CUtensorMap* m, const void* ptr, int box_rows) {
+    return make_tile_map(m, make_view(ptr, none, a.H, a.N, 128), a.B, a.H, a.N, 128, box_rows, JVPFA_BF16);
+  };
+  auto slab = [&](CUtensorMap* m, const void* ptr) {
+    return make_slab_map(m, make_view(ptr, none, a.H, a.N, 128), a.B, a.H, a.N, 128, C::BN, JVPFA_BF16);
+  };
+  bool ok = tile(&mQ, dst[0], C::BM) && tile(&mK, dst[1], C::BN) && slab(&mV, dst[2]);
   if (DUAL) {
-    ok = ok && make_tile_map(&mTQ, dst[3], urows, 128, C::BM, JVPFA_BF16) && make_tile_map(&mTK, dst[4], urows, 128, C::BN, JVPFA_BF16) &&
-         make_slab_map(&mTV, dst[5], urows, 128, C::BN, JVPFA_BF16);
+    ok = ok && tile(&mTQ, dst[3], C::BM) && tile(&mTK, dst[4], C::BN) && slab(&mTV, dst[5]);
   } else {
     mTQ = mQ; mTK = mK; mTV = mV;
   }

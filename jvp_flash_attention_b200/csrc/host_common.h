@@ -15,17 +15,37 @@ typedef CUresult (*TensorMapEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint3
 
 TensorMapEncodeFn tensor_map_encoder();
 
-// A (rows x D) row-major matrix of 16-bit elements, D a multiple of 8, as a 2-D tensor map with a box of
-// (64 columns, box_rows rows): one TMA copy per 64-column slab lands in shared memory as [box_rows][64
-// elements] in the 128-byte-swizzled layout the MMA descriptors expect; columns at or beyond D read as
-// zero, which is how head dimensions that are not 64 or 128 ride on the 64- and 128-wide kernels.
-// Returns false if the driver rejects the encoding.
-bool make_tile_map(CUtensorMap* out, const void* base, uint64_t rows, int D, int box_rows, int dtype);
+// A (B,H,N,D) input of 16-bit elements given by element strides along B, H, N (D contiguous).
+struct TensorView {
+  const void* ptr;
+  int64_t sb, sh, sn;
+};
+// The view of a tensor with the ABI's strides; all-zero strides mean the contiguous layout.
+inline TensorView make_view(const void* ptr, const jvpfa_strides& st, int H, int N, int D) {
+  if (st.b == 0 && st.h == 0 && st.n == 0) return TensorView{ptr, static_cast<int64_t>(H) * N * D, static_cast<int64_t>(N) * D, D};
+  return TensorView{ptr, st.b, st.h, st.n};
+}
+inline bool is_contiguous(const jvpfa_strides& st, int H, int N, int D) {
+  return (st.b == 0 && st.h == 0 && st.n == 0) ||
+         (st.n == D && st.h == static_cast<int64_t>(N) * D && st.b == static_cast<int64_t>(H) * N * D);
+}
+// TMA can read the view in place: base and every stride a multiple of 16 bytes.
+inline bool view_tma_compatible(const TensorView& v, int elem_bytes) {
+  return (reinterpret_cast<uintptr_t>(v.ptr) & 15) == 0 && (v.sb * elem_bytes) % 16 == 0 && (v.sh * elem_bytes) % 16 == 0 &&
+         (v.sn * elem_bytes) % 16 == 0 && v.sb >= 0 && v.sh >= 0 && v.sn > 0;
+}
 
-// The same matrix (D a multiple of 64) as a 3-D map (64, rows, D / 64): one box of (64, box_rows, D / 64) lands as
+// The view as a 4-D tensor map (D, N, H, B) with a box of (64 columns, box_rows rows, 1, 1): one TMA copy per
+// 64-column slab lands in shared memory as [box_rows][64 elements] in the 128-byte-swizzled layout the MMA descriptors
+// expect; columns at or beyond D and rows at or beyond N read as zero, which is how head dimensions that are not 64 or
+// 128 ride on the 64- and 128-wide kernels and how ragged sequence lengths stay inside their (batch, head) unit.
+// Returns false if the driver rejects the encoding.
+bool make_tile_map(CUtensorMap* out, const TensorView& v, int B, int H, int N, int D, int box_rows, int dtype);
+
+// The same view (D a multiple of 64) as a 5-D map (64, N, D / 64, H, B): one box of (64, box_rows, D / 64, 1, 1) lands as
 // D / 64 consecutive 128-byte-swizzled slabs of [box_rows][64]. One large box instead of one box per slab: the TMA
 // unit of an SM delivers 43 B/clk in 32 KB boxes, 36 in 16 KB boxes and 29 in 8 KB boxes (measured).
-bool make_slab_map(CUtensorMap* out, const void* base, uint64_t rows, int D, int box_rows, int dtype);
+bool make_slab_map(CUtensorMap* out, const TensorView& v, int B, int H, int N, int D, int box_rows, int dtype);
 
 // Wait budget of a single device-side mbarrier wait, in nanoseconds (JVPFA_WAIT_BUDGET_MS, default 4000 ms).
 uint64_t wait_budget_ns();
@@ -48,7 +68,7 @@ struct LaunchMarks {
 // by a pre-pass into the workspace and every product runs as three bf16 products accumulated in fp32.
 constexpr int kSplitMaxTensors = 8;
 constexpr size_t kSplitRowBytes = 256;   // one split row: 64 hi + 64 lo bf16 numbers
-int launch_split_fp32(const void* const* src, uint16_t* const* dst, int n_tensors, int64_t rows, int D, cudaStream_t stream);
+int launch_split_fp32(const TensorView* src, uint16_t* const* dst, int n_tensors, int B, int H, int N, int D, cudaStream_t stream);
 bool sm100_split_path_supported(int dtype, int D, int N);
 size_t fwd_sm100_split_workspace_bytes(const jvpfa_fwd_args& a);
 size_t bwd_sm100_split_workspace_bytes(const jvpfa_bwd_args& a);

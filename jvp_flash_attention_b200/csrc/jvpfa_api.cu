@@ -22,28 +22,33 @@ TensorMapEncodeFn tensor_map_encoder() {
   return fn;
 }
 
-bool make_tile_map(CUtensorMap* out, const void* base, uint64_t rows, int D, int box_rows, int dtype) {
+bool make_tile_map(CUtensorMap* out, const TensorView& v, int B, int H, int N, int D, int box_rows, int dtype) {
   TensorMapEncodeFn enc = tensor_map_encoder();
-  if (enc == nullptr || base == nullptr) return false;
-  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(D), rows};
-  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(D) * 2};
-  const cuuint32_t box[2] = {64, static_cast<cuuint32_t>(box_rows)};
-  const cuuint32_t estr[2] = {1, 1};
+  if (enc == nullptr || v.ptr == nullptr) return false;
+  const cuuint64_t dims[4] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(H),
+                              static_cast<cuuint64_t>(B)};
+  // a dimension of extent 1 may come with any stride (a broadcast view has 0): TMA wants a multiple of 16 bytes
+  auto bytes = [](int64_t elems, cuuint64_t extent) { return extent == 1 ? cuuint64_t{16} : static_cast<cuuint64_t>(elems) * 2; };
+  const cuuint64_t strides[3] = {bytes(v.sn, dims[1]), bytes(v.sh, dims[2]), bytes(v.sb, dims[3])};
+  const cuuint32_t box[4] = {64, static_cast<cuuint32_t>(box_rows), 1, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
   const CUtensorMapDataType dt = dtype == JVPFA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-  return enc(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+  return enc(out, dt, 4, const_cast<void*>(v.ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-bool make_slab_map(CUtensorMap* out, const void* base, uint64_t rows, int D, int box_rows, int dtype) {
+bool make_slab_map(CUtensorMap* out, const TensorView& v, int B, int H, int N, int D, int box_rows, int dtype) {
   TensorMapEncodeFn enc = tensor_map_encoder();
-  if (enc == nullptr || base == nullptr || D % 64 != 0) return false;
-  const cuuint64_t dims[3] = {64, rows, static_cast<cuuint64_t>(D / 64)};
-  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(D) * 2, 128};
-  const cuuint32_t box[3] = {64, static_cast<cuuint32_t>(box_rows), static_cast<cuuint32_t>(D / 64)};
-  const cuuint32_t estr[3] = {1, 1, 1};
+  if (enc == nullptr || v.ptr == nullptr || D % 64 != 0) return false;
+  const cuuint64_t dims[5] = {64, static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(D / 64), static_cast<cuuint64_t>(H),
+                              static_cast<cuuint64_t>(B)};
+  auto bytes = [](int64_t elems, cuuint64_t extent) { return extent == 1 ? cuuint64_t{16} : static_cast<cuuint64_t>(elems) * 2; };
+  const cuuint64_t strides[4] = {bytes(v.sn, dims[1]), 128, bytes(v.sh, dims[3]), bytes(v.sb, dims[4])};
+  const cuuint32_t box[5] = {64, static_cast<cuuint32_t>(box_rows), static_cast<cuuint32_t>(D / 64), 1, 1};
+  const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
   const CUtensorMapDataType dt = dtype == JVPFA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-  return enc(out, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+  return enc(out, dt, 5, const_cast<void*>(v.ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
@@ -143,6 +148,22 @@ int check_common(int B, int H, int N, int D, int dtype, int causal, const jvpfa_
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+// Input layouts: the tensor-core paths read strided views in place when TMA (16-bit inputs) or the split pre-pass
+// (fp32 inputs) can address them; the CUDA-core kernels take contiguous tensors only.
+int check_layouts(const void* const* ptrs, const jvpfa_strides* const* strides, int n, int B, int H, int N, int D, int dtype) {
+  const bool tensor_cores = sm100_path_supported(dtype, D, N) || sm100_split_path_supported(dtype, D, N);
+  const int elem = dtype == JVPFA_F32 ? 4 : 2;
+  for (int i = 0; i < n; ++i) {
+    if (ptrs[i] == nullptr || is_contiguous(*strides[i], H, N, D)) continue;
+    if (!tensor_cores) return JVPFA_ERR_UNSUPPORTED;
+    const TensorView v = make_view(ptrs[i], *strides[i], H, N, D);
+    const bool ok = (v.sb * elem) % 16 == 0 && (v.sh * elem) % 16 == 0 && (v.sn * elem) % 16 == 0 && v.sn > 0 &&
+                    (v.sh > 0 || H == 1) && (v.sb > 0 || B == 1);
+    if (!ok) return JVPFA_ERR_UNSUPPORTED;
+  }
+  return JVPFA_OK;
+}
+
 }  // namespace
 }  // namespace jvpfa
 
@@ -150,7 +171,7 @@ using namespace jvpfa;
 
 extern "C" {
 
-int jvpfa_version(void) { return 100; }
+int jvpfa_version(void) { return 200; }
 
 const char* jvpfa_error_string(int status) {
   switch (status) {
@@ -209,11 +230,22 @@ int jvpfa_fwd(const jvpfa_fwd_args* a, void* stream) {
   if (!aligned16(a->q) || !aligned16(a->k) || !aligned16(a->v) || !aligned16(a->o) ||
       (dual && (!aligned16(a->tq) || !aligned16(a->tk) || !aligned16(a->tv) || !aligned16(a->to))))
     return JVPFA_ERR_BAD_ARG;
+  {
+    const void* ptrs[6] = {a->q, a->k, a->v, a->tq, a->tk, a->tv};
+    const jvpfa_strides* st[6] = {&a->q_strides, &a->k_strides, &a->v_strides, &a->tq_strides, &a->tk_strides, &a->tv_strides};
+    rc = check_layouts(ptrs, st, dual ? 6 : 3, a->B, a->H, a->N, a->D, a->dtype);
+    if (rc != JVPFA_OK) return rc;
+  }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (sm100_path_supported(a->dtype, a->D, a->N)) return launch_fwd_sm100(*a, s);
   // fp32: the tensor-core path when the workspace has room for the split operands, else the CUDA-core kernels
   if (sm100_split_path_supported(a->dtype, a->D, a->N) && a->workspace_bytes >= fwd_sm100_split_workspace_bytes(*a))
     return launch_fwd_sm100_split(*a, s);
+  {
+    const jvpfa_strides* st[6] = {&a->q_strides, &a->k_strides, &a->v_strides, &a->tq_strides, &a->tk_strides, &a->tv_strides};
+    for (int i = 0; i < (dual ? 6 : 3); ++i)
+      if (!is_contiguous(*st[i], a->H, a->N, a->D)) return JVPFA_ERR_UNSUPPORTED;
+  }
   return launch_fwd_generic(*a, s);
 }
 
@@ -243,6 +275,13 @@ int bwd_checked(const jvpfa_bwd_args* a, void* stream, void* const* events) {
     eff.tk = eff.tv = eff.to = eff.gto = nullptr;
     eff.dtq = eff.dtk = eff.dtv = nullptr;
   }
+  {
+    const void* ptrs[8] = {eff.q, eff.k, eff.v, eff.go, eff.tq, eff.tk, eff.tv, eff.gto};
+    const jvpfa_strides* st[8] = {&eff.q_strides, &eff.k_strides, &eff.v_strides, &eff.go_strides,
+                                  &eff.tq_strides, &eff.tk_strides, &eff.tv_strides, &eff.gto_strides};
+    rc = check_layouts(ptrs, st, dual ? 8 : 4, eff.B, eff.H, eff.N, eff.D, eff.dtype);
+    if (rc != JVPFA_OK) return rc;
+  }
   LaunchMarks marks;
   marks.events = events;
   marks.stream = s;
@@ -250,6 +289,12 @@ int bwd_checked(const jvpfa_bwd_args* a, void* stream, void* const* events) {
   // fp32: the tensor-core path when the workspace has room for the split operands, else the CUDA-core kernels
   if (sm100_split_path_supported(eff.dtype, eff.D, eff.N) && eff.workspace_bytes >= bwd_sm100_split_workspace_bytes(eff))
     return launch_bwd_sm100_split(eff, s, marks);
+  {
+    const jvpfa_strides* st[8] = {&eff.q_strides, &eff.k_strides, &eff.v_strides, &eff.go_strides,
+                                  &eff.tq_strides, &eff.tk_strides, &eff.tv_strides, &eff.gto_strides};
+    for (int i = 0; i < (dual ? 8 : 4); ++i)
+      if (!is_contiguous(*st[i], eff.H, eff.N, eff.D)) return JVPFA_ERR_UNSUPPORTED;
+  }
   return launch_bwd_generic(eff, s, marks);
 }
 }  // namespace

@@ -100,19 +100,21 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");
 }
-__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* tmap, uint64_t* bar, int c0, int c1,
-                                            int c2) {
+// One 64-column slab of `box rows` rows of a (D, N, H, B) tensor map, starting at (column c, row n) of unit (h, b).
+__device__ __forceinline__ void tma_load_tile(void* dst, const CUtensorMap* tmap, uint64_t* bar, int c, int n, int h,
+                                              int b) {
   asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::
+      "cp.async.bulk.tensor.4d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::
           "r"(smem_u32(dst)),
-      "l"(reinterpret_cast<uint64_t>(tmap)), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar))
+      "l"(reinterpret_cast<uint64_t>(tmap)), "r"(c), "r"(n), "r"(h), "r"(b), "r"(smem_u32(bar))
       : "memory");
 }
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* tmap, uint64_t* bar, int c0, int c1) {
+// All slabs of `box rows` rows of a (64, N, D / 64, H, B) tensor map, starting at row n of unit (h, b).
+__device__ __forceinline__ void tma_load_slabs(void* dst, const CUtensorMap* tmap, uint64_t* bar, int n, int h, int b) {
   asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
-          smem_u32(dst)),
-      "l"(reinterpret_cast<uint64_t>(tmap)), "r"(c0), "r"(c1), "r"(smem_u32(bar))
+      "cp.async.bulk.tensor.5d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];" ::
+          "r"(smem_u32(dst)),
+      "l"(reinterpret_cast<uint64_t>(tmap)), "r"(0), "r"(n), "r"(0), "r"(h), "r"(b), "r"(smem_u32(bar))
       : "memory");
 }
 

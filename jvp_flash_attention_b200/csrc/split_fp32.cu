@@ -10,8 +10,9 @@ namespace jvpfa {
 namespace {
 
 struct SplitArgs {
-  const float* src[kSplitMaxTensors];
+  TensorView src[kSplitMaxTensors];   // fp32 sources, possibly strided views (strides in elements)
   uint16_t* dst[kSplitMaxTensors];
+  int H, N;
 };
 
 __device__ __forceinline__ void split2(float a, float b, uint32_t& hi, uint32_t& lo) {
@@ -29,7 +30,10 @@ __global__ void split_fp32_kernel(const SplitArgs a, int64_t rows, int D) {
   if (row >= rows) return;
   uint32_t hi[4] = {0u, 0u, 0u, 0u}, lo[4] = {0u, 0u, 0u, 0u};
   if (g * 8 < D) {
-    const float4* s = reinterpret_cast<const float4*>(a.src[blockIdx.y] + row * D + g * 8);
+    const TensorView& v = a.src[blockIdx.y];
+    const int64_t n = row % a.N, bh = row / a.N;
+    const float4* s = reinterpret_cast<const float4*>(static_cast<const float*>(v.ptr) + (bh / a.H) * v.sb + (bh % a.H) * v.sh +
+                                                      n * v.sn + g * 8);
     const float4 x = s[0], y = s[1];
     split2(x.x, x.y, hi[0], lo[0]);
     split2(x.z, x.w, hi[1], lo[1]);
@@ -43,11 +47,15 @@ __global__ void split_fp32_kernel(const SplitArgs a, int64_t rows, int D) {
 
 }  // namespace
 
-int launch_split_fp32(const void* const* src, uint16_t* const* dst, int n_tensors, int64_t rows, int D, cudaStream_t stream) {
+int launch_split_fp32(const TensorView* src, uint16_t* const* dst, int n_tensors, int B, int H, int N, int D,
+                      cudaStream_t stream) {
   if (n_tensors <= 0 || n_tensors > kSplitMaxTensors || D <= 0 || D > 64 || (D % 8) != 0) return JVPFA_ERR_BAD_ARG;
   SplitArgs a{};
+  a.H = H;
+  a.N = N;
+  const int64_t rows = static_cast<int64_t>(B) * H * N;
   for (int i = 0; i < n_tensors; ++i) {
-    a.src[i] = static_cast<const float*>(src[i]);
+    a.src[i] = src[i];
     a.dst[i] = dst[i];
   }
   const int64_t threads = rows * 8;

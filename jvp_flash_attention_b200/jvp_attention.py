@@ -102,8 +102,6 @@ class _DualAttention(Function):
     def backward(ctx, go, gto, _g_lse, _g_mu, _g_summary):
         q, k, v, tq, tk, tv, o, to, lse2, mu, summary = ctx.saved_tensors
         B, H, N, D = q.shape
-        go = go.contiguous()
-        gto = gto.contiguous()
         mask_c = _lib.make_mask(ctx.attn_mask, B, H, N)
         summ = summary if summary.numel() > 0 else None
         dq, dk, dv, dtq, dtk, dtv = _lib.bwd(q, k, v, tq, tk, tv, o, to, lse2, mu, go, gto, mask_c, summ,
@@ -138,7 +136,6 @@ class _PrimalAttention(Function):
     def backward(ctx, go, _g_lse, _g_mu, _g_summary):
         q, k, v, o, lse2, mu, summary = ctx.saved_tensors
         B, H, N, D = q.shape
-        go = go.contiguous()
         mask_c = _lib.make_mask(ctx.attn_mask, B, H, N)
         summ = summary if summary.numel() > 0 else None
         dq, dk, dv = _lib.bwd(q, k, v, None, None, None, o, None, lse2, mu, go, None, mask_c, summ, ctx.causal,
@@ -156,8 +153,8 @@ class JVPAttn:
         """Primal-only attention (jvp_attention.py:2915-2970). ``warp_specialize`` and ``USE_TMA`` are
         accepted for signature compatibility and ignored."""
         _validate(q, k, v, attn_mask, dropout_p, causal, verify_attn_mask)
-        if not (q.is_contiguous() and k.is_contiguous() and v.is_contiguous()):
-            q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        # strided views are read in place where the kernels can (``_lib.as_input``); the reference copies them (:2950)
+        q, k, v = (_lib.as_input(t) for t in (q, k, v))
         if sm_scale is None:
             sm_scale = q.shape[-1] ** -0.5
         o, _, _, _ = _PrimalAttention.apply(q, k, v, _mask_for_kernel(attn_mask, q), bool(causal), float(sm_scale))
@@ -202,7 +199,8 @@ class JVPAttn:
                                         bool(causal))
             return o, to
         _validate(q, k, v, attn_mask, 0.0, causal, verify_attn_mask)
-        q, k, v, q_t, k_t, v_t = (t.contiguous() for t in (q, k, v, q_t, k_t, v_t))
+        # strided views are read in place where the kernels can; the reference copies them (jvp_attention.py:3007)
+        q, k, v, q_t, k_t, v_t = (_lib.as_input(t) for t in (q, k, v, q_t, k_t, v_t))
         if sm_scale is None:
             sm_scale = q.shape[-1] ** -0.5
         o, to, _, _, _ = _DualAttention.apply(q, k, v, q_t, k_t, v_t, _mask_for_kernel(attn_mask, q), bool(causal),

@@ -58,11 +58,9 @@ def _run_cuda(ts, dev, attn_mask=None, causal=False, sm_scale=None, how="dual_le
     return {n: t.double().cpu() for n, t in out.items()}
 
 
-def _compare(got, ref, tol, slices=None, names=("O", "tO") + GRAD_NAMES, ulp_dtype=None):
-    """Max abs error of every tensor against the oracle, at most ``tol``. With ``ulp_dtype`` the bound of a tensor is
-    ``tol`` or one unit of that type's spacing at the tensor's largest oracle value, whichever is larger (bf16 keeps 8
-    significant bits: a tensor that reaches magnitude 4 is stored, and its 16-bit operands are rounded, in steps of up to
-    0.03)."""
+def _compare(got, ref, tol, slices=None, names=("O", "tO") + GRAD_NAMES, grad_tol=None):
+    """Max abs error of every tensor against the oracle: at most ``tol`` (``grad_tol``, if given, for the six
+    gradients)."""
     worst, bad = {}, {}
     for n in names:
         r = ref[n]
@@ -72,15 +70,12 @@ def _compare(got, ref, tol, slices=None, names=("O", "tO") + GRAD_NAMES, ulp_dty
             g = torch.stack([g[b, h] for b, h in slices])
         assert torch.isfinite(g).all(), f"{n} has non-finite values"
         err = (g - r).abs()
-        allowed = tol
-        if ulp_dtype is not None:
-            mant = 7 if ulp_dtype == torch.bfloat16 else 10
-            allowed = max(tol, 2.0 ** (math.floor(math.log2(float(r.abs().max()))) - mant))
+        allowed = grad_tol if (grad_tol is not None and n in GRAD_NAMES) else tol
         worst[n] = float(err.max())
         if worst[n] > allowed:
             i = int(torch.argmax(err))
             bad[n] = {"error": worst[n], "allowed": allowed, "oracle value": float(r.flatten()[i]), "oracle max": float(r.abs().max())}
-    assert not bad, f"max abs error over tolerance {tol}: {bad} (all: {worst})"
+    assert not bad, f"max abs error over tolerance: {bad} (all: {worst})"
     return worst
 
 
@@ -119,10 +114,11 @@ def test_cfg3_causal_headline_shape(dev, dtype):
     interior = [(int(rng.integers(1, B - 1)), int(rng.integers(0, H))) for _ in range(2)]
     slices = [(0, 0), (7, 15)] + interior
     ref = closed_form_oracle(*ts, causal=True, slices=slices)
-    # fp16: 2e-2 everywhere. bf16: N(0,1) inputs at this length give gradients of magnitude 4 to 8, and the 16-bit operands
-    # P, dS of the products carry 8 significant bits, so a gradient tensor is allowed one bf16 step at its largest value
-    # (up to 0.06; measured: up to 0.05 on interior units, 0.018 on the first and the last one)
-    _compare(got, ref, TOL[dtype], slices, ulp_dtype=dtype if dtype == torch.bfloat16 else None)
+    # fp16: 2e-2 everywhere. bf16: 2e-2 for O and tO; the gradients of N(0,1) inputs at this length reach magnitude 6 to 8
+    # and are sums of a few large terms whose 16-bit operands (P, dS) carry 8 significant bits, so single elements are off
+    # by up to 5e-2 on interior units (1.8e-2 on the first and the last unit): 6e-2 is the bound enforced here, stated for
+    # what it is -- bf16 operand rounding, not a tolerance the 2e-2 target covers.
+    _compare(got, ref, TOL[dtype], slices, grad_tol=6e-2 if dtype == torch.bfloat16 else None)
 
 
 @pytest.mark.parametrize("kind", ["bool", "block_sparse", "additive"])
@@ -398,3 +394,89 @@ def test_torch_compile_fwd_dual(dev, how):
     ref = closed_form_oracle(*ts, causal=True)
     got = {"O": o.detach(), "tO": to.detach(), **dict(zip(GRAD_NAMES, grads))}
     _compare({n: t.double().cpu() for n, t in got.items()}, ref, TOL[torch.bfloat16])
+
+
+def test_fp32_tensor_core_and_cuda_core_paths(dev):
+    """fp32 inputs with a head dimension of at most 64 run on the tensor cores when the workspace has room for the split
+    operands (what ``jvpfa_*_workspace_bytes`` asks for) and on the CUDA cores when it has not; both through the C ABI,
+    both within 1e-4 of the oracle."""
+    import ctypes as C
+    from jvp_flash_attention_b200 import _lib
+    B, H, N, D = 1, 2, 256, 64
+    ts = make_inputs(B, H, N, D, dtype=torch.float32, seed=9)
+    q, k, v, tq, tk, tv, go, gto = [t.to(dev) for t in ts]
+    ref = closed_form_oracle(*ts, causal=True)
+    s = 1.0 / math.sqrt(D)
+    L = _lib.lib()
+    rows = B * H * N
+    for path in ("tensor cores", "cuda cores"):
+        o, to = torch.empty_like(q), torch.empty_like(q)
+        lse2 = torch.empty(B, H, N, device=dev)
+        mu = torch.empty(B, H, N, device=dev)
+        fa = _lib.FwdArgs()
+        fa.B, fa.H, fa.N, fa.D = B, H, N, D
+        fa.dtype, fa.causal, fa.sm_scale = _lib.F32, 1, s
+        fa.mask, fa.mask_summary = _lib.make_mask(None, B, H, N), None
+        fa.q, fa.k, fa.v, fa.tq, fa.tk, fa.tv = (t.data_ptr() for t in (q, k, v, tq, tk, tv))
+        fa.o, fa.to, fa.lse2, fa.mu = o.data_ptr(), to.data_ptr(), lse2.data_ptr(), mu.data_ptr()
+        want_f = L.jvpfa_fwd_workspace_bytes(C.byref(fa))
+        assert want_f == 256 + 6 * rows * 256
+        ws_f = torch.zeros(want_f if path == "tensor cores" else 256, dtype=torch.uint8, device=dev)
+        fa.workspace, fa.workspace_bytes = ws_f.data_ptr(), ws_f.numel()
+        _lib.check(L.jvpfa_fwd(C.byref(fa), _lib.stream_ptr(dev)))
+        grads = [torch.empty_like(q) for _ in range(6)]
+        ba = _lib.BwdArgs()
+        ba.B, ba.H, ba.N, ba.D = B, H, N, D
+        ba.dtype, ba.causal, ba.sm_scale = _lib.F32, 1, s
+        ba.mask, ba.mask_summary = fa.mask, None
+        ba.q, ba.k, ba.v, ba.tq, ba.tk, ba.tv = (t.data_ptr() for t in (q, k, v, tq, tk, tv))
+        ba.o, ba.to, ba.lse2, ba.mu = o.data_ptr(), to.data_ptr(), lse2.data_ptr(), mu.data_ptr()
+        ba.go, ba.gto = go.data_ptr(), gto.data_ptr()
+        ba.dq, ba.dk, ba.dv, ba.dtq, ba.dtk, ba.dtv = (t.data_ptr() for t in grads)
+        want_b = L.jvpfa_bwd_workspace_bytes(C.byref(ba))
+        assert want_b >= 256 + 16 * rows + 8 * rows * 256
+        ws_b = torch.zeros(want_b if path == "tensor cores" else 256 + 16 * rows, dtype=torch.uint8, device=dev)
+        ba.workspace, ba.workspace_bytes = ws_b.data_ptr(), ws_b.numel()
+        _lib.check(L.jvpfa_bwd(C.byref(ba), _lib.stream_ptr(dev)))
+        torch.cuda.synchronize()
+        for ws in (ws_f, ws_b):
+            assert int(ws[:4].view(torch.int32).item()) == 0, "a device-side wait gave up"
+        got = {"O": o, "tO": to, **dict(zip(GRAD_NAMES, grads))}
+        _compare({n: t.double().cpu() for n, t in got.items()}, ref, TOL[torch.float32])
+
+
+@pytest.mark.parametrize("dtype,D", [(torch.bfloat16, 72), (torch.float16, 128), (torch.float32, 64)])
+def test_strided_inputs_are_read_in_place(dev, dtype, D):
+    """q, k, v (and their tangents) as views of one fused projection, ``qkv.permute(2, 0, 3, 1, 4)[i]`` -- the reference
+    copies such inputs (jvp_attention.py:2950, 3007); here the tensor maps carry the strides. Upstream gradients arrive
+    as transposed views. Results against the oracle, and bit-equal to the run on contiguous copies."""
+    from jvp_flash_attention_b200 import _lib
+    JVPAttn, _ = _api()
+    B, H, N = 2, 4, 200
+    g = torch.Generator().manual_seed(31)
+    scale = 0.5 if dtype == torch.bfloat16 else 1.0
+    qkv = (torch.randn(B, N, 3, H, D, generator=g) * scale).to(dtype)
+    tqkv = (torch.randn(B, N, 3, H, D, generator=g) * scale).to(dtype)
+    gO = torch.randn(B, N, H, D, generator=g).to(dtype)
+    gtO = torch.randn(B, N, H, D, generator=g).to(dtype)
+    views = lambda t: [t.permute(2, 0, 3, 1, 4)[i] for i in range(3)]
+    ts = [*views(qkv), *views(tqkv), gO.transpose(1, 2), gtO.transpose(1, 2)]         # all (B, H, N, D), none contiguous
+    ref = closed_form_oracle(*[t.contiguous() for t in ts], causal=True)
+
+    def run(make):
+        dq, dt = qkv.to(dev), tqkv.to(dev)
+        ins = [make(v) for v in (*views(dq), *views(dt))]
+        assert all(_lib.readable_in_place(v) for v in ins)
+        leaves = [v.detach().requires_grad_(True) for v in ins]
+        O, tO = JVPAttn.dual(*leaves, causal=True)
+        go, gto = make(gO.to(dev).transpose(1, 2)), make(gtO.to(dev).transpose(1, 2))
+        grads = torch.autograd.grad([O, tO], leaves, [go, gto])
+        torch.cuda.synchronize()
+        _lib.read_status(dev)
+        return {"O": O.detach(), "tO": tO.detach(), **dict(zip(GRAD_NAMES, grads))}
+
+    strided = run(lambda v: v)
+    copied = run(lambda v: v.contiguous())
+    assert all(t.is_contiguous() for t in strided.values())
+    assert all(torch.equal(strided[n], copied[n]) for n in strided)
+    _compare({n: t.double().cpu() for n, t in strided.items()}, ref, TOL[dtype])
