@@ -283,6 +283,27 @@ def gpu_incumbent_record(args, timeout_s=420):
     return {"unavailable": f"reference-on-B200: unavailable (child exit code {r.returncode}: {tail[0][:300]})"}
 
 
+def dit_record(timeout_s=300):
+    """The end-to-end configuration (bench_dit.py: DiT JVP training step, 32 samples on this GPU) with this library's
+    attention and, for an A/B on the same box, with SDPA forced to its MATH backend; child processes."""
+    import subprocess
+    rec = {}
+    for impl in ("jvpfa", "sdpa"):
+        cmd = [sys.executable, os.path.join(ROOT, "bench_dit.py"), "--steps", "4", "--warmup", "2", "--attention", impl]
+        try:
+            r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout_s, cwd=ROOT)
+            line = [ln for ln in r.stdout.strip().splitlines() if ln.startswith("{")]
+            d = json.loads(line[-1])
+            rec[impl] = {"ms_per_step": d["ms_per_step"], "samples_per_s": d["value"], "loss": d["loss"]}
+        except Exception as exc:  # noqa: BLE001
+            rec[impl] = {"unavailable": f"{type(exc).__name__}: {exc}"[:200]}
+    if "ms_per_step" in rec.get("jvpfa", {}) and "ms_per_step" in rec.get("sdpa", {}):
+        rec["speedup_vs_sdpa_math"] = rec["sdpa"]["ms_per_step"] / rec["jvpfa"]["ms_per_step"]
+    rec["workload"] = ("DiT 28 blocks, hidden 1152, 16 heads of 72, 256 tokens, bf16, 32 samples: torch.func.jvp + MSE on "
+                       "primal and tangent + backward + AdamW")
+    return rec
+
+
 # ------------------------------------------------------------------------------------------------
 # CUDA arm
 # ------------------------------------------------------------------------------------------------
@@ -515,6 +536,12 @@ def run_cuda(args, rank, world, local_rank):
         torch.cuda.empty_cache()
         incumbent = gpu_incumbent_record(args)
 
+    # ---- the end-to-end model configuration (rank 0, N = 1 only) ----
+    dit = None
+    if rank == 0 and world == 1 and not args.no_dit:
+        torch.cuda.empty_cache()
+        dit = dit_record()
+
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
@@ -531,7 +558,7 @@ def run_cuda(args, rank, world, local_rank):
             "frac_of_measured_peak": value / world / peak_burst,
             "frac_of_measured_sustained_peak": value / world / peak_sustained,
             "roofline": roofline, "kernels": kernels, other_name: other_rec, "weak": weak,
-            "cpu_baseline": cpu_baseline, "gpu_incumbent": incumbent, "e2e": e2e,
+            "cpu_baseline": cpu_baseline, "gpu_incumbent": incumbent, "dit": dit, "e2e": e2e,
             "gpu_launches": 5 * args.steps, "clocks": clocks.summary(),
         }
         sys.stdout.flush()
@@ -556,6 +583,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-weak", action="store_true")
     ap.add_argument("--no-incumbent", action="store_true")
+    ap.add_argument("--no-dit", action="store_true")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -59,7 +59,7 @@ class Attention(nn.Module):
     def forward(self, x):
         B, N, C = x.shape
         qkv = self.qkv(x).reshape(B, N, 3, self.heads, C // self.heads).permute(2, 0, 3, 1, 4)
-        q, k, v = qkv[0].contiguous(), qkv[1].contiguous(), qkv[2].contiguous()
+        q, k, v = qkv[0], qkv[1], qkv[2]        # strided views of the fused projection; the kernels read them in place
         if self.impl == "jvpfa":
             from jvp_flash_attention_b200.jvp_attention import JVPAttn
             o = JVPAttn.fwd_dual(q, k, v, verify_attn_mask=False)

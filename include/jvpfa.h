@@ -153,7 +153,10 @@ int jvpfa_selftest_timeout(void* workspace, int32_t budget_us, int32_t* out4, vo
  * JVPFA_NO_ALLOC_MAX_ROWS rows (B*H*N) are refused with JVPFA_ERR_NO_ALLOC_LIMIT before anything runs.
  *
  * The first call on each device looks up the device address of that array (with that device current);
- * make that first call before starting any stream capture. Every call clears the status word at the
+ * make that first call before starting any stream capture. With CUDA's default lazy module loading that
+ * look-up is also where the driver sets the array up on the device, so a process whose memory pool is about
+ * to claim the rest of the GPU's memory makes the first call before the pool grows (or sets
+ * CUDA_MODULE_LOADING=EAGER). fp32 inputs run on the CUDA-core kernels here. Every call clears the status word at the
  * start of the array on `stream` and then reuses the rest as it is. All calls on a device share the
  * one array: two calls whose kernels can overlap on the GPU (different streams without an ordering
  * between them) race on it and give undefined results -- order them yourself.

@@ -7,7 +7,10 @@
 // still pass its input and output tensors, but has nowhere to get the backward's scratch from (the
 // device status word and one float4 of per-row statistics per query row). This entry point keeps
 // that scratch in a fixed array that is part of the library image, so the call itself allocates
-// nothing: no cudaMalloc, no cudaFree, no allocating library routine.
+// nothing: no cudaMalloc, no cudaFree, no allocating library routine. (With CUDA's lazy module loading the
+// driver sets the image's 4 MiB array up when the first call on a device asks for its address; a caller whose
+// pool is about to take the rest of the GPU's memory makes that first call before the pool grows, or runs
+// with CUDA_MODULE_LOADING=EAGER.)
 #include <mutex>
 #include "host_common.h"
 
@@ -32,7 +35,10 @@ int scratch_address(void** out) {
   std::lock_guard<std::mutex> guard(g_setup_mutex);
   if (g_scratch_addr[dev] == nullptr) {
     void* ptr = nullptr;
-    if (cudaGetSymbolAddress(&ptr, g_noalloc_scratch) != cudaSuccess || ptr == nullptr) return JVPFA_ERR_LAUNCH;
+    if (cudaGetSymbolAddress(&ptr, g_noalloc_scratch) != cudaSuccess || ptr == nullptr) {
+      (void)cudaGetLastError();   // do not leave the failed look-up behind as this thread's sticky error
+      return JVPFA_ERR_LAUNCH;
+    }
     g_scratch_addr[dev] = ptr;
   }
   *out = g_scratch_addr[dev];
@@ -56,7 +62,9 @@ extern "C" int jvpfa_bwd_noalloc(const jvpfa_bwd_args* args, int32_t* status_wor
   if (cudaMemsetAsync(scratch, 0, jvpfa::kStatusBytes, s) != cudaSuccess) return JVPFA_ERR_LAUNCH;
   jvpfa_bwd_args with_scratch = *args;
   with_scratch.workspace = scratch;
-  with_scratch.workspace_bytes = kNoAllocBytes;
+  // exactly what the status word and the statistics take: fp32 inputs therefore run on the CUDA-core kernels here
+  // (their tensor-core path would want room for split operands that this fixed array does not have)
+  with_scratch.workspace_bytes = jvpfa::kStatusBytes + static_cast<size_t>(rows) * 16;
   rc = jvpfa_bwd(&with_scratch, stream);
   if (rc != JVPFA_OK) return rc;
   if (status_word_out != nullptr &&
