@@ -156,8 +156,13 @@ def tensor_core_path(dtype: torch.dtype, D: int) -> bool:
 def readable_in_place(t: torch.Tensor) -> bool:
     """A (B,H,N,D) input the tensor-core kernels can read as it is: last axis contiguous, every other stride (of an
     axis longer than 1) positive and a multiple of 16 bytes, 16-byte aligned storage."""
-    if t.stride(-1) != 1 or t.data_ptr() % 16 != 0:
+    if t.stride(-1) != 1:
         return False
+    try:
+        if t.data_ptr() % 16 != 0:
+            return False
+    except RuntimeError:
+        pass        # a functorch wrapper without storage: the launch wrappers look again at the plain tensor inside
     es = t.element_size()
     for dim in range(3):
         if t.shape[dim] > 1 and (t.stride(dim) <= 0 or (t.stride(dim) * es) % 16 != 0):
