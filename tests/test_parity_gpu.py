@@ -480,3 +480,36 @@ def test_strided_inputs_are_read_in_place(dev, dtype, D):
     assert all(t.is_contiguous() for t in strided.values())
     assert all(torch.equal(strided[n], copied[n]) for n in strided)
     _compare({n: t.double().cpu() for n, t in strided.items()}, ref, TOL[dtype])
+
+
+def test_hessian_vector_product_reverse_over_forward(dev):
+    """The reference advertises Hessian-vector products (README.md:18) but its backward ignores the tangent output
+    (jvp_attention.py:3081, 3226), so the reverse-over-forward form cannot pass through it. Here it can: for
+    f(q) = 1/2 |attention(q, k, v)|^2 the directional derivative along u is <O, tO>, a function of both outputs of the dual
+    call, and its gradient with respect to q is H u. Checked against autograd-of-autograd over SDPA-MATH in fp64."""
+    import torch.nn.functional as F
+    from torch.nn.attention import SDPBackend, sdpa_kernel
+    JVPAttn, _ = _api()
+    B, H, N, D = 1, 2, 128, 64
+    g = torch.Generator().manual_seed(12)
+    q, k, v, u = [torch.randn(B, H, N, D, generator=g) * 0.5 for _ in range(4)]
+    # oracle: H u = d/dq <grad f(q), u>
+    qd = q.double().requires_grad_(True)
+    with sdpa_kernel(SDPBackend.MATH):
+        o = F.scaled_dot_product_attention(qd, k.double(), v.double(), is_causal=True)
+    (gq,) = torch.autograd.grad(0.5 * (o * o).sum(), qd, create_graph=True)
+    (hu_ref,) = torch.autograd.grad((gq * u.double()).sum(), qd)
+    for dtype, tol in ((torch.float32, 1e-4), (torch.float16, 2e-2)):
+        ql = q.to(dev, dtype).requires_grad_(True)
+        z = torch.zeros(B, H, N, D, device=dev, dtype=dtype)
+        O, tO = JVPAttn.dual(ql, k.to(dev, dtype), v.to(dev, dtype), u.to(dev, dtype), z, z, causal=True)
+        (hu,) = torch.autograd.grad((O * tO).sum(), ql)
+        ref = hu_ref if dtype == torch.float32 else None
+        if ref is None:   # the oracle on the rounded inputs
+            qd2 = q.to(dtype).double().requires_grad_(True)
+            with sdpa_kernel(SDPBackend.MATH):
+                o2 = F.scaled_dot_product_attention(qd2, k.to(dtype).double(), v.to(dtype).double(), is_causal=True)
+            (g2,) = torch.autograd.grad(0.5 * (o2 * o2).sum(), qd2, create_graph=True)
+            (ref,) = torch.autograd.grad((g2 * u.to(dtype).double()).sum(), qd2)
+        err = float((hu.double().cpu() - ref).abs().max())
+        assert err <= tol, (dtype, err)
