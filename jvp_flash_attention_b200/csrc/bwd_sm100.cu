@@ -42,6 +42,8 @@ enum { FAM_Q = 0, FAM_K = 1, FAM_V = 2 };
 
 struct BwdKParams {
   int H, N;
+  int n_rt, n_units;   // row tiles per (batch, head) unit, number of units: the grid has n_rt * n_units blocks
+  int unit_group;      // units per group of the block order
   int D;     // head dimension of the tensors (the kernel is compiled for it rounded up to 64 or 128)
   int causal;
   float c1;  // sm_scale * log2(e)
@@ -166,10 +168,11 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
   }
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int n_rt = gridDim.x;
+  const int n_rt = p.n_rt;
   // heavier tiles first under a causal mask: late query tiles, early key tiles
-  const int rt = (p.causal && FAM == FAM_Q) ? (n_rt - 1 - static_cast<int>(blockIdx.x)) : blockIdx.x;
-  const int bh = blockIdx.y;
+  const BlockWork work = block_work(blockIdx.x, n_rt, p.n_units, p.unit_group, p.causal && FAM == FAM_Q);
+  const int rt = work.tile;
+  const int bh = work.unit;
   const int b = bh / p.H, h = bh % p.H;
   const int r0 = rt * C::BR;
   const int N = p.N;
@@ -924,7 +927,10 @@ int launch_family(const jvpfa_bwd_args& a, const float4* stats, cudaStream_t str
   const size_t smem = C::smem_bytes();
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
     return JVPFA_ERR_LAUNCH;
-  dim3 grid((a.N + C::BR - 1) / C::BR, a.B * a.H);
+  p.n_rt = (a.N + C::BR - 1) / C::BR;
+  p.n_units = a.B * a.H;
+  p.unit_group = unit_group_size(p.n_units);
+  dim3 grid(static_cast<unsigned>(p.n_rt) * static_cast<unsigned>(p.n_units));
   kern<<<grid, 352, smem, stream>>>(rm[0], rm[1], rm[2], rm[3], cm[0], cm[1], cm[2], cm[3], p);
   return cudaGetLastError() == cudaSuccess ? JVPFA_OK : JVPFA_ERR_LAUNCH;
 }

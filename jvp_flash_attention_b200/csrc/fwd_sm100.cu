@@ -34,6 +34,8 @@ namespace {
 
 struct FwdKParams {
   int H, N;
+  int n_qt, n_units;   // query tiles per (batch, head) unit, number of units: the grid has n_qt * n_units blocks
+  int unit_group;      // units per group of the block order
   int D;       // head dimension of the tensors (the kernel is compiled for it rounded up to 64 or 128)
   int causal;
   float c1;      // sm_scale * log2(e)
@@ -143,8 +145,9 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   }
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int qt = p.causal ? (static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x)) : blockIdx.x;
-  const int bh = blockIdx.y;
+  const BlockWork work = block_work(blockIdx.x, p.n_qt, p.n_units, p.unit_group, p.causal != 0);   // heavy query tiles first
+  const int qt = work.tile;
+  const int bh = work.unit;
   const int b = bh / p.H, h = bh % p.H;
   const int q0 = qt * C::BM;
   const int N = p.N;
@@ -635,7 +638,10 @@ int launch_one(const jvpfa_fwd_args& a, cudaStream_t stream) {
   const size_t smem = C::smem_bytes();
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
     return JVPFA_ERR_LAUNCH;
-  dim3 grid((a.N + C::BM - 1) / C::BM, a.B * a.H);
+  p.n_qt = (a.N + C::BM - 1) / C::BM;
+  p.n_units = a.B * a.H;
+  p.unit_group = unit_group_size(p.n_units);
+  dim3 grid(static_cast<unsigned>(p.n_qt) * static_cast<unsigned>(p.n_units));
   kern<<<grid, 384, smem, stream>>>(mQ, mTQ, mK, mTK, mV, mTV, p);
   return cudaGetLastError() == cudaSuccess ? JVPFA_OK : JVPFA_ERR_LAUNCH;
 }
@@ -687,7 +693,10 @@ int launch_split(const jvpfa_fwd_args& a, cudaStream_t stream) {
   const size_t smem = C::smem_bytes();
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
     return JVPFA_ERR_LAUNCH;
-  dim3 grid((a.N + C::BM - 1) / C::BM, a.B * a.H);
+  p.n_qt = (a.N + C::BM - 1) / C::BM;
+  p.n_units = a.B * a.H;
+  p.unit_group = unit_group_size(p.n_units);
+  dim3 grid(static_cast<unsigned>(p.n_qt) * static_cast<unsigned>(p.n_units));
   kern<<<grid, 384, smem, stream>>>(mQ, mTQ, mK, mTK, mV, mTV, p);
   return cudaGetLastError() == cudaSuccess ? JVPFA_OK : JVPFA_ERR_LAUNCH;
 }

@@ -47,6 +47,9 @@ bool make_tile_map(CUtensorMap* out, const TensorView& v, int B, int H, int N, i
 // unit of an SM delivers 43 B/clk in 32 KB boxes, 36 in 16 KB boxes and 29 in 8 KB boxes (measured).
 bool make_slab_map(CUtensorMap* out, const TensorView& v, int B, int H, int N, int D, int box_rows, int dtype);
 
+// Units per group of the block order (see block_work in sm100_prims.cuh).
+int unit_group_size(int n_units);
+
 // Wait budget of a single device-side mbarrier wait, in nanoseconds (JVPFA_WAIT_BUDGET_MS, default 4000 ms).
 uint64_t wait_budget_ns();
 

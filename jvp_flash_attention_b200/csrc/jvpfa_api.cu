@@ -53,6 +53,13 @@ bool make_slab_map(CUtensorMap* out, const TensorView& v, int B, int H, int N, i
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+int unit_group_size(int n_units) {
+  // Measured on the causal headline shape: with 16 or 32 units on a GPU groups of 4, 8 and 16 units are 9-15 % faster
+  // than unit-by-unit order and equal among themselves; with 128 units all group sizes are within noise of one another.
+  // 4 keeps the working set that the running blocks stream (4 MB per unit at N = 4096, D = 128) far below the L2 size.
+  return n_units < 4 ? (n_units < 1 ? 1 : n_units) : 4;
+}
+
 uint64_t wait_budget_ns() {
   static uint64_t ns = [] {
     const char* e = std::getenv("JVPFA_WAIT_BUDGET_MS");

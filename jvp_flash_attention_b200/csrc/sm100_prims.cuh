@@ -307,6 +307,32 @@ __device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t nthreads) {
 }
 
 // ---------------------------------------------------------------------------------------------
+// Order of the CTAs of a launch. The hardware hands out blocks in increasing blockIdx.x, one whenever an SM has
+// room, which is a dynamic longest-first schedule if heavy blocks come first. Under a causal mask the cost of a
+// (row tile, batch*head unit) block depends on the row tile, so inside a group of `unit_group` units all units' heaviest
+// tiles come first, then the next heaviest, and so on (a unit-by-unit order leaves a tail of heavy blocks of the last
+// unit, which shows once a GPU holds only a few units); groups follow one another so that the key/value (or query-side)
+// tensors the running blocks stream stay a working set of that many units in L2.
+// ---------------------------------------------------------------------------------------------
+struct BlockWork {
+  int tile;   // row tile of the block
+  int unit;   // batch * head unit
+};
+// `descending`: the heaviest row tile is the last one (queries under a causal mask), else the first.
+__device__ __forceinline__ BlockWork block_work(int block, int n_tiles, int n_units, int unit_group, bool descending) {
+  const int per_group = unit_group * n_tiles;
+  const int g = block / per_group;
+  const int rem = block - g * per_group;
+  const int u0 = g * unit_group;
+  const int gs = min(unit_group, n_units - u0);
+  const int ti = rem / gs;
+  BlockWork w;
+  w.tile = descending ? n_tiles - 1 - ti : ti;
+  w.unit = u0 + (rem - ti * gs);
+  return w;
+}
+
+// ---------------------------------------------------------------------------------------------
 // Epilogue stores. After a 32x32b TMEM load every lane of a warp holds one output row; written as they are, one
 // 16-byte store instruction touches 32 different 128-byte lines and the kernel spends thousands of cycles in the
 // store unit. The rows go through a per-warp shared-memory patch instead, so that each store instruction writes
