@@ -57,6 +57,7 @@ class ClockSampler:
     def __init__(self, index: int, period_s: float = 0.02):
         self.index, self.period, self.samples, self.reasons, self.power = index, period_s, [], set(), []
         self.max_mhz, self._stop, self._thread, self.ok = None, threading.Event(), None, False
+        self.in_kernel_mhz = None
         try:
             import pynvml
             pynvml.nvmlInit()
@@ -101,10 +102,13 @@ class ClockSampler:
 
     def summary(self):
         if not self.ok or not self.samples:
-            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "note": "NVML unavailable"}
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "note": "NVML unavailable",
+                    "sm_mhz_in_kernel": self.in_kernel_mhz}
         return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
                 "samples": len(self.samples), "power_w_median": statistics.median(self.power) if self.power else None,
-                "power_w_max": max(self.power) if self.power else None}
+                "power_w_max": max(self.power) if self.power else None,
+                # cycles per microsecond counted on an SM beside the timed kernels (NVML's figure is sampled between them)
+                "sm_mhz_in_kernel": self.in_kernel_mhz}
 
 
 def physical_gpu_index(local: int) -> int:
@@ -344,6 +348,8 @@ def run_cuda(args, rank, world, local_rank):
             return float(t)
         return ms
 
+    probe_stream = torch.cuda.Stream(dev)
+
     def make_inputs(n_units, dtype, seed):
         g = torch.Generator(device=dev).manual_seed(seed)
         return [torch.randn(1, n_units, N, D, device=dev, dtype=dtype, generator=g) for _ in range(8)]
@@ -362,10 +368,20 @@ def run_cuda(args, rank, world, local_rank):
             step()
         barrier()
         _lib.read_status(dev)
+        we0, we1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        we0.record()
+        step()
+        we1.record()
+        torch.cuda.synchronize()
+        est_ms = we0.elapsed_time(we1)                 # length of one step, to size the clock probe
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         if sampler is not None:
             sampler.__enter__()
         barrier()
+        probe = None
+        if sampler is not None:
+            # the SM clock the kernels actually get: a one-thread probe beside them for about the length of the region
+            probe = _lib.sm_clock_probe(probe_stream, int(min(900000, max(2000, steps * est_ms * 1000 * 0.9))))
         e0.record()
         for _ in range(steps):
             step()
@@ -373,6 +389,8 @@ def run_cuda(args, rank, world, local_rank):
         barrier()
         if sampler is not None:
             sampler.__exit__(None, None, None)
+            probe_stream.synchronize()
+            sampler.in_kernel_mhz = float(probe.item())
         ms = max_over_ranks(e0.elapsed_time(e1)) / steps
         _lib.read_status(dev)
         return ms
@@ -560,6 +578,8 @@ def run_cuda(args, rank, world, local_rank):
             "roofline": roofline, "kernels": kernels, other_name: other_rec, "weak": weak,
             "cpu_baseline": cpu_baseline, "gpu_incumbent": incumbent, "dit": dit, "e2e": e2e,
             "gpu_launches": 5 * args.steps, "clocks": clocks.summary(),
+            # time x clock: millions of SM cycles per step at the clock counted beside the kernels (power-cap noise drops out)
+            "mcycles_per_step": (ms_step * clocks.in_kernel_mhz / 1e3) if clocks.in_kernel_mhz else None,
         }
         sys.stdout.flush()
         os.write(json_fd, (json.dumps(line) + "\n").encode())

@@ -129,6 +129,13 @@ int jvpfa_bwd(const jvpfa_bwd_args* args, void* stream);
  * 100 + the id of the wait that gave up). */
 int jvpfa_read_status(void* workspace, void* stream, int32_t* detail);
 
+/* Diagnostic: the SM clock that running kernels actually get. Launches a one-thread kernel on `stream` that reads its
+ * SM's cycle counter and the global timer, sleeps for `duration_us` microseconds (1 .. 1000000) and reads them again;
+ * `mhz_out` (device, one float) receives cycles per microsecond. Launched on a stream of its own just before a timed
+ * region it runs beside the attention kernels (it needs no shared memory) and reports the clock under their load, which
+ * on a power-limited part is well below what the management library shows between kernels. No reference counterpart. */
+int jvpfa_sm_clock_probe(float* mhz_out, int32_t duration_us, void* stream);
+
 /* Self-test of the failure-detection path. Launches one tiny kernel on `stream` in which a single thread waits, with
  * the kernels' own bounded wait, on a barrier that nothing arrives on: after `budget_us` microseconds (1 .. 1000000)
  * the wait gives up, writes 177 (100 + wait id 77) into the status word at the start of `workspace` and the kernel

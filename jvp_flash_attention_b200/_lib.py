@@ -32,6 +32,7 @@ EXPORTED_SYMBOLS = (
     "jvpfa_read_status",
     "jvpfa_bwd_marked",
     "jvpfa_selftest_timeout",
+    "jvpfa_sm_clock_probe",
     "jvpfa_bwd_noalloc",
 )
 
@@ -120,6 +121,8 @@ def lib():
                 L.jvpfa_bwd.argtypes = [C.POINTER(BwdArgs), C.c_void_p]
                 L.jvpfa_read_status.restype = C.c_int
                 L.jvpfa_read_status.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_int32)]
+                L.jvpfa_sm_clock_probe.restype = C.c_int
+                L.jvpfa_sm_clock_probe.argtypes = [C.c_void_p, C.c_int32, C.c_void_p]
                 L.jvpfa_selftest_timeout.restype = C.c_int
                 L.jvpfa_selftest_timeout.argtypes = [C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p]
                 L.jvpfa_bwd_marked.restype = C.c_int
@@ -278,6 +281,14 @@ def read_status(device=None) -> None:
         ws.host.zero_()
         if rc != OK:
             raise JvpfaError(rc, lib().jvpfa_error_string(rc).decode() + f" (wait id {detail.value})")
+
+
+def sm_clock_probe(stream: "torch.cuda.Stream", duration_us: int) -> torch.Tensor:
+    """Launches the clock probe on ``stream`` (one that the measured kernels do not use); returns the (1,) float
+    device tensor that will hold the average SM clock in MHz over the next ``duration_us`` microseconds."""
+    out = torch.zeros(1, dtype=torch.float32, device=stream.device)
+    check(lib().jvpfa_sm_clock_probe(C.c_void_p(out.data_ptr()), int(duration_us), C.c_void_p(stream.cuda_stream)))
+    return out
 
 
 def selftest_timeout(device, budget_us: int = 2000) -> torch.Tensor:

@@ -784,6 +784,7 @@ struct GradLayout {
   int H, N;
   TensorView go, gto;
   __host__ __device__ int64_t offset(int64_t row, const TensorView& v) const {
+    if (v.sh == v.sn * N && v.sb == v.sh * H) return row * v.sn;   // rows evenly spaced (the contiguous case)
     const int64_t n = row % N, bh = row / N;
     return (bh / H) * v.sb + (bh % H) * v.sh + n * v.sn;
   }

@@ -137,6 +137,22 @@ __global__ void selftest_timeout_kernel(int* status, uint64_t budget_ns, int* ou
   }
 }
 
+// Average SM clock over a stretch of time: one thread reads the SM's cycle counter and the global nanosecond timer,
+// sleeps until `duration_ns` have passed (bounded: at most one second), and reads both again. Launched on a stream of
+// its own it sits beside whatever else runs on that SM and reports the clock that work actually got.
+__global__ void sm_clock_probe_kernel(uint64_t duration_ns, float* mhz_out) {
+  if (threadIdx.x != 0) return;
+  const uint64_t t0 = sm100::global_timer_ns();
+  const long long c0 = clock64();
+  uint64_t t1 = t0;
+  for (int i = 0; i < 2000000 && t1 - t0 < duration_ns; ++i) {
+    __nanosleep(1000);
+    t1 = sm100::global_timer_ns();
+  }
+  const long long c1 = clock64();
+  *mhz_out = t1 > t0 ? static_cast<float>(static_cast<double>(c1 - c0) * 1e3 / static_cast<double>(t1 - t0)) : 0.f;
+}
+
 int check_common(int B, int H, int N, int D, int dtype, int causal, const jvpfa_mask& mask, const void* ws, size_t ws_bytes,
                  size_t ws_need) {
   if (B <= 0 || H <= 0 || N <= 0 || D <= 0) return JVPFA_ERR_BAD_ARG;
@@ -313,6 +329,12 @@ int jvpfa_bwd_marked(const jvpfa_bwd_args* a, void* stream, void* const* events,
   for (int i = 0; i < 5; ++i)
     if (events[i] == nullptr) return JVPFA_ERR_BAD_ARG;
   return bwd_checked(a, stream, events);
+}
+
+int jvpfa_sm_clock_probe(float* mhz_out, int32_t duration_us, void* stream) {
+  if (mhz_out == nullptr || duration_us <= 0 || duration_us > 1000000) return JVPFA_ERR_BAD_ARG;
+  sm_clock_probe_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<uint64_t>(duration_us) * 1000ull, mhz_out);
+  return cudaGetLastError() == cudaSuccess ? JVPFA_OK : JVPFA_ERR_LAUNCH;
 }
 
 int jvpfa_selftest_timeout(void* workspace, int32_t budget_us, int32_t* out4, void* stream) {
