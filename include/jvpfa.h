@@ -114,8 +114,9 @@ size_t jvpfa_bwd_workspace_bytes(const jvpfa_bwd_args* args);
 
 /* Bytes of the per-tile mask summary for a mask over sequences of length N with Bm x Hm
  * distinct (batch, head) planes, and the kernel that fills it: per 64x64 tile, bit 0 = some
- * element kept, bit 1 = some element excluded. Lets the kernels skip fully excluded tiles and
- * skip mask loads on fully kept ones. No reference counterpart (the reference reads the mask in
+ * element kept, bit 1 = some element that needs the mask (a boolean False; an additive entry other
+ * than zero). Lets the kernels skip fully excluded tiles and skip mask loads on tiles whose entries
+ * are all True / all zero. No reference counterpart (the reference reads the mask in
  * every tile, jvp_attention.py:250-262). */
 size_t jvpfa_mask_summary_bytes(int32_t Bm, int32_t Hm, int32_t N);
 int jvpfa_mask_summary(const jvpfa_mask* mask, int32_t B, int32_t H, int32_t N, uint8_t* summary, void* stream);

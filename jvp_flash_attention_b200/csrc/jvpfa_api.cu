@@ -91,10 +91,15 @@ __global__ void mask_summary_kernel(MaskView mv, int N, int Bm, uint8_t* out) {
         const int k = kt * 64 + c;
         if (k >= N) continue;
         const int64_t idx = plane_off + static_cast<int64_t>(q) * mv.s2 + static_cast<int64_t>(k) * mv.s3;
-        bool kept;
-        if (mv.kind == JVPFA_MASK_BOOL) kept = static_cast<const uint8_t*>(mv.ptr)[idx] != 0;
-        else kept = mask_elem_as_float(mv.ptr, idx, mv.dtype) != -INFINITY;
-        local |= kept ? kTileAnyKept : kTileAnyMasked;
+        // bit "kept": the element takes part; bit "masked": the tile cannot be computed without looking at the mask
+        // (a boolean False, or an additive entry other than zero -- excluded or merely biased)
+        if (mv.kind == JVPFA_MASK_BOOL) {
+          local |= static_cast<const uint8_t*>(mv.ptr)[idx] != 0 ? kTileAnyKept : kTileAnyMasked;
+        } else {
+          const float m = mask_elem_as_float(mv.ptr, idx, mv.dtype);
+          if (m != -INFINITY) local |= kTileAnyKept;
+          if (m != 0.f) local |= kTileAnyMasked;
+        }
       }
       local |= __shfl_xor_sync(0xFFFFFFFFu, local, 16);
       local |= __shfl_xor_sync(0xFFFFFFFFu, local, 8);

@@ -19,8 +19,8 @@ struct MaskView {
   int Hm;                  // number of distinct head planes in the summary
 };
 
-constexpr uint8_t kTileAnyKept = 1;
-constexpr uint8_t kTileAnyMasked = 2;
+constexpr uint8_t kTileAnyKept = 1;     // some element of the tile takes part in attention
+constexpr uint8_t kTileAnyMasked = 2;   // some element needs the mask: a boolean False, or an additive entry that is not zero
 
 #if defined(__CUDACC__)
 // Summary bits of the 64x64 tile (qt, kt) for batch b, head h; "mixed" when there is no summary.

@@ -513,3 +513,18 @@ def test_hessian_vector_product_reverse_over_forward(dev):
             (ref,) = torch.autograd.grad((g2 * u.to(dtype).double()).sum(), qd2)
         err = float((hu.double().cpu() - ref).abs().max())
         assert err <= tol, (dtype, err)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_additive_mask_without_excluded_entries(dev, dtype):
+    """A float mask whose entries are finite everywhere (a bias such as ALiBi, or the reference's {0, MASK_CONST} masks)
+    has no tile that may skip the mask: the tile summary marks a tile as "needs the mask" when any entry is not zero,
+    not only when an entry is -inf."""
+    B, H, N, D = 1, 2, 256, 64
+    ts = make_inputs(B, H, N, D, dtype=dtype, seed=13, scale=0.5)
+    g = torch.Generator().manual_seed(14)
+    mask = torch.randn(B, 1, N, N, generator=g).to(dtype)
+    mask[:, :, :64, :64] = 0.0                       # one tile that really is all zero
+    got = _run_cuda(ts, dev, attn_mask=mask)
+    ref = closed_form_oracle(*ts, attn_mask=mask)
+    _compare(got, ref, TOL[dtype])
