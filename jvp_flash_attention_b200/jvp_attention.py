@@ -12,6 +12,10 @@ Same public names as the reference module (jvp_flash_attention/jvp_attention.py)
 * there is no Triton, no dispatch to another backend and no CPU path: without the CUDA library,
   or on CPU tensors, calls raise.
 
+Second derivatives: Hessian-vector products work in reverse-over-forward form (the gradient of a directional derivative
+taken with ``fwd_dual`` / ``dual``: the tangent output is part of the autograd graph); differentiating the backward itself
+(``create_graph=True`` through these functions) is not supported and raises.
+
 Failure detection: every device-side wait in the kernels is bounded; one that gives up records a code in a status
 word and the kernel runs to its end. Each call enqueues a copy of that word to pinned host memory behind its
 kernels, and the next call on the same stream (without synchronising) or ``check()`` (which synchronises the
@@ -26,6 +30,7 @@ import torch
 import torch.autograd.forward_ad as fwAD
 from torch import Tensor
 from torch.autograd import Function
+from torch.autograd.function import once_differentiable
 
 from . import _lib
 
@@ -99,6 +104,7 @@ class _DualAttention(Function):
         ctx.sm_scale = sm_scale
 
     @staticmethod
+    @once_differentiable      # the gradients come from kernels: differentiating them again raises instead of returning zeros
     def backward(ctx, go, gto, _g_lse, _g_mu, _g_summary):
         q, k, v, tq, tk, tv, o, to, lse2, mu, summary = ctx.saved_tensors
         B, H, N, D = q.shape
@@ -133,6 +139,7 @@ class _PrimalAttention(Function):
         ctx.sm_scale = sm_scale
 
     @staticmethod
+    @once_differentiable
     def backward(ctx, go, _g_lse, _g_mu, _g_summary):
         q, k, v, o, lse2, mu, summary = ctx.saved_tensors
         B, H, N, D = q.shape

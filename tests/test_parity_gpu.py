@@ -528,3 +528,13 @@ def test_additive_mask_without_excluded_entries(dev, dtype):
     got = _run_cuda(ts, dev, attn_mask=mask)
     ref = closed_form_oracle(*ts, attn_mask=mask)
     _compare(got, ref, TOL[dtype])
+
+
+def test_double_backward_raises(dev):
+    """The backward pass is computed by kernels: asking autograd to differentiate it again must fail loudly."""
+    JVPAttn, attention = _api()
+    q = torch.randn(1, 2, 64, 64, device=dev, dtype=torch.float16, requires_grad=True)
+    o = attention(q, q.detach(), q.detach())
+    (g,) = torch.autograd.grad(o.sum(), q, create_graph=True)
+    with pytest.raises(RuntimeError):
+        g.sum().backward()
