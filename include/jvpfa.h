@@ -73,6 +73,8 @@ typedef struct jvpfa_fwd_args {
   void* workspace;
   size_t workspace_bytes;
   jvpfa_strides q_strides, k_strides, v_strides, tq_strides, tk_strides, tv_strides;
+  float dropout_p;        /* 0 = no dropout; see jvpfa_bwd_args */
+  uint64_t dropout_seed;
 } jvpfa_fwd_args;
 
 /* Dual backward: gradients of sum(o*go)+sum(to*gto) for all six inputs. Replaces
@@ -97,6 +99,14 @@ typedef struct jvpfa_bwd_args {
   void* workspace;
   size_t workspace_bytes;
   jvpfa_strides q_strides, k_strides, v_strides, tq_strides, tk_strides, tv_strides, go_strides, gto_strides;
+  /* Dropout on the attention probabilities (after the softmax, kept entries scaled by 1 / (1 - p)); the tangent
+   * output is the derivative of the dropped-out output for the same keep pattern. The pattern is a function of
+   * (dropout_seed, batch*head unit, query, key) -- Philox4x32-10, see csrc/dropout.cuh -- and is regenerated by the
+   * backward: pass the forward's dropout_p and dropout_seed. Tensor-core kernels with head dimension 64 or 128 and
+   * 16-bit inputs only, other shapes answer JVPFA_ERR_UNSUPPORTED. The reference sketches dropout
+   * (jvp_attention.py:105-133) but raises NotImplementedError for dropout_p != 0 (:2550). */
+  float dropout_p;
+  uint64_t dropout_seed;
 } jvpfa_bwd_args;
 
 /* Library version (major*10000 + minor*100 + patch). */

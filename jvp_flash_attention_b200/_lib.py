@@ -56,6 +56,7 @@ class FwdArgs(C.Structure):
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("q_strides", Strides), ("k_strides", Strides), ("v_strides", Strides),
         ("tq_strides", Strides), ("tk_strides", Strides), ("tv_strides", Strides),
+        ("dropout_p", C.c_float), ("dropout_seed", C.c_uint64),
     ]
 
 
@@ -74,6 +75,7 @@ class BwdArgs(C.Structure):
         ("q_strides", Strides), ("k_strides", Strides), ("v_strides", Strides),
         ("tq_strides", Strides), ("tk_strides", Strides), ("tv_strides", Strides),
         ("go_strides", Strides), ("gto_strides", Strides),
+        ("dropout_p", C.c_float), ("dropout_seed", C.c_uint64),
     ]
 
 
@@ -315,8 +317,15 @@ def mask_summary(mask_c: Mask, mask_tensor, B, H, N):
     return out
 
 
-def fwd(q, k, v, tq, tk, tv, mask_c: Mask, summary, causal: bool, sm_scale: float):
-    """Launches the dual forward; returns (o, to, lse2, mu). tq/tk/tv None -> primal only (to None)."""
+def dropout_supported(dtype: torch.dtype, D: int) -> bool:
+    """Dropout runs in the tensor-core kernels of the exact head dimensions 64 and 128 with 16-bit inputs."""
+    return dtype in (torch.float16, torch.bfloat16) and D in (64, 128)
+
+
+def fwd(q, k, v, tq, tk, tv, mask_c: Mask, summary, causal: bool, sm_scale: float, dropout_p: float = 0.0,
+        dropout_seed: int = 0):
+    """Launches the dual forward; returns (o, to, lse2, mu). tq/tk/tv None -> primal only (to None). ``dropout_p`` > 0:
+    dropout on the attention probabilities with the keep pattern of ``dropout_seed`` (pass both to ``bwd`` again)."""
     B, H, N, D = q.shape
     dual = tq is not None
     o = torch.empty(q.shape, dtype=q.dtype, device=q.device)        # outputs are always contiguous
@@ -328,6 +337,7 @@ def fwd(q, k, v, tq, tk, tv, mask_c: Mask, summary, causal: bool, sm_scale: floa
     a.dtype, a.causal, a.sm_scale = dtype_code(q.dtype), int(bool(causal)), float(sm_scale)
     a.mask = mask_c
     a.mask_summary = None if summary is None else summary.data_ptr()
+    a.dropout_p, a.dropout_seed = float(dropout_p), int(dropout_seed) & 0xFFFFFFFFFFFFFFFF
     q, k, v, tq, tk, tv = (as_input(t) for t in (q, k, v, tq, tk, tv))
     a.q, a.k, a.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
     a.tq, a.tk, a.tv = (tq.data_ptr(), tk.data_ptr(), tv.data_ptr()) if dual else (None, None, None)
@@ -344,7 +354,7 @@ def fwd(q, k, v, tq, tk, tv, mask_c: Mask, summary, causal: bool, sm_scale: floa
 
 
 def bwd(q, k, v, tq, tk, tv, o, to, lse2, mu, go, gto, mask_c: Mask, summary, causal: bool, sm_scale: float,
-        marks=None):
+        marks=None, dropout_p: float = 0.0, dropout_seed: int = 0):
     """Launches the backward. Dual form: returns (dq, dk, dv, dtq, dtk, dtv). With tq None (primal-only: tk, tv,
     to, gto are ignored) returns (dq, dk, dv). ``marks``: five ``torch.cuda.Event(enable_timing=True)`` that have
     been recorded once (so that they exist); they are recorded before the preprocess kernel, before each of the three
@@ -358,6 +368,7 @@ def bwd(q, k, v, tq, tk, tv, o, to, lse2, mu, go, gto, mask_c: Mask, summary, ca
     a.dtype, a.causal, a.sm_scale = dtype_code(q.dtype), int(bool(causal)), float(sm_scale)
     a.mask = mask_c
     a.mask_summary = None if summary is None else summary.data_ptr()
+    a.dropout_p, a.dropout_seed = float(dropout_p), int(dropout_seed) & 0xFFFFFFFFFFFFFFFF
     a.q, a.k, a.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
     a.o, a.lse2, a.mu = o.data_ptr(), lse2.data_ptr(), mu.data_ptr()
     a.go = go.data_ptr()

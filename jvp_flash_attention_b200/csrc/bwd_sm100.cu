@@ -29,6 +29,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include "host_common.h"
+#include "dropout.cuh"
 #include "mask_common.cuh"
 #include "sm100_prims.cuh"
 
@@ -55,6 +56,7 @@ struct BwdKParams {
   void* out1;
   int* status;
   uint64_t budget_ns;
+  DropoutParams drop;
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -121,7 +123,10 @@ struct BwdCfg {
 // output columns that would only see zeros are then skipped at run time.
 // DUAL = false: primal-only backward (no tangents, no gradient through a tangent output): S and X = gO V^T only,
 // dS = P (X - Delta); dQ = s dS K, dK = s dS^T Q, dV = P^T gO. Tangent tiles are neither loaded nor multiplied.
-template <int D, int FAM, bool BF16, bool PAD, bool DUAL, bool SPLIT = false>
+// DROP: the forward applied dropout to the probabilities that multiply V, tV (dropout.cuh). The same keep pattern is
+// regenerated here: it scales X and A (the gradients that arrive through V, tV) in families Q, K, and P, tP (the operands
+// of dV, dtV) in family V; Delta and a come from the dropped-out O, tO and need no change.
+template <int D, int FAM, bool BF16, bool PAD, bool DUAL, bool SPLIT = false, bool DROP = false>
 __global__ void __launch_bounds__(352, 1)
 bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant__ CUtensorMap rm1,
                  const __grid_constant__ CUtensorMap rm2, const __grid_constant__ CUtensorMap rm3,
@@ -495,6 +500,11 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
       const int sb = (FAM == FAM_V) ? (it & 1) : 0;   // family V: P, tP buffer of this tile
       const uint32_t T0 = TS0 + 32 * wg, T1 = T0 + 64;
       const uint32_t EV0 = TS0 + 128 + sb * C::EBUF + 16 * wg, EV1 = EV0 + C::EBUF / 2;   // family V: this thread's 16 columns of P, tP
+      // dropout pattern of this thread's 32 score elements: its row is a query in family Q, a key in families K and V
+      uint32_t keep_bits = 0xFFFFFFFFu;
+      if constexpr (DROP)
+        keep_bits = (FAM == FAM_Q) ? dropout_keep_along_k(p.drop, bh, gr, cw) : dropout_keep_along_q(p.drop, bh, cw, gr);
+      auto keep2 = [&](int ip) -> float2 { return dropout_factors(keep_bits, ip, p.drop.inv_keep); };
       // family V, dual: P goes back to TMEM first (its two output products start while tP is computed)
       constexpr bool SPLIT_P = (FAM == FAM_V) && DUAL;
       mbar_wait(&st_full[0], it & 1, w, 30);
@@ -562,6 +572,10 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
         }
         {
           uint32_t e0[16];
+          if constexpr (DROP) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) P2[i] = __fmul2_rn(P2[i], keep2(i));   // from here on P is only an operand of dV, dtV
+          }
 #pragma unroll
           for (int i = 0; i < 16; ++i) e0[i] = pack2<BF16>(P2[i].x, P2[i].y);
           tmem_st_x16(EV0, e0);
@@ -596,6 +610,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             const int ip = 8 * hch + i;
+            if constexpr (DROP) P2[ip] = __fmul2_rn(P2[ip], keep2(ip));
             e0[i] = pack2<BF16>(P2[ip].x, P2[ip].y);
             if constexpr (SPLIT) l0[i] = pack2_residual(P2[ip].x, P2[ip].y, e0[i]);
             if constexpr (DUAL) {
@@ -633,7 +648,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
               const int ip = 8 * hch + i;
-              const float2 A = make_float2(__uint_as_float(ar[hch][2 * i]), __uint_as_float(ar[hch][2 * i + 1]));
+              float2 A = make_float2(__uint_as_float(ar[hch][2 * i]), __uint_as_float(ar[hch][2 * i + 1]));
+              if constexpr (DROP) A = __fmul2_rn(A, keep2(ip));
               const float2 d = __fadd2_rn(A, stat2(3, ip));                       // A - a
               float2 t = __ffma2_rn(ts2[ip], d, stat2(2, ip));                    // ts (A - a) - Delta
               ts2[ip] = __ffma2_rn(stat2(1, ip), A, t);                           // - mu A
@@ -666,7 +682,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
               const int ip = 8 * hch + i;
-              const float2 X = make_float2(__uint_as_float(xr[hch][2 * i]), __uint_as_float(xr[hch][2 * i + 1]));
+              float2 X = make_float2(__uint_as_float(xr[hch][2 * i]), __uint_as_float(xr[hch][2 * i + 1]));
+              if constexpr (DROP) X = __fmul2_rn(X, keep2(ip));
               const float2 ds = __fmul2_rn(P2[ip], __fadd2_rn(X, ts2[ip]));
               e0[i] = pack2<BF16>(ds.x, ds.y);
               if constexpr (SPLIT) l0[i] = pack2_residual(ds.x, ds.y, e0[i]);
@@ -694,7 +711,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
               const int ip = 8 * hch + i;
-              const float2 X = make_float2(__uint_as_float(xr[hch][2 * i]), __uint_as_float(xr[hch][2 * i + 1]));
+              float2 X = make_float2(__uint_as_float(xr[hch][2 * i]), __uint_as_float(xr[hch][2 * i + 1]));
+              if constexpr (DROP) X = __fmul2_rn(X, keep2(ip));
               const float2 ds = __fmul2_rn(P2[ip], __fadd2_rn(X, stat2(2, ip)));  // P (X - Delta)
               e0[i] = pack2<BF16>(ds.x, ds.y);
               if constexpr (SPLIT) l0[i] = pack2_residual(ds.x, ds.y, e0[i]);
@@ -877,7 +895,7 @@ __global__ void bwd_preprocess_f32_kernel(const float* __restrict__ o, const flo
 
 // `a` holds the operands the tensor maps are built on: in the split-fp32 mode (SPLIT) the bf16 hi/lo tensors of the
 // pre-pass with 128 columns, and `real_D` is the head dimension of the outputs.
-template <int D, int FAM, bool BF16, bool PAD, bool DUAL, bool SPLIT = false>
+template <int D, int FAM, bool BF16, bool PAD, bool DUAL, bool SPLIT = false, bool DROP = false>
 int launch_family(const jvpfa_bwd_args& a, const float4* stats, cudaStream_t stream, int real_D = 0) {
   using C = BwdCfg<D, FAM, SPLIT>;
   const TensorView vq = make_view(a.q, a.q_strides, a.H, a.N, a.D), vk = make_view(a.k, a.k_strides, a.H, a.N, a.D),
@@ -924,7 +942,8 @@ int launch_family(const jvpfa_bwd_args& a, const float4* stats, cudaStream_t str
   p.out0 = out0; p.out1 = out1;
   p.status = static_cast<int*>(a.workspace);
   p.budget_ns = wait_budget_ns();
-  auto kern = bwd_sm100_kernel<D, FAM, BF16, PAD, DUAL, SPLIT>;
+  p.drop = make_dropout_params(a.dropout_p, a.dropout_seed);
+  auto kern = bwd_sm100_kernel<D, FAM, BF16, PAD, DUAL, SPLIT, DROP>;
   const size_t smem = C::smem_bytes();
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
     return JVPFA_ERR_LAUNCH;
@@ -948,22 +967,26 @@ int launch_all(const jvpfa_bwd_args& a, cudaStream_t stream, const LaunchMarks& 
       static_cast<const uint16_t*>(a.o), static_cast<const uint16_t*>(a.to), static_cast<const uint16_t*>(a.go),
       static_cast<const uint16_t*>(a.gto), a.lse2, a.mu, stats, rows, a.D, gl);
   if (cudaGetLastError() != cudaSuccess) return JVPFA_ERR_LAUNCH;
-  auto three = [&](auto pad, auto dual) {
-    constexpr bool P = decltype(pad)::value, DU = decltype(dual)::value;
+  auto three = [&](auto pad, auto dual, auto drop) {
+    constexpr bool P = decltype(pad)::value, DU = decltype(dual)::value, DR = decltype(drop)::value;
     marks.mark(1);
-    int rc = launch_family<D, FAM_Q, BF16, P, DU>(a, stats, stream);
+    int rc = launch_family<D, FAM_Q, BF16, P, DU, false, DR>(a, stats, stream);
     if (rc != JVPFA_OK) return rc;
     marks.mark(2);
-    rc = launch_family<D, FAM_K, BF16, P, DU>(a, stats, stream);
+    rc = launch_family<D, FAM_K, BF16, P, DU, false, DR>(a, stats, stream);
     if (rc != JVPFA_OK) return rc;
     marks.mark(3);
-    rc = launch_family<D, FAM_V, BF16, P, DU>(a, stats, stream);
+    rc = launch_family<D, FAM_V, BF16, P, DU, false, DR>(a, stats, stream);
     marks.mark(4);
     return rc;
   };
   const bool dual = a.tq != nullptr;
-  if (a.D == D) return dual ? three(std::false_type{}, std::true_type{}) : three(std::false_type{}, std::false_type{});
-  return dual ? three(std::true_type{}, std::true_type{}) : three(std::true_type{}, std::false_type{});
+  if (a.dropout_p > 0.f) {   // dropout: the kernels of the exact head dimensions only
+    if (a.D != D) return JVPFA_ERR_UNSUPPORTED;
+    return dual ? three(std::false_type{}, std::true_type{}, std::true_type{}) : three(std::false_type{}, std::false_type{}, std::true_type{});
+  }
+  if (a.D == D) return dual ? three(std::false_type{}, std::true_type{}, std::false_type{}) : three(std::false_type{}, std::false_type{}, std::false_type{});
+  return dual ? three(std::true_type{}, std::true_type{}, std::false_type{}) : three(std::true_type{}, std::false_type{}, std::false_type{});
 }
 
 // fp32 inputs: statistics from the fp32 tensors, split pre-pass of the eight (primal-only: four) MMA operands into the

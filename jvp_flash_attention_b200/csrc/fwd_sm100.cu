@@ -23,6 +23,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include "host_common.h"
+#include "dropout.cuh"
 #include "mask_common.cuh"
 #include "sm100_prims.cuh"
 
@@ -48,6 +49,7 @@ struct FwdKParams {
   float* mu;
   int* status;
   uint64_t budget_ns;
+  DropoutParams drop;
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -105,7 +107,9 @@ struct FwdCfg {
 // TMEM allocation.
 // PAD: the tensors' head dimension is smaller than D (columns beyond it are zero-filled by TMA); the K steps and
 // output columns that would only see zeros are then skipped at run time.
-template <int D, bool DUAL, bool BF16, bool PAD, bool SPLIT = false>
+// DROP: dropout on the attention probabilities (dropout.cuh): P and W reach TMEM dropped out and rescaled, the row sums l
+// and mu are those of the probabilities before dropout.
+template <int D, bool DUAL, bool BF16, bool PAD, bool SPLIT = false, bool DROP = false>
 __global__ void __launch_bounds__(384, 1)
 fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmTQ,
                  const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmTK,
@@ -472,6 +476,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
       const float m_eff = (m_used == -INFINITY) ? 0.f : m_used;
       const float2 nm2 = make_float2(-m_eff, -m_eff);
+      uint32_t keep_bits = 0xFFFFFFFFu;
+      if constexpr (DROP) keep_bits = dropout_keep_along_k(p.drop, bh, qi, k0);
       {
         // the PV products of tile it - 2 read this P, W buffer
         if (it >= 2) {
@@ -487,14 +493,18 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             const float2 e = __fadd2_rn(x2[ip], nm2);
             const float2 pp = make_float2(fast_exp2(e.x), fast_exp2(e.y));
             l2 = __fadd2_rn(l2, pp);
-            pk[i] = pack2<BF16>(pp.x, pp.y);
-            if constexpr (SPLIT) pkl[i] = pack2_residual(pp.x, pp.y, pk[i]);
+            float2 keep2 = make_float2(1.f, 1.f);
+            if constexpr (DROP) keep2 = dropout_factors(keep_bits, ip, p.drop.inv_keep);
+            const float2 pd = DROP ? __fmul2_rn(pp, keep2) : pp;     // what multiplies V, tV
+            pk[i] = pack2<BF16>(pd.x, pd.y);
+            if constexpr (SPLIT) pkl[i] = pack2_residual(pd.x, pd.y, pk[i]);
             if constexpr (DUAL) {
               const float2 tsv = __fmul2_rn(make_float2(__uint_as_float(ts[2 * ip]), __uint_as_float(ts[2 * ip + 1])), s_2);
               const float2 ww = __fmul2_rn(pp, tsv);
               mu2 = __fadd2_rn(mu2, ww);
-              wk[i] = pack2<BF16>(ww.x, ww.y);
-              if constexpr (SPLIT) wkl[i] = pack2_residual(ww.x, ww.y, wk[i]);
+              const float2 wd = DROP ? __fmul2_rn(ww, keep2) : ww;
+              wk[i] = pack2<BF16>(wd.x, wd.y);
+              if constexpr (SPLIT) wkl[i] = pack2_residual(wd.x, wd.y, wk[i]);
             }
           }
           tmem_st_x8(P_t + 8 * c, pk);
@@ -603,7 +613,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   if (warp == 9) tmem_dealloc(tmem, C::TMEM_COLS);
 }
 
-template <int D, bool DUAL, bool BF16, bool PAD>
+template <int D, bool DUAL, bool BF16, bool PAD, bool DROP = false>
 int launch_one(const jvpfa_fwd_args& a, cudaStream_t stream) {
   using C = FwdCfg<D>;
   CUtensorMap mQ, mTQ, mK, mTK, mV, mTV;
@@ -634,7 +644,8 @@ int launch_one(const jvpfa_fwd_args& a, cudaStream_t stream) {
   p.o = a.o; p.to = a.to; p.lse2 = a.lse2; p.mu = a.mu;
   p.status = static_cast<int*>(a.workspace);
   p.budget_ns = wait_budget_ns();
-  auto kern = fwd_sm100_kernel<D, DUAL, BF16, PAD>;
+  p.drop = make_dropout_params(a.dropout_p, a.dropout_seed);
+  auto kern = fwd_sm100_kernel<D, DUAL, BF16, PAD, false, DROP>;
   const size_t smem = C::smem_bytes();
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
     return JVPFA_ERR_LAUNCH;
@@ -726,6 +737,13 @@ template <int D, bool PAD>
 int launch_by_mode(const jvpfa_fwd_args& a, cudaStream_t stream) {
   const bool dual = a.tq != nullptr;
   const bool bf = a.dtype == JVPFA_BF16;
+  if constexpr (!PAD) {
+    if (a.dropout_p > 0.f) {
+      if (dual) return bf ? launch_one<D, true, true, false, true>(a, stream) : launch_one<D, true, false, false, true>(a, stream);
+      return bf ? launch_one<D, false, true, false, true>(a, stream) : launch_one<D, false, false, false, true>(a, stream);
+    }
+  }
+  if (a.dropout_p > 0.f) return JVPFA_ERR_UNSUPPORTED;
   if (dual) return bf ? launch_one<D, true, true, PAD>(a, stream) : launch_one<D, true, false, PAD>(a, stream);
   return bf ? launch_one<D, false, true, PAD>(a, stream) : launch_one<D, false, false, PAD>(a, stream);
 }

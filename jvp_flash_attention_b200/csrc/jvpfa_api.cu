@@ -264,6 +264,8 @@ int jvpfa_fwd(const jvpfa_fwd_args* a, void* stream) {
     rc = check_layouts(ptrs, st, dual ? 6 : 3, a->B, a->H, a->N, a->D, a->dtype);
     if (rc != JVPFA_OK) return rc;
   }
+  if (!(a->dropout_p >= 0.f && a->dropout_p < 1.f)) return JVPFA_ERR_BAD_ARG;
+  if (a->dropout_p > 0.f && !(sm100_path_supported(a->dtype, a->D, a->N) && (a->D == 64 || a->D == 128))) return JVPFA_ERR_UNSUPPORTED;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (sm100_path_supported(a->dtype, a->D, a->N)) return launch_fwd_sm100(*a, s);
   // fp32: the tensor-core path when the workspace has room for the split operands, else the CUDA-core kernels
@@ -310,6 +312,8 @@ int bwd_checked(const jvpfa_bwd_args* a, void* stream, void* const* events) {
     rc = check_layouts(ptrs, st, dual ? 8 : 4, eff.B, eff.H, eff.N, eff.D, eff.dtype);
     if (rc != JVPFA_OK) return rc;
   }
+  if (!(eff.dropout_p >= 0.f && eff.dropout_p < 1.f)) return JVPFA_ERR_BAD_ARG;
+  if (eff.dropout_p > 0.f && !(sm100_path_supported(eff.dtype, eff.D, eff.N) && (eff.D == 64 || eff.D == 128))) return JVPFA_ERR_UNSUPPORTED;
   LaunchMarks marks;
   marks.events = events;
   marks.stream = s;

@@ -77,10 +77,48 @@ def sdpa_jvp_oracle(q, k, v, tq, tk, tv, gO=None, gtO=None, attn_mask=None, caus
 
 
 # --------------------------------------------------------------------------------------------
+# dropout pattern: Philox4x32-10 (Salmon et al., "Parallel random numbers: as easy as 1, 2, 3", SC'11), keyed by the
+# 64-bit seed, counter (q >> 1, k >> 1, batch*head unit, 0); the four 32-bit outputs of one call belong to the 2 x 2
+# block of elements (q, k), index (q & 1) * 2 + (k & 1). An element is kept when its number is >= p * 2^32.
+# --------------------------------------------------------------------------------------------
+def philox4x32_10(c0, c1, c2, c3, k0, k1):
+    """Vectorised Philox4x32 with 10 rounds on uint32 numpy arrays; returns the four output words."""
+    M0, M1, W0, W1 = np.uint64(0xD2511F53), np.uint64(0xCD9E8D57), 0x9E3779B9, 0xBB67AE85
+    c0, c1, c2, c3 = (np.asarray(c, dtype=np.uint32) for c in (c0, c1, c2, c3))
+    k0, k1 = int(k0) & 0xFFFFFFFF, int(k1) & 0xFFFFFFFF
+    for _ in range(10):
+        p0 = M0 * c0.astype(np.uint64)
+        p1 = M1 * c2.astype(np.uint64)
+        hi0, lo0 = (p0 >> np.uint64(32)).astype(np.uint32), p0.astype(np.uint32)
+        hi1, lo1 = (p1 >> np.uint64(32)).astype(np.uint32), p1.astype(np.uint32)
+        c0, c1, c2, c3 = hi1 ^ c1 ^ np.uint32(k0), lo1, hi0 ^ c3 ^ np.uint32(k1), lo0
+        k0, k1 = (k0 + W0) & 0xFFFFFFFF, (k1 + W1) & 0xFFFFFFFF
+    return c0, c1, c2, c3
+
+
+def dropout_threshold(p: float) -> int:
+    """The 32-bit threshold of the keep test ``number >= threshold`` for drop probability p."""
+    return min(0xFFFFFFFF, max(0, int(round(p * 4294967296.0))))
+
+
+def dropout_keep(seed: int, unit: int, N: int, p: float) -> np.ndarray:
+    """(N, N) array of 0.0 / 1.0: which attention probabilities of (batch, head) unit ``unit`` survive dropout."""
+    half = (N + 1) // 2
+    qp, kp = np.meshgrid(np.arange(half, dtype=np.uint32), np.arange(half, dtype=np.uint32), indexing="ij")
+    words = philox4x32_10(qp, kp, np.full_like(qp, unit), np.zeros_like(qp), seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF)
+    full = np.empty((2 * half, 2 * half), dtype=np.uint32)
+    for i in range(2):
+        for j in range(2):
+            full[i::2, j::2] = words[i * 2 + j]
+    return (full[:N, :N] >= np.uint32(dropout_threshold(p))).astype(np.float64)
+
+
+# --------------------------------------------------------------------------------------------
 # second oracle: closed-form numpy restatement, one (batch, head) slice at a time
 # --------------------------------------------------------------------------------------------
-def _closed_form_head(q, k, v, tq, tk, tv, gO, gtO, bias, s):
-    """One head in numpy fp64. ``bias`` is an (N, N) additive matrix (0 / -inf / finite) or None."""
+def _closed_form_head(q, k, v, tq, tk, tv, gO, gtO, bias, s, keep=None):
+    """One head in numpy fp64. ``bias`` is an (N, N) additive matrix (0 / -inf / finite) or None. ``keep`` is an (N, N)
+    dropout matrix (0 for dropped probabilities, 1 / (1 - p) for kept ones) applied after the softmax, or None."""
     S = s * (q @ k.T)                                   # jvp_attention.py:244 (qk), scaled
     if bias is not None:
         S = S + bias
@@ -95,24 +133,28 @@ def _closed_form_head(q, k, v, tq, tk, tv, gO, gtO, bias, s):
     tS = s * (tq @ k.T + q @ tk.T)                      # jvp_attention.py:245-247 (t_qk)
     mu = (P * tS).sum(axis=-1, keepdims=True)           # jvp_attention.py:330-331 (mu accumulation)
     tP = P * (tS - mu)
-    O = P @ v                                           # jvp_attention.py:333 (acc)
-    tO = tP @ v + P @ tv                                # jvp_attention.py:1041-1044 (epilogue)
+    Pd, tPd = (P, tP) if keep is None else (P * keep, tP * keep)   # dropout acts on the probabilities that reach V
+    O = Pd @ v                                          # jvp_attention.py:333 (acc)
+    tO = tPd @ v + Pd @ tv                              # jvp_attention.py:1041-1044 (epilogue)
     out = {"O": O, "tO": tO, "lse": lse, "mu": mu[:, 0]}
     if gO is None:
         return out
     A = gtO @ v.T
+    X = gO @ v.T + gtO @ tv.T
+    if keep is not None:
+        A, X = A * keep, X * keep
     a = (gtO * O).sum(axis=-1, keepdims=True)
     dtS = P * (A - a)                                   # gradient w.r.t. the tangent scores
-    dP = gO @ v.T + gtO @ tv.T + A * (tS - mu) - a * tS
+    dP = X + A * (tS - mu) - a * tS
     delta = (gO * O).sum(-1, keepdims=True) + (gtO * tO).sum(-1, keepdims=True) - a * mu  # :1419 when gtO == 0
     dS = P * (dP - delta)                               # jvp_attention.py:1557 (dsT)
     out.update(
         dq=s * (dS @ k + dtS @ tk),                     # jvp_attention.py:1708 (+ tangent term)
         dk=s * (dS.T @ q + dtS.T @ tq),                 # jvp_attention.py:1564
-        dv=P.T @ gO + tP.T @ gtO,                       # jvp_attention.py:1552
+        dv=Pd.T @ gO + tPd.T @ gtO,                     # jvp_attention.py:1552
         dtq=s * (dtS @ k),
         dtk=s * (dtS.T @ q),
-        dtv=P.T @ gtO,
+        dtv=Pd.T @ gtO,
         delta=delta[:, 0],
         a=a[:, 0],
     )
@@ -126,12 +168,16 @@ def _as_np64(t):
 
 
 def closed_form_oracle(q, k, v, tq, tk, tv, gO=None, gtO=None, attn_mask=None, causal=False, sm_scale=None,
-                       slices: Optional[Sequence[tuple]] = None):
+                       slices: Optional[Sequence[tuple]] = None, dropout_p: float = 0.0, dropout_seed: int = 0):
     """Closed-form fp64 oracle. Returns a dict of numpy arrays shaped like the inputs (plus the
     per-row statistics ``lse``, ``mu`` and, with gradients, ``delta`` and ``a``).
 
     ``slices`` = iterable of (b, h) pairs restricts the work to those heads; the returned arrays
     then have shape (len(slices), N, D) in that order (used for the large configurations).
+
+    ``dropout_p`` > 0 applies dropout to the attention probabilities with the keep pattern of ``dropout_keep``
+    (a counter-based generator keyed by the seed and the element's position, so that any implementation can
+    regenerate it); the reference only sketches this (jvp_attention.py:105-133) and refuses dropout_p != 0 (:2550).
     """
     qn, kn, vn, tqn, tkn, tvn = (_as_np64(t) for t in (q, k, v, tq, tk, tv))
     gOn = _as_np64(gO) if gO is not None else None
@@ -155,8 +201,11 @@ def closed_form_oracle(q, k, v, tq, tk, tv, gO=None, gtO=None, attn_mask=None, c
             bias = mask[b, h]
         if tri is not None:
             bias = tri if bias is None else bias + tri
+        keep = None
+        if dropout_p > 0.0:
+            keep = dropout_keep(dropout_seed, b * H + h, N, dropout_p) / (1.0 - dropout_p)
         r = _closed_form_head(qn[b, h], kn[b, h], vn[b, h], tqn[b, h], tkn[b, h], tvn[b, h],
-                              None if gOn is None else gOn[b, h], None if gtOn is None else gtOn[b, h], bias, s)
+                              None if gOn is None else gOn[b, h], None if gtOn is None else gtOn[b, h], bias, s, keep)
         for name, val in r.items():
             res.setdefault(name, []).append(val)
     out = {name: np.stack(vals) for name, vals in res.items()}

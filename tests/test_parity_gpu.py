@@ -260,7 +260,9 @@ def test_error_behaviour_on_gpu(dev):
     with pytest.raises(ValueError):
         attention(q, q, q, attn_mask=m, causal=True)
     with pytest.raises(NotImplementedError):
-        JVPAttn.fwd_dual(q, q, q, dropout_p=0.5)
+        JVPAttn.fwd_dual(q.float(), q.float(), q.float(), dropout_p=0.5)    # dropout: 16-bit inputs, head dimension 64 / 128 only
+    with pytest.raises(NotImplementedError):
+        JVPAttn.fwd_dual(q[..., :32], q[..., :32], q[..., :32], dropout_p=0.5)
     with pytest.raises(AssertionError):
         attention(q, q, q, attn_mask=torch.zeros_like(m))       # all-False head
     with pytest.raises(AssertionError):
