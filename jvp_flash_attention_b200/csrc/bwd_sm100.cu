@@ -149,7 +149,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
   // per-query statistics of the current column tile, negated, one array per field: [buffer][-lse2, -mu, -Delta, -a][column]
   float(*stats_s)[4][C::BC] = reinterpret_cast<float(*)[4][C::BC]>(tail);
   uint64_t* bars = reinterpret_cast<uint64_t*>(tail + 2 * C::BC * sizeof(float4));
-  uint64_t& r_full = bars[0];
+  uint64_t& r_full = bars[0];       // row-side tiles 0, 1 (what the score products S, tS read) have landed
   uint64_t* st_full = bars + 1;   // [2] (family V uses both, Q/K only [0])
   uint64_t* p_full = bars + 3;    // [2]
   uint64_t& ph1_done = bars[5];
@@ -162,6 +162,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
   uint64_t* e_free = b_empty + NB;   // [2] family V: the output products that read P, tP buffer b have completed
   uint64_t& a_ready = e_free[2];     // families Q, K: A of the current tile is complete (X still accumulating)
   uint64_t& pt_full = e_free[3];     // families Q, K: dtS of the current tile is in TMEM
+  uint64_t& r23_full = e_free[4];    // families Q, K: row-side tiles 2, 3 (what the X, A products read) have landed
   uint64_t& sc_free = e_free[5];     // family V: all 256 element-wise threads hold S, tS in registers, the next tile's
                                      // score products may overwrite them
   uint64_t* pp_full = e_free + 6;    // [2] family V: P of buffer b is in TMEM
@@ -194,6 +195,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
   if (tid == 0) {
     poisoned = 0;
     mbar_init(&r_full, 1);
+    mbar_init(&r23_full, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&st_full[i], 1);
       mbar_init(&p_full[i], 256);
@@ -250,16 +252,24 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
   if (warp == 8) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      mbar_arrive_expect_tx(&r_full, (DUAL ? C::NR : C::NR / 2) * C::TILE_R);
+      // Order of the first loads: the row-side tiles of the score products, the first column pair, then the row-side
+      // tiles of X, A and their first column pair -- the first score products start after 96 KB instead of 192 KB.
+      mbar_arrive_expect_tx(&r_full, (DUAL ? 2 : 1) * C::TILE_R);
 #pragma unroll
       for (int sl = 0; sl < SLABS; ++sl) {
         tma_load_tile(sR(0) + sl * C::SLAB, &rm0, &r_full, 64 * sl, r0, h, b);
         if constexpr (DUAL) tma_load_tile(sR(1) + sl * C::SLAB, &rm1, &r_full, 64 * sl, r0, h, b);
-        if constexpr (C::NR == 4) {
-          tma_load_tile(sR(2) + sl * C::SLAB, &rm2, &r_full, 64 * sl, r0, h, b);
-          if constexpr (DUAL) tma_load_tile(sR(3) + sl * C::SLAB, &rm3, &r_full, 64 * sl, r0, h, b);
-        }
       }
+      auto load_rows23 = [&]() {
+        if constexpr (C::NR == 4) {
+          mbar_arrive_expect_tx(&r23_full, (DUAL ? 2 : 1) * C::TILE_R);
+#pragma unroll
+          for (int sl = 0; sl < SLABS; ++sl) {
+            tma_load_tile(sR(2) + sl * C::SLAB, &rm2, &r23_full, 64 * sl, r0, h, b);
+            if constexpr (DUAL) tma_load_tile(sR(3) + sl * C::SLAB, &rm3, &r23_full, 64 * sl, r0, h, b);
+          }
+        }
+      };
       int it = 0;
       for (int j = next_active(j_begin); j < j_end; j = next_active(j + 1), ++it) {
         const int crow = j * C::BC;   // first row of the column tile inside its (batch, head) unit
@@ -273,6 +283,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
             if constexpr (DUAL) tma_load_tile(sA(buf) + sl * C::SLAB + C::HALF, &cm1, &a_full[buf], 64 * sl, crow, h, b);
           }
         }
+        if (it == 0) load_rows23();
         {
           const int buf = it % NB;
           mbar_wait(&b_empty[buf], ((it / NB) & 1) ^ 1, w, 11);
@@ -284,6 +295,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
           }
         }
       }
+      if (it == 0) load_rows23();   // no column tile takes part: the loads still have to happen before the CTA ends
     }
     __syncwarp();
   } else if (warp >= 9) {
@@ -379,7 +391,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
         if (leader) umma_commit(&b_empty[buf]);
       };
 
-      wait_all(&r_full, 0, 22);
+      if (warp == 9) wait_all(&r_full, 0, 22);
+      else if constexpr (C::NR == 4) wait_all(&r23_full, 0, 37);
       int j = next_active(j_begin);
       int it = 0;
       if (warp == 9) {
@@ -731,7 +744,10 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
     tc_fence_after_sync();
     // Each warpgroup writes half of the head dimension; the rows go through this warp's patch of shared memory (the
     // first row-side tile is no longer needed: every product has completed) so that the global stores are row segments.
-    if (it == 0) mbar_wait(&r_full, 0, w, 36);   // nothing was multiplied: the row-side loads may still be in flight
+    if (it == 0) {   // nothing was multiplied: the row-side loads may still be in flight
+      mbar_wait(&r_full, 0, w, 36);
+      if constexpr (C::NR == 4) mbar_wait(&r23_full, 0, w, 38);
+    }
     if constexpr (SPLIT) {
       // fp32 outputs: this warpgroup's 32 columns are 128 bytes per row
       uint8_t* patch = sR(0) + warp * (32 * 128);
