@@ -11,6 +11,8 @@
 //   family Q : rows = queries.  scores S, tS, X, A (q on TMEM lanes)    -> dQ, dtQ
 //   family K : rows = keys.     transposed scores (k on TMEM lanes)      -> dK, dtK
 //   family V : rows = keys.     transposed S, tS only                    -> dV, dtV
+//   family KV: families K and V in one pass for head dimensions up to 64, where four accumulators and four score
+//              tiles fit the 512 TMEM columns: 12 tile products where the two passes run 15
 // with  S = Q K^T, tS = tQ K^T + Q tK^T, X = gO V^T + gtO tV^T, A = gtO V^T and per score element
 //   P = exp2(c1 S + bias - lse2_q), ts = s tS, dtS = P (A - a_q),
 //   dS = P (X + A (ts - mu_q) - a_q ts - Delta_q), tP = P (ts - mu_q);
@@ -38,7 +40,7 @@ using namespace sm100;
 
 namespace {
 
-enum { FAM_Q = 0, FAM_K = 1, FAM_V = 2 };
+enum { FAM_Q = 0, FAM_K = 1, FAM_V = 2, FAM_KV = 3 };
 
 
 struct BwdKParams {
@@ -54,6 +56,8 @@ struct BwdKParams {
   const float4* stats;  // per (b,h,q): lse2, mu, Delta, a
   void* out0;
   void* out1;
+  void* out2;   // family KV: dV, dtV (written unscaled)
+  void* out3;
   int* status;
   uint64_t budget_ns;
   DropoutParams drop;
@@ -91,15 +95,20 @@ struct BwdCfg {
   static constexpr int BC = 64;                          // columns per streamed tile
   static constexpr int NR = (FAM == FAM_V) ? 2 : 4;      // resident row-side operand tiles
   static constexpr int NA = 2;                           // buffers of the first column-side pair
-  static constexpr int NB = (FAM == FAM_V) ? 2 : 1;      // buffers of the second column-side pair
+  static constexpr bool KV = (FAM == FAM_KV);            // families K and V in one pass (head dimension <= 64)
+  static constexpr int NB = (FAM == FAM_V || KV) ? 2 : 1;   // buffers of the second column-side pair
   static constexpr int TILE_R = BR * D * 2;
   static constexpr int PAIR = 2 * BC * D * 2;            // two stacked 64-row tiles = one 128-row operand
   static constexpr int SLAB = 128 * 128;                 // bytes of one 64-column slab of a 128-row tile
   static constexpr int HALF = BC * 128;                  // byte offset of the second tile inside a slab
   static constexpr int DV = SPLIT ? 64 : D;                 // columns of an accumulator
+  static constexpr int NACC = KV ? 4 : 2;                // accumulators
   static constexpr int TMEM_ACC0 = 0;
   static constexpr int TMEM_ACC1 = DV;
-  static constexpr int TMEM_T = 2 * DV;                  // score tiles, 64 columns each
+  static constexpr int TMEM_ACC2 = 2 * DV;
+  static constexpr int TMEM_T = NACC * DV;               // score tiles, 64 columns each
+  static constexpr int EUP = 16;                         // family KV: columns from dS (dtS) to the P (tP) that shares its score tile
+  static_assert(!KV || (D == 64 && !SPLIT), "four accumulators and four score tiles fit 512 TMEM columns only at 64");
   static constexpr int EBUF = SPLIT ? 128 : 64;             // family V: columns of one buffer of 16-bit P, tP (SPLIT: hi and lo parts)
   static constexpr int ELO = SPLIT ? (FAM == FAM_V ? 32 : 16) : 0;   // columns from the hi part of an operand to its lo part
   static constexpr int TMEM_COLS = 512;
@@ -118,7 +127,9 @@ struct BwdCfg {
 //  Q: [A | gtO tV^T] = gtO [V; tV]^T, X += gO V^T;    K: [V gO^T | A^T] = V [gO; gtO]^T, X^T += tV gtO^T.
 // Families Q and K keep one set of score tiles and overlap in two phases per tile: phase 1 reads S, tS
 // (which frees them for the next tile's products), phase 2 reads X, A and writes the 16-bit dS, dtS operands;
-// family V double-buffers S, tS.
+// family V keeps one set of S, tS and two buffers of 16-bit P, tP. Family KV is family K whose element-wise threads
+// also write tP and P, into the halves of the A and X tiles that the in-place dtS and dS leave unused, and whose output
+// issuer adds the three products of family V.
 // PAD: the tensors' head dimension is smaller than D (columns beyond it are zero-filled by TMA); the K steps and
 // output columns that would only see zeros are then skipped at run time.
 // DUAL = false: primal-only backward (no tangents, no gradient through a tangent output): S and X = gO V^T only,
@@ -388,7 +399,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
           mma_nt(T2, sR(3), sB(buf) + C::HALF, idesc_64, 1);      // X^T += tV gtO^T
         }
         if (leader) umma_commit(&xa_full);
-        if (leader) umma_commit(&b_empty[buf]);
+        if constexpr (!C::KV) if (leader) umma_commit(&b_empty[buf]);   // family KV: gO, gtO are also operands of dV, dtV
       };
 
       if (warp == 9) wait_all(&r_full, 0, 22);
@@ -434,9 +445,10 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
             if (leader) umma_commit(&b_empty[buf]);
             if (leader) umma_commit(&e_free[it & 1]);
           } else {
-            const int buf = it % NA;
+            const int buf = it % NA, bufb = it % NB;
             // dtS replaces A and dS replaces X in place (family Q: A first, X second; family K: X first, A second).
             // dtS only needs A, which the first X/A chain completes, so its two products run before dS exists.
+            // Family KV: tP arrives with dtS (in the other half of the A tile), P with dS (in the X tile).
             const uint32_t E0 = (DUAL && FAM == FAM_Q) ? TS0 + 192 : TS0 + 128;   // dS
             const uint32_t E1 = (DUAL && FAM == FAM_Q) ? TS0 + 128 : TS0 + 192;   // dtS
             if constexpr (DUAL) {
@@ -444,11 +456,17 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
               tc_fence_after_sync();
               mma_out(tmem + C::TMEM_ACC0, E1, sA(buf) + C::HALF, it > 0);   // dtS c1
               mma_out(tmem + C::TMEM_ACC1, E1, sA(buf), it > 0);             // dtS c0
+              if constexpr (C::KV) mma_out(tmem + C::TMEM_ACC2, E1 + C::EUP, sB(bufb) + C::HALF, it > 0);   // dV += tP^T gtO
             }
             wait_all(&p_full[0], it & 1, 26);
             tc_fence_after_sync();
             mma_out(tmem + C::TMEM_ACC0, E0, sA(buf), DUAL ? 1u : static_cast<uint32_t>(it > 0));   // dS c0
             if (leader) umma_commit(&a_empty[buf]);
+            if constexpr (C::KV) {
+              mma_out(tmem + C::TMEM_ACC2, E0 + C::EUP, sB(bufb), DUAL ? 1u : static_cast<uint32_t>(it > 0));   // dV += P^T gO
+              if constexpr (DUAL) mma_out(tmem + C::TMEM_ACC2 + DV, E0 + C::EUP, sB(bufb) + C::HALF, it > 0);       // dtV += P^T gtO
+              if (leader) umma_commit(&b_empty[bufb]);
+            }
             if (has_next) issue_xa(it + 1);
           }
           j = jn;
@@ -520,6 +538,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
       auto keep2 = [&](int ip) -> float2 { return dropout_factors(keep_bits, ip, p.drop.inv_keep); };
       // family V, dual: P goes back to TMEM first (its two output products start while tP is computed)
       constexpr bool SPLIT_P = (FAM == FAM_V) && DUAL;
+      // families Q, K: the upper 16 of a thread's 32 score columns take the lo parts (split mode) or P, tP (family KV)
+      constexpr bool UPPER_USED = SPLIT || C::KV;
       mbar_wait(&st_full[0], it & 1, w, 30);
       tc_fence_after_sync();
       // ---- phase 1: P and ts of this thread's 32 columns (packed fp32x2 arithmetic: the element-wise
@@ -577,6 +597,12 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
 #pragma unroll
         for (int i = 0; i < 16; ++i) P2[i] = make_float2(fast_exp2(x2[i].x), fast_exp2(x2[i].y));
       }
+      // family KV: P as the 16-bit operand of dV, dtV (dropped out; dS, dtS use the P before dropout)
+      auto pack_p = [&](int ip) -> uint32_t {
+        float2 pk = P2[ip];
+        if constexpr (DROP) pk = __fmul2_rn(pk, keep2(ip));
+        return pack2<BF16>(pk.x, pk.y);
+      };
       if constexpr (SPLIT_P) {
         // P into this tile's 16-bit buffer (which the output products of tile it - 2 read), then tP = P (ts - mu)
         if (it >= 2) {
@@ -644,25 +670,31 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
           // phase 2a, as soon as A is complete: dtS, and everything of dS that does not need X (kept in ts2)
           mbar_wait(&a_ready, it & 1, w, 33);
           tc_fence_after_sync();
-          // (split mode: the lo parts go into the upper half of this thread's 32 columns, so all of them are read first)
+          // (split mode: the lo parts go into the upper half of this thread's 32 columns, so all of them are read first;
+          // family KV puts tP there)
           uint32_t ar[2][16];
-          if constexpr (SPLIT) {
+          if constexpr (UPPER_USED) {
             tmem_ld_x16(TA, ar[0]);
             tmem_ld_x16(TA + 16, ar[1]);
             tmem_wait_ld();
           }
 #pragma unroll
           for (int hch = 0; hch < 2; ++hch) {
-            if constexpr (!SPLIT) {
+            if constexpr (!UPPER_USED) {
               tmem_ld_x16(TA + 16 * hch, ar[hch]);
               tmem_wait_ld();
             }
-            uint32_t e1[8], l1[8];
+            uint32_t e1[8], l1[8], u1[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
               const int ip = 8 * hch + i;
               float2 A = make_float2(__uint_as_float(ar[hch][2 * i]), __uint_as_float(ar[hch][2 * i + 1]));
               if constexpr (DROP) A = __fmul2_rn(A, keep2(ip));
+              if constexpr (C::KV) {   // tP = P (ts - mu), the operand of dV += tP^T gtO (dropped out like P)
+                float2 tp = __fmul2_rn(P2[ip], __fadd2_rn(ts2[ip], stat2(1, ip)));
+                if constexpr (DROP) tp = __fmul2_rn(tp, keep2(ip));
+                u1[i] = pack2<BF16>(tp.x, tp.y);
+              }
               const float2 d = __fadd2_rn(A, stat2(3, ip));                       // A - a
               float2 t = __ffma2_rn(ts2[ip], d, stat2(2, ip));                    // ts (A - a) - Delta
               ts2[ip] = __ffma2_rn(stat2(1, ip), A, t);                           // - mu A
@@ -672,6 +704,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
             }
             tmem_st_x8(TA + 8 * hch, e1);
             if constexpr (SPLIT) tmem_st_x8(TA + C::ELO + 8 * hch, l1);
+            if constexpr (C::KV) tmem_st_x8(TA + C::EUP + 8 * hch, u1);
           }
           tmem_wait_st();
           tc_fence_before_sync();
@@ -680,18 +713,18 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
           mbar_wait(&xa_full, it & 1, w, 31);
           tc_fence_after_sync();
           uint32_t xr[2][16];
-          if constexpr (SPLIT) {
+          if constexpr (UPPER_USED) {
             tmem_ld_x16(TX, xr[0]);
             tmem_ld_x16(TX + 16, xr[1]);
             tmem_wait_ld();
           }
 #pragma unroll
           for (int hch = 0; hch < 2; ++hch) {
-            if constexpr (!SPLIT) {
+            if constexpr (!UPPER_USED) {
               tmem_ld_x16(TX + 16 * hch, xr[hch]);
               tmem_wait_ld();
             }
-            uint32_t e0[8], l0[8];
+            uint32_t e0[8], l0[8], u0[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
               const int ip = 8 * hch + i;
@@ -700,27 +733,29 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
               const float2 ds = __fmul2_rn(P2[ip], __fadd2_rn(X, ts2[ip]));
               e0[i] = pack2<BF16>(ds.x, ds.y);
               if constexpr (SPLIT) l0[i] = pack2_residual(ds.x, ds.y, e0[i]);
+              if constexpr (C::KV) u0[i] = pack_p(ip);
             }
             tmem_st_x8(TX + 8 * hch, e0);
             if constexpr (SPLIT) tmem_st_x8(TX + C::ELO + 8 * hch, l0);
+            if constexpr (C::KV) tmem_st_x8(TX + C::EUP + 8 * hch, u0);
           }
         } else {
           mbar_wait(&xa_full, it & 1, w, 31);
           tc_fence_after_sync();
           const uint32_t TX = (FAM == FAM_Q) ? T3 : T2;
           uint32_t xr[2][16];
-          if constexpr (SPLIT) {
+          if constexpr (UPPER_USED) {
             tmem_ld_x16(TX, xr[0]);
             tmem_ld_x16(TX + 16, xr[1]);
             tmem_wait_ld();
           }
 #pragma unroll
           for (int hch = 0; hch < 2; ++hch) {
-            if constexpr (!SPLIT) {
+            if constexpr (!UPPER_USED) {
               tmem_ld_x16(TX + 16 * hch, xr[hch]);
               tmem_wait_ld();
             }
-            uint32_t e0[8], l0[8];
+            uint32_t e0[8], l0[8], u0[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
               const int ip = 8 * hch + i;
@@ -729,9 +764,11 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
               const float2 ds = __fmul2_rn(P2[ip], __fadd2_rn(X, stat2(2, ip)));  // P (X - Delta)
               e0[i] = pack2<BF16>(ds.x, ds.y);
               if constexpr (SPLIT) l0[i] = pack2_residual(ds.x, ds.y, e0[i]);
+              if constexpr (C::KV) u0[i] = pack_p(ip);
             }
             tmem_st_x8(T2 + 8 * hch, e0);
             if constexpr (SPLIT) tmem_st_x8(T2 + C::ELO + 8 * hch, l0);
+            if constexpr (C::KV) tmem_st_x8(T2 + C::EUP + 8 * hch, u0);
           }
         }
       }
@@ -780,32 +817,40 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
     } else {
       constexpr int CH = D / 64;
       uint8_t* patch = sR(0) + warp * (32 * CH * 64);
-      uint32_t q0[CH][16], q1[CH][16];
-#pragma unroll
-      for (int cc = 0; cc < CH; ++cc) {
-        const int c = wg * CH + cc;
-        uint32_t a0[32], a1[32];
-        if (it > 0) {
-          tmem_ld_x32(tmem + lane_off + C::TMEM_ACC0 + c * 32, a0);
-          if constexpr (DUAL) tmem_ld_x32(tmem + lane_off + C::TMEM_ACC1 + c * 32, a1);
-          tmem_wait_ld();
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) { a0[i] = 0u; a1[i] = 0u; }
-        }
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          q0[cc][i] = pack2<BF16>(__uint_as_float(a0[2 * i]) * p.out_scale, __uint_as_float(a0[2 * i + 1]) * p.out_scale);
-          if constexpr (DUAL)
-            q1[cc][i] = pack2<BF16>(__uint_as_float(a1[2 * i]) * p.out_scale, __uint_as_float(a1[2 * i + 1]) * p.out_scale);
-        }
-      }
       const int col0 = wg * (D / 2);
       const int wrow0 = r0 + (warp & 3) * 32;
       const size_t goff = (static_cast<size_t>(row_base) + wrow0) * p.D + col0;
       const int rows = N - wrow0, cols = p.D - col0;
-      store_rows_via_smem<CH>(patch, q0, static_cast<uint16_t*>(p.out0) + goff, p.D, rows, cols, lane);
-      if constexpr (DUAL) store_rows_via_smem<CH>(patch, q1, static_cast<uint16_t*>(p.out1) + goff, p.D, rows, cols, lane);
+      // one pair of accumulators (an output and its tangent counterpart) at a time; family KV has two pairs
+#pragma unroll
+      for (int g = 0; g < C::NACC / 2; ++g) {
+        const uint32_t acc = tmem + lane_off + (g == 0 ? C::TMEM_ACC0 : C::TMEM_ACC2);
+        const float scale = (g == 0) ? p.out_scale : 1.0f;
+        void* const o0 = (g == 0) ? p.out0 : p.out2;
+        void* const o1 = (g == 0) ? p.out1 : p.out3;
+        uint32_t q0[CH][16], q1[CH][16];
+#pragma unroll
+        for (int cc = 0; cc < CH; ++cc) {
+          const int c = wg * CH + cc;
+          uint32_t a0[32], a1[32];
+          if (it > 0) {
+            tmem_ld_x32(acc + c * 32, a0);
+            if constexpr (DUAL) tmem_ld_x32(acc + DV + c * 32, a1);
+            tmem_wait_ld();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) { a0[i] = 0u; a1[i] = 0u; }
+          }
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            q0[cc][i] = pack2<BF16>(__uint_as_float(a0[2 * i]) * scale, __uint_as_float(a0[2 * i + 1]) * scale);
+            if constexpr (DUAL)
+              q1[cc][i] = pack2<BF16>(__uint_as_float(a1[2 * i]) * scale, __uint_as_float(a1[2 * i + 1]) * scale);
+          }
+        }
+        store_rows_via_smem<CH>(patch, q0, static_cast<uint16_t*>(o0) + goff, p.D, rows, cols, lane);
+        if constexpr (DUAL) store_rows_via_smem<CH>(patch, q1, static_cast<uint16_t*>(o1) + goff, p.D, rows, cols, lane);
+      }
     }
   }
   tc_fence_before_sync();
@@ -920,16 +965,17 @@ int launch_family(const jvpfa_bwd_args& a, const float4* stats, cudaStream_t str
                    vgo = make_view(a.go, a.go_strides, a.H, a.N, a.D), vgto = make_view(a.gto, a.gto_strides, a.H, a.N, a.D);
   TensorView rsrc[4];
   TensorView csrc[4];
-  void *out0, *out1;
+  void *out0, *out1, *out2 = nullptr, *out3 = nullptr;
   float out_scale;
   if (FAM == FAM_Q) {
     rsrc[0] = vq; rsrc[1] = vtq; rsrc[2] = vgo; rsrc[3] = vgto;
     csrc[0] = vk; csrc[1] = vtk; csrc[2] = vv; csrc[3] = vtv;
     out0 = a.dq; out1 = a.dtq; out_scale = a.sm_scale;
-  } else if (FAM == FAM_K) {
+  } else if (FAM == FAM_K || FAM == FAM_KV) {
     rsrc[0] = vk; rsrc[1] = vtk; rsrc[2] = vv; rsrc[3] = vtv;
     csrc[0] = vq; csrc[1] = vtq; csrc[2] = vgo; csrc[3] = vgto;
     out0 = a.dk; out1 = a.dtk; out_scale = a.sm_scale;
+    if (FAM == FAM_KV) { out2 = a.dv; out3 = a.dtv; }
   } else {
     rsrc[0] = vk; rsrc[1] = vtk; rsrc[2] = vk; rsrc[3] = vtk;
     csrc[0] = vq; csrc[1] = vtq; csrc[2] = vgo; csrc[3] = vgto;
@@ -955,7 +1001,7 @@ int launch_family(const jvpfa_bwd_args& a, const float4* stats, cudaStream_t str
   p.mv.n64 = (a.N + 63) / 64;
   p.mv.Hm = a.mask.stride[1] == 0 ? 1 : a.H;
   p.stats = stats;
-  p.out0 = out0; p.out1 = out1;
+  p.out0 = out0; p.out1 = out1; p.out2 = out2; p.out3 = out3;
   p.status = static_cast<int*>(a.workspace);
   p.budget_ns = wait_budget_ns();
   p.drop = make_dropout_params(a.dropout_p, a.dropout_seed);
@@ -989,10 +1035,15 @@ int launch_all(const jvpfa_bwd_args& a, cudaStream_t stream, const LaunchMarks& 
     int rc = launch_family<D, FAM_Q, BF16, P, DU, false, DR>(a, stats, stream);
     if (rc != JVPFA_OK) return rc;
     marks.mark(2);
-    rc = launch_family<D, FAM_K, BF16, P, DU, false, DR>(a, stats, stream);
-    if (rc != JVPFA_OK) return rc;
-    marks.mark(3);
-    rc = launch_family<D, FAM_V, BF16, P, DU, false, DR>(a, stats, stream);
+    if constexpr (D == 64) {   // the key-side gradients in one pass
+      rc = launch_family<D, FAM_KV, BF16, P, DU, false, DR>(a, stats, stream);
+      marks.mark(3);
+    } else {
+      rc = launch_family<D, FAM_K, BF16, P, DU, false, DR>(a, stats, stream);
+      if (rc != JVPFA_OK) return rc;
+      marks.mark(3);
+      rc = launch_family<D, FAM_V, BF16, P, DU, false, DR>(a, stats, stream);
+    }
     marks.mark(4);
     return rc;
   };
