@@ -185,7 +185,9 @@ int jvpfa_bwd_noalloc(const jvpfa_bwd_args* args, int32_t* status_word_out, void
 /* jvpfa_bwd with caller-owned CUDA events recorded between its launches, for benchmarks that want the
  * duration of each kernel: events[0] is recorded on `stream` before the preprocess kernel, events[1], [2], [3]
  * before the three main kernels (gradients of the query side, of the key side, of the value side) and events[4]
- * after the last one. `events` holds five cudaEvent_t created by the caller with timing enabled; n_events must be 5.
+ * after the last one (16-bit inputs with a head dimension of at most 64: the key side and the value side are one kernel,
+ * events[3] and events[4] are recorded together after it). `events` holds five cudaEvent_t created by the caller with
+ * timing enabled; n_events must be 5.
  * The library keeps no state for this. No reference counterpart (the reference times whole calls with perf_counter,
  * tests/test_jvp_attention.py:116-143). */
 int jvpfa_bwd_marked(const jvpfa_bwd_args* args, void* stream, void* const* events, int32_t n_events);

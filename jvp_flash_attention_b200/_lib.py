@@ -358,7 +358,8 @@ def bwd(q, k, v, tq, tk, tv, o, to, lse2, mu, go, gto, mask_c: Mask, summary, ca
     """Launches the backward. Dual form: returns (dq, dk, dv, dtq, dtk, dtv). With tq None (primal-only: tk, tv,
     to, gto are ignored) returns (dq, dk, dv). ``marks``: five ``torch.cuda.Event(enable_timing=True)`` that have
     been recorded once (so that they exist); they are recorded before the preprocess kernel, before each of the three
-    family kernels and after the last one."""
+    family kernels and after the last one (head dimensions up to 64 in fp16 / bf16 run the key and value families as one
+    kernel: the last two events are then recorded together)."""
     B, H, N, D = q.shape
     dual = tq is not None
     outs = [torch.empty(q.shape, dtype=q.dtype, device=q.device) for _ in range(6 if dual else 3)]
