@@ -102,8 +102,9 @@ typedef struct jvpfa_bwd_args {
   /* Dropout on the attention probabilities (after the softmax, kept entries scaled by 1 / (1 - p)); the tangent
    * output is the derivative of the dropped-out output for the same keep pattern. The pattern is a function of
    * (dropout_seed, batch*head unit, query, key) -- Philox4x32-10, see csrc/dropout.cuh -- and is regenerated by the
-   * backward: pass the forward's dropout_p and dropout_seed. Tensor-core kernels with head dimension 64 or 128 and
-   * 16-bit inputs only, other shapes answer JVPFA_ERR_UNSUPPORTED. The reference sketches dropout
+   * backward: pass the forward's dropout_p and dropout_seed. Tensor-core kernels only (fp16 / bf16 with a head dimension
+   * that is a multiple of 8 up to 128; fp32 up to 64 with the workspace of its tensor-core path); calls that would run on
+   * the CUDA-core kernels answer JVPFA_ERR_UNSUPPORTED. The reference sketches dropout
    * (jvp_attention.py:105-133) but raises NotImplementedError for dropout_p != 0 (:2550). */
   float dropout_p;
   uint64_t dropout_seed;

@@ -318,8 +318,9 @@ def mask_summary(mask_c: Mask, mask_tensor, B, H, N):
 
 
 def dropout_supported(dtype: torch.dtype, D: int) -> bool:
-    """Dropout runs in the tensor-core kernels of the exact head dimensions 64 and 128 with 16-bit inputs."""
-    return dtype in (torch.float16, torch.bfloat16) and D in (64, 128)
+    """Dropout runs in the tensor-core kernels: fp16 / bf16 with a head dimension that is a multiple of 8 up to 128, fp32
+    up to 64."""
+    return tensor_core_path(dtype, D)
 
 
 def fwd(q, k, v, tq, tk, tv, mask_c: Mask, summary, causal: bool, sm_scale: float, dropout_p: float = 0.0,

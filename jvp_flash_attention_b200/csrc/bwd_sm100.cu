@@ -1048,9 +1048,9 @@ int launch_all(const jvpfa_bwd_args& a, cudaStream_t stream, const LaunchMarks& 
     return rc;
   };
   const bool dual = a.tq != nullptr;
-  if (a.dropout_p > 0.f) {   // dropout: the kernels of the exact head dimensions only
-    if (a.D != D) return JVPFA_ERR_UNSUPPORTED;
-    return dual ? three(std::false_type{}, std::true_type{}, std::true_type{}) : three(std::false_type{}, std::false_type{}, std::true_type{});
+  if (a.dropout_p > 0.f) {
+    if (a.D == D) return dual ? three(std::false_type{}, std::true_type{}, std::true_type{}) : three(std::false_type{}, std::false_type{}, std::true_type{});
+    return dual ? three(std::true_type{}, std::true_type{}, std::true_type{}) : three(std::true_type{}, std::false_type{}, std::true_type{});
   }
   if (a.D == D) return dual ? three(std::false_type{}, std::true_type{}, std::false_type{}) : three(std::false_type{}, std::false_type{}, std::false_type{});
   return dual ? three(std::true_type{}, std::true_type{}, std::false_type{}) : three(std::true_type{}, std::false_type{}, std::false_type{});
@@ -1059,7 +1059,7 @@ int launch_all(const jvpfa_bwd_args& a, cudaStream_t stream, const LaunchMarks& 
 // fp32 inputs: statistics from the fp32 tensors, split pre-pass of the eight (primal-only: four) MMA operands into the
 // workspace, then the three family kernels in their split mode on the split tensors. Workspace: status block, statistics,
 // split tensors.
-template <bool DUAL>
+template <bool DUAL, bool DROP>
 int launch_split(const jvpfa_bwd_args& a, cudaStream_t stream, const LaunchMarks& marks) {
   const int64_t rows = static_cast<int64_t>(a.B) * a.H * a.N;
   uint8_t* ws = static_cast<uint8_t*>(a.workspace);
@@ -1091,13 +1091,13 @@ int launch_split(const jvpfa_bwd_args& a, cudaStream_t stream, const LaunchMarks
   m.q = dst[0]; m.k = dst[1]; m.v = dst[2]; m.go = dst[3];
   if (DUAL) { m.tq = dst[4]; m.tk = dst[5]; m.tv = dst[6]; m.gto = dst[7]; }
   marks.mark(1);
-  rc = launch_family<128, FAM_Q, true, false, DUAL, true>(m, stats, stream, a.D);
+  rc = launch_family<128, FAM_Q, true, false, DUAL, true, DROP>(m, stats, stream, a.D);
   if (rc != JVPFA_OK) return rc;
   marks.mark(2);
-  rc = launch_family<128, FAM_K, true, false, DUAL, true>(m, stats, stream, a.D);
+  rc = launch_family<128, FAM_K, true, false, DUAL, true, DROP>(m, stats, stream, a.D);
   if (rc != JVPFA_OK) return rc;
   marks.mark(3);
-  rc = launch_family<128, FAM_V, true, false, DUAL, true>(m, stats, stream, a.D);
+  rc = launch_family<128, FAM_V, true, false, DUAL, true, DROP>(m, stats, stream, a.D);
   marks.mark(4);
   return rc;
 }
@@ -1110,7 +1110,9 @@ size_t bwd_sm100_split_workspace_bytes(const jvpfa_bwd_args& a) {
 }
 
 int launch_bwd_sm100_split(const jvpfa_bwd_args& a, cudaStream_t stream, const LaunchMarks& marks) {
-  return a.tq != nullptr ? launch_split<true>(a, stream, marks) : launch_split<false>(a, stream, marks);
+  if (a.dropout_p > 0.f)
+    return a.tq != nullptr ? launch_split<true, true>(a, stream, marks) : launch_split<false, true>(a, stream, marks);
+  return a.tq != nullptr ? launch_split<true, false>(a, stream, marks) : launch_split<false, false>(a, stream, marks);
 }
 
 size_t bwd_sm100_workspace_bytes(const jvpfa_bwd_args& a) {

@@ -658,7 +658,7 @@ int launch_one(const jvpfa_fwd_args& a, cudaStream_t stream) {
 }
 
 // fp32 inputs: split pre-pass into the workspace, then the 128-column kernel in its split mode on the split tensors.
-template <bool DUAL>
+template <bool DUAL, bool DROP>
 int launch_split(const jvpfa_fwd_args& a, cudaStream_t stream) {
   using C = FwdCfg<128, true>;
   const int64_t rows = static_cast<int64_t>(a.B) * a.H * a.N;
@@ -700,7 +700,8 @@ int launch_split(const jvpfa_fwd_args& a, cudaStream_t stream) {
   p.o = a.o; p.to = a.to; p.lse2 = a.lse2; p.mu = a.mu;
   p.status = static_cast<int*>(a.workspace);
   p.budget_ns = wait_budget_ns();
-  auto kern = fwd_sm100_kernel<128, DUAL, true, false, true>;
+  p.drop = make_dropout_params(a.dropout_p, a.dropout_seed);
+  auto kern = fwd_sm100_kernel<128, DUAL, true, false, true, DROP>;
   const size_t smem = C::smem_bytes();
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
     return JVPFA_ERR_LAUNCH;
@@ -724,7 +725,8 @@ size_t fwd_sm100_split_workspace_bytes(const jvpfa_fwd_args& a) {
 }
 
 int launch_fwd_sm100_split(const jvpfa_fwd_args& a, cudaStream_t stream) {
-  return a.tq != nullptr ? launch_split<true>(a, stream) : launch_split<false>(a, stream);
+  if (a.dropout_p > 0.f) return a.tq != nullptr ? launch_split<true, true>(a, stream) : launch_split<false, true>(a, stream);
+  return a.tq != nullptr ? launch_split<true, false>(a, stream) : launch_split<false, false>(a, stream);
 }
 
 bool sm100_path_supported(int dtype, int D, int N) {
@@ -737,13 +739,10 @@ template <int D, bool PAD>
 int launch_by_mode(const jvpfa_fwd_args& a, cudaStream_t stream) {
   const bool dual = a.tq != nullptr;
   const bool bf = a.dtype == JVPFA_BF16;
-  if constexpr (!PAD) {
-    if (a.dropout_p > 0.f) {
-      if (dual) return bf ? launch_one<D, true, true, false, true>(a, stream) : launch_one<D, true, false, false, true>(a, stream);
-      return bf ? launch_one<D, false, true, false, true>(a, stream) : launch_one<D, false, false, false, true>(a, stream);
-    }
+  if (a.dropout_p > 0.f) {
+    if (dual) return bf ? launch_one<D, true, true, PAD, true>(a, stream) : launch_one<D, true, false, PAD, true>(a, stream);
+    return bf ? launch_one<D, false, true, PAD, true>(a, stream) : launch_one<D, false, false, PAD, true>(a, stream);
   }
-  if (a.dropout_p > 0.f) return JVPFA_ERR_UNSUPPORTED;
   if (dual) return bf ? launch_one<D, true, true, PAD>(a, stream) : launch_one<D, true, false, PAD>(a, stream);
   return bf ? launch_one<D, false, true, PAD>(a, stream) : launch_one<D, false, false, PAD>(a, stream);
 }

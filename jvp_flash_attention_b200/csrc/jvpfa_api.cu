@@ -265,7 +265,10 @@ int jvpfa_fwd(const jvpfa_fwd_args* a, void* stream) {
     if (rc != JVPFA_OK) return rc;
   }
   if (!(a->dropout_p >= 0.f && a->dropout_p < 1.f)) return JVPFA_ERR_BAD_ARG;
-  if (a->dropout_p > 0.f && !(sm100_path_supported(a->dtype, a->D, a->N) && (a->D == 64 || a->D == 128))) return JVPFA_ERR_UNSUPPORTED;
+  // dropout exists in the tensor-core kernels only
+  if (a->dropout_p > 0.f && !sm100_path_supported(a->dtype, a->D, a->N) &&
+      !(sm100_split_path_supported(a->dtype, a->D, a->N) && a->workspace_bytes >= fwd_sm100_split_workspace_bytes(*a)))
+    return JVPFA_ERR_UNSUPPORTED;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (sm100_path_supported(a->dtype, a->D, a->N)) return launch_fwd_sm100(*a, s);
   // fp32: the tensor-core path when the workspace has room for the split operands, else the CUDA-core kernels
@@ -313,7 +316,10 @@ int bwd_checked(const jvpfa_bwd_args* a, void* stream, void* const* events) {
     if (rc != JVPFA_OK) return rc;
   }
   if (!(eff.dropout_p >= 0.f && eff.dropout_p < 1.f)) return JVPFA_ERR_BAD_ARG;
-  if (eff.dropout_p > 0.f && !(sm100_path_supported(eff.dtype, eff.D, eff.N) && (eff.D == 64 || eff.D == 128))) return JVPFA_ERR_UNSUPPORTED;
+  // dropout exists in the tensor-core kernels only
+  if (eff.dropout_p > 0.f && !sm100_path_supported(eff.dtype, eff.D, eff.N) &&
+      !(sm100_split_path_supported(eff.dtype, eff.D, eff.N) && eff.workspace_bytes >= bwd_sm100_split_workspace_bytes(eff)))
+    return JVPFA_ERR_UNSUPPORTED;
   LaunchMarks marks;
   marks.events = events;
   marks.stream = s;

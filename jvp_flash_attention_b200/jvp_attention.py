@@ -45,7 +45,7 @@ def _validate(q: Tensor, k: Tensor, v: Tensor, attn_mask: Optional[Tensor], drop
         raise ValueError(f"dropout_p must be in [0, 1), got {dropout_p}")
     if dropout_p != 0.0 and not _lib.dropout_supported(q.dtype, q.shape[-1]):
         # the reference refuses every dropout_p != 0 with this exception (jvp_attention.py:2550-2551); here dropout exists
-        # for fp16 / bf16 with head dimension 64 or 128
+        # wherever the tensor-core kernels run (head dimensions that are multiples of 8: up to 128 in fp16 / bf16, 64 in fp32)
         raise NotImplementedError("Dropout is not currently supported in JVP attention.")
     assert q.dim() == 4 and k.dim() == 4 and v.dim() == 4, "q, k, v must have shape (Z, H, N_CTX, HEAD_DIM)"
     Z, H, N_CTX, HEAD_DIM_Q = q.shape
@@ -174,7 +174,7 @@ class JVPAttn:
             causal: bool = False, sm_scale: float | None = None, warp_specialize: bool = True, USE_TMA: bool = True,
             verify_attn_mask: bool = True, dropout_seed: int | None = None) -> Tensor:
         """Primal-only attention (jvp_attention.py:2915-2970). ``warp_specialize`` and ``USE_TMA`` are
-        accepted for signature compatibility and ignored. ``dropout_p`` > 0 (fp16 / bf16, head dimension 64 or 128; the
+        accepted for signature compatibility and ignored. ``dropout_p`` > 0 (every shape the tensor-core kernels take; the
         reference refuses it) drops attention probabilities with a pattern drawn from ``dropout_seed``, or from torch's
         CPU generator when no seed is given."""
         _validate(q, k, v, attn_mask, dropout_p, causal, verify_attn_mask)

@@ -1,4 +1,4 @@
-"""Dropout on the attention probabilities (fp16 / bf16, head dimension 64 or 128). The reference sketches it
+"""Dropout on the attention probabilities (every shape the tensor-core kernels take). The reference sketches it
 (jvp_attention.py:105-133) but refuses dropout_p != 0 (:2550); here the keep pattern is a counter-based function of
 (seed, batch*head unit, query, key) that the forward, the three backward kernels and the CPU oracle all regenerate."""
 import numpy as np
@@ -41,6 +41,10 @@ def test_keep_pattern_matches_the_oracle_bit_for_bit(dev):
     (torch.float16, 1, 2, 256, 128, False, 0.5),
     (torch.float16, 2, 2, 333, 64, True, 0.25),
     (torch.bfloat16, 1, 2, 512, 128, True, 0.2),
+    (torch.bfloat16, 2, 2, 256, 72, False, 0.15),     # padded head dimensions
+    (torch.float16, 1, 3, 130, 40, True, 0.3),
+    (torch.float32, 1, 2, 256, 64, True, 0.25),       # fp32 as three bf16 products
+    (torch.float32, 2, 1, 97, 24, False, 0.1),
 ])
 def test_dual_forward_and_backward_with_dropout(dev, dtype, B, H, N, D, causal, p):
     from jvp_flash_attention_b200 import _lib

@@ -79,8 +79,9 @@ def test_python_api_error_behaviour():
     from jvp_flash_attention_b200.jvp_attention import JVPAttn, attention, MASK_CONST, MIN_SEQUENCE_LENGTH
     assert MASK_CONST == -100.0 and MIN_SEQUENCE_LENGTH == 32
     q = torch.randn(1, 2, 64, 64)
+    big = torch.randn(1, 2, 64, 160)           # a head dimension of the CUDA-core kernels, which have no dropout
     with pytest.raises(NotImplementedError):
-        attention(q, q, q, dropout_p=0.1)
+        attention(big, big, big, dropout_p=0.1)
     with pytest.raises(AssertionError):
         attention(q, q[..., :32], q)
     with pytest.raises(RuntimeError):          # CPU tensors: there is no CPU path

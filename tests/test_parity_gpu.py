@@ -259,10 +259,13 @@ def test_error_behaviour_on_gpu(dev):
     m = torch.ones(1, 2, 64, 64, dtype=torch.bool, device=dev)
     with pytest.raises(ValueError):
         attention(q, q, q, attn_mask=m, causal=True)
+    # dropout exists in the tensor-core kernels only: fp32 above head dimension 64 and 16-bit above 128 refuse it
+    wide32 = torch.randn(1, 2, 64, 72, device=dev)
+    wide16 = torch.randn(1, 2, 64, 160, device=dev, dtype=torch.bfloat16)
     with pytest.raises(NotImplementedError):
-        JVPAttn.fwd_dual(q.float(), q.float(), q.float(), dropout_p=0.5)    # dropout: 16-bit inputs, head dimension 64 / 128 only
+        JVPAttn.fwd_dual(wide32, wide32, wide32, dropout_p=0.5)
     with pytest.raises(NotImplementedError):
-        JVPAttn.fwd_dual(q[..., :32], q[..., :32], q[..., :32], dropout_p=0.5)
+        JVPAttn.fwd_dual(wide16, wide16, wide16, dropout_p=0.5)
     with pytest.raises(AssertionError):
         attention(q, q, q, attn_mask=torch.zeros_like(m))       # all-False head
     with pytest.raises(AssertionError):
