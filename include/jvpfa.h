@@ -123,12 +123,15 @@ const char* jvpfa_error_string(int status);
 size_t jvpfa_fwd_workspace_bytes(const jvpfa_fwd_args* args);
 size_t jvpfa_bwd_workspace_bytes(const jvpfa_bwd_args* args);
 
-/* Bytes of the per-tile mask summary for a mask over sequences of length N with Bm x Hm
- * distinct (batch, head) planes, and the kernel that fills it: per 64x64 tile, bit 0 = some
- * element kept, bit 1 = some element that needs the mask (a boolean False; an additive entry other
- * than zero). Lets the kernels skip fully excluded tiles and skip mask loads on tiles whose entries
- * are all True / all zero. No reference counterpart (the reference reads the mask in
- * every tile, jvp_attention.py:250-262). */
+/* Bytes of the mask summary for a mask over sequences of length N with Bm x Hm distinct (batch, head)
+ * planes, and the kernel that fills it (`summary` 16-byte aligned). Per 64x64 tile: bit 0 = some element
+ * kept, bit 1 = some element that needs the mask (a boolean False; an additive entry other than zero), which
+ * lets the kernels skip fully excluded tiles and skip the mask on tiles whose entries are all True / all zero.
+ * For a boolean mask the buffer also receives the mask packed into 64-bit words, once by query row and once
+ * by key row, so that a kernel thread fetches the 32 entries it needs of a tile with one load whatever the
+ * mask's strides are (2 * N^2 / 8 bytes per plane, N rounded up to 64). The summary belongs to the mask's
+ * contents: compute it again when they change. No reference counterpart (the reference reads the mask
+ * element-wise in every tile, jvp_attention.py:250-262). */
 size_t jvpfa_mask_summary_bytes(int32_t Bm, int32_t Hm, int32_t N);
 int jvpfa_mask_summary(const jvpfa_mask* mask, int32_t B, int32_t H, int32_t N, uint8_t* summary, void* stream);
 

@@ -566,7 +566,17 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
           x2[i] = __ffma2_rn(make_float2(__uint_as_float(a0[2 * i]), __uint_as_float(a0[2 * i + 1])), c1_2, stat2(0, i));
           if constexpr (DUAL) ts2[i] = __fmul2_rn(make_float2(__uint_as_float(a1[2 * i]), __uint_as_float(a1[2 * i + 1])), s_2);
         }
-        if (need_causal || need_bound || need_mask) {
+        if (need_mask && p.mv.rowbits != nullptr) {
+          // boolean mask packed by the summary pre-pass: this thread's 32 entries of the tile in one word (its query row
+          // against the tile's keys in family Q, its key row against the tile's queries in the other families; entries
+          // past the end of the sequence are zero bits; a mask excludes a causal call)
+          const uint32_t mb = (FAM == FAM_Q) ? mask_row_bits(p.mv, b, h, gr_c, j, wg) : mask_col_bits(p.mv, b, h, j, gr_c, wg);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            if (!((mb >> (2 * i)) & 1u)) x2[i].x = -INFINITY;
+            if (!((mb >> (2 * i + 1)) & 1u)) x2[i].y = -INFINITY;
+          }
+        } else if (need_causal || need_bound || need_mask) {
 #pragma unroll
           for (int hch = 0; hch < 2; ++hch) {
             float bias[16];
@@ -995,11 +1005,7 @@ int launch_family(const jvpfa_bwd_args& a, const float4* stats, cudaStream_t str
   p.s = a.sm_scale;
   p.c1 = a.sm_scale * 1.4426950408889634f;
   p.out_scale = out_scale;
-  p.mv.ptr = a.mask.ptr; p.mv.summary = a.mask_summary;
-  p.mv.s0 = a.mask.stride[0]; p.mv.s1 = a.mask.stride[1]; p.mv.s2 = a.mask.stride[2]; p.mv.s3 = a.mask.stride[3];
-  p.mv.kind = a.mask.kind; p.mv.dtype = a.mask.dtype;
-  p.mv.n64 = (a.N + 63) / 64;
-  p.mv.Hm = a.mask.stride[1] == 0 ? 1 : a.H;
+  p.mv = make_mask_view(a.mask, a.mask_summary, a.B, a.H, a.N);
   p.stats = stats;
   p.out0 = out0; p.out1 = out1; p.out2 = out2; p.out3 = out3;
   p.status = static_cast<int*>(a.workspace);

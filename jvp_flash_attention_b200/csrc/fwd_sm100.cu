@@ -421,7 +421,16 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const bool need_causal = p.causal && j * C::BN + C::BN - 1 > q0;
       const bool need_bound = j * C::BN + C::BN > N;
       const bool need_mask = p.mv.kind != JVPFA_MASK_NONE && (bits & kTileAnyMasked);
-      if (need_causal || need_bound || need_mask) {
+      if (need_mask && p.mv.rowbits != nullptr) {
+        // boolean mask packed by the summary pre-pass: this row's 32 entries of the tile in one word (keys past the end
+        // of the sequence are zero bits; a mask excludes a causal call)
+        const uint32_t mb = mask_row_bits(p.mv, b, h, qi_c, j, wg);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          if (!((mb >> (2 * i)) & 1u)) x2[i].x = -INFINITY;
+          if (!((mb >> (2 * i + 1)) & 1u)) x2[i].y = -INFINITY;
+        }
+      } else if (need_causal || need_bound || need_mask) {
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           float bias[16];
@@ -636,11 +645,7 @@ int launch_one(const jvpfa_fwd_args& a, cudaStream_t stream) {
   p.s = a.sm_scale;
   p.c1 = a.sm_scale * 1.4426950408889634f;
   p.thresh = BF16 ? 8.0f : 6.0f;
-  p.mv.ptr = a.mask.ptr; p.mv.summary = a.mask_summary;
-  p.mv.s0 = a.mask.stride[0]; p.mv.s1 = a.mask.stride[1]; p.mv.s2 = a.mask.stride[2]; p.mv.s3 = a.mask.stride[3];
-  p.mv.kind = a.mask.kind; p.mv.dtype = a.mask.dtype;
-  p.mv.n64 = (a.N + 63) / 64;
-  p.mv.Hm = a.mask.stride[1] == 0 ? 1 : a.H;
+  p.mv = make_mask_view(a.mask, a.mask_summary, a.B, a.H, a.N);
   p.o = a.o; p.to = a.to; p.lse2 = a.lse2; p.mu = a.mu;
   p.status = static_cast<int*>(a.workspace);
   p.budget_ns = wait_budget_ns();
@@ -692,11 +697,7 @@ int launch_split(const jvpfa_fwd_args& a, cudaStream_t stream) {
   p.s = a.sm_scale;
   p.c1 = a.sm_scale * 1.4426950408889634f;
   p.thresh = 8.0f;
-  p.mv.ptr = a.mask.ptr; p.mv.summary = a.mask_summary;
-  p.mv.s0 = a.mask.stride[0]; p.mv.s1 = a.mask.stride[1]; p.mv.s2 = a.mask.stride[2]; p.mv.s3 = a.mask.stride[3];
-  p.mv.kind = a.mask.kind; p.mv.dtype = a.mask.dtype;
-  p.mv.n64 = (a.N + 63) / 64;
-  p.mv.Hm = a.mask.stride[1] == 0 ? 1 : a.H;
+  p.mv = make_mask_view(a.mask, a.mask_summary, a.B, a.H, a.N);
   p.o = a.o; p.to = a.to; p.lse2 = a.lse2; p.mu = a.mu;
   p.status = static_cast<int*>(a.workspace);
   p.budget_ns = wait_budget_ns();

@@ -71,48 +71,98 @@ uint64_t wait_budget_ns() {
 
 namespace {
 
-// One CTA per (plane, 64-row band): thread t scans mask rows and ORs per-64-column-tile bits.
-__global__ void mask_summary_kernel(MaskView mv, int N, int Bm, uint8_t* out) {
-  const int qt = blockIdx.x;
+// Summary pre-pass. One CTA per (mask plane, band of 64 queries). The band is walked in chunks of 256 bytes per row
+// (256 boolean entries, 128 16-bit or 64 fp32 ones): the chunk goes through shared memory (16-byte loads when the rows are
+// contiguous and aligned, element-wise loads for any other layout), then thread t owns column t of the chunk and
+// walks down its 64 queries. That gives, per chunk: the key-major 64-bit word of every column, the query-major 32-bit
+// half-words of every row (one warp ballot per row), and the "anything kept" / "anything excluded or biased" flags of
+// the 64x64 tiles the chunk touches. Entries outside the sequence count as not kept and set no flag. The bit words
+// are written for boolean masks only.
+constexpr int kSummaryRowBytes = 256;
+__global__ void __launch_bounds__(256)
+mask_summary_kernel(MaskView mv, int N, uint8_t* flags, uint32_t* rowbits, uint64_t* colbits, int vec_ok) {
+  const int band = blockIdx.x;
   const int plane = blockIdx.y;
   const int bm = plane / mv.Hm, hm = plane % mv.Hm;
-  extern __shared__ uint32_t bits[];  // n64 words
-  for (int i = threadIdx.x; i < mv.n64; i += blockDim.x) bits[i] = 0;
-  __syncthreads();
+  extern __shared__ __align__(16) uint8_t sm[];
+  uint8_t* tile = sm;                                                    // [64][256 bytes]
+  uint32_t* tflags = reinterpret_cast<uint32_t*>(sm + 64 * kSummaryRowBytes);   // n64 words
+  for (int i = threadIdx.x; i < mv.n64; i += blockDim.x) tflags[i] = 0;
+  const int es = mv.kind == JVPFA_MASK_BOOL ? 1 : (mv.dtype == JVPFA_F32 ? 4 : 2);
+  const int cc = kSummaryRowBytes / es;   // columns per chunk
   const int64_t plane_off = bm * mv.s0 + hm * mv.s1;
-  // each warp takes rows, lanes stride over columns
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-  for (int r = warp; r < 64; r += nwarps) {
-    const int q = qt * 64 + r;
-    if (q >= N) break;
-    for (int kt = 0; kt < mv.n64; ++kt) {
-      uint32_t local = 0;
-      for (int c = lane; c < 64; c += 32) {
-        const int k = kt * 64 + c;
-        if (k >= N) continue;
-        const int64_t idx = plane_off + static_cast<int64_t>(q) * mv.s2 + static_cast<int64_t>(k) * mv.s3;
-        // bit "kept": the element takes part; bit "masked": the tile cannot be computed without looking at the mask
-        // (a boolean False, or an additive entry other than zero -- excluded or merely biased)
-        if (mv.kind == JVPFA_MASK_BOOL) {
-          local |= static_cast<const uint8_t*>(mv.ptr)[idx] != 0 ? kTileAnyKept : kTileAnyMasked;
-        } else {
-          const float m = mask_elem_as_float(mv.ptr, idx, mv.dtype);
-          if (m != -INFINITY) local |= kTileAnyKept;
-          if (m != 0.f) local |= kTileAnyMasked;
+  const uint8_t* base = static_cast<const uint8_t*>(mv.ptr);
+  const int t = threadIdx.x, lane = t & 31;
+  const int q0 = band * 64;
+  for (int k0 = 0; k0 < mv.n_pad; k0 += cc) {
+    __syncthreads();   // the previous chunk has been consumed (and, the first time, the flags are cleared)
+    // ---- load the chunk: rows q0 .. q0 + 63, columns k0 .. k0 + cc - 1, zero where outside the sequence
+    if (vec_ok) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int r = (t >> 4) + 16 * i, piece = t & 15;
+        const int q = q0 + r, kf = k0 + piece * (16 / es);      // first column of this 16-byte piece
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (q < N && kf + 16 / es <= N) {
+          v = *reinterpret_cast<const uint4*>(base + (plane_off + static_cast<int64_t>(q) * mv.s2 + kf) * es);
+        } else if (q < N && kf < N) {                           // the piece straddles the end of the row
+          uint8_t tmp[16] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+          const uint8_t* src = base + (plane_off + static_cast<int64_t>(q) * mv.s2 + kf) * es;
+          for (int j = 0; j < (N - kf) * es; ++j) tmp[j] = src[j];
+          v = *reinterpret_cast<const uint4*>(tmp);
         }
+        *reinterpret_cast<uint4*>(tile + r * kSummaryRowBytes + piece * 16) = v;
       }
-      local |= __shfl_xor_sync(0xFFFFFFFFu, local, 16);
-      local |= __shfl_xor_sync(0xFFFFFFFFu, local, 8);
-      local |= __shfl_xor_sync(0xFFFFFFFFu, local, 4);
-      local |= __shfl_xor_sync(0xFFFFFFFFu, local, 2);
-      local |= __shfl_xor_sync(0xFFFFFFFFu, local, 1);
-      if (lane == 0 && local) atomicOr(&bits[kt], local);
+    } else {
+      for (int e = t; e < 64 * cc; e += 256) {
+        const int r = e / cc, c = e - r * cc;
+        const int q = q0 + r, k = k0 + c;
+        const bool in = q < N && k < N;
+        const int64_t idx = plane_off + static_cast<int64_t>(q) * mv.s2 + static_cast<int64_t>(k) * mv.s3;
+        if (es == 1) tile[r * kSummaryRowBytes + c] = in ? base[idx] : 0;
+        else if (es == 2) reinterpret_cast<uint16_t*>(tile)[r * (kSummaryRowBytes / 2) + c] = in ? reinterpret_cast<const uint16_t*>(base)[idx] : 0;
+        else reinterpret_cast<uint32_t*>(tile)[r * (kSummaryRowBytes / 4) + c] = in ? reinterpret_cast<const uint32_t*>(base)[idx] : 0u;
+      }
+    }
+    __syncthreads();
+    // ---- thread t owns column k0 + t
+    if (t < cc && k0 + t < mv.n_pad) {   // (whole warps: cc and n_pad are multiples of 32)
+      const int k = k0 + t;
+      uint64_t word = 0;
+      bool any_masked = false;
+      uint32_t mine0 = 0, mine1 = 0;   // ballots of rows lane and lane + 32
+#pragma unroll 8
+      for (int r = 0; r < 64; ++r) {
+        const bool in = (q0 + r < N) && (k < N);
+        bool kept, masked;
+        if (mv.kind == JVPFA_MASK_BOOL) {
+          kept = tile[r * kSummaryRowBytes + t] != 0;
+          masked = !kept;
+        } else {
+          const float m = mask_elem_as_float(tile, r * cc + t, mv.dtype);
+          kept = m != -INFINITY;
+          masked = m != 0.f;
+        }
+        kept = kept && in;
+        any_masked |= masked && in;
+        word |= static_cast<uint64_t>(kept) << r;
+        const uint32_t ballot = __ballot_sync(0xFFFFFFFFu, kept);
+        if ((r & 31) == lane) { if (r < 32) mine0 = ballot; else mine1 = ballot; }
+      }
+      const int kt = k >> 6, half = (k >> 5) & 1;   // the same for the whole warp
+      if (mv.kind == JVPFA_MASK_BOOL) {
+        colbits[(static_cast<int64_t>(plane) * mv.n64 + band) * mv.n_pad + k] = word;
+        uint32_t* rb = rowbits + ((static_cast<int64_t>(plane) * mv.n64 + kt) * mv.n_pad + q0) * 2 + half;
+        rb[2 * lane] = mine0;
+        rb[2 * (lane + 32)] = mine1;
+      }
+      const uint32_t fl = (__any_sync(0xFFFFFFFFu, word != 0) ? kTileAnyKept : 0u) | (__any_sync(0xFFFFFFFFu, any_masked) ? kTileAnyMasked : 0u);
+      if (lane == 0 && fl) atomicOr(&tflags[kt], fl);
     }
   }
   __syncthreads();
   for (int i = threadIdx.x; i < mv.n64; i += blockDim.x)
-    out[(static_cast<int64_t>(plane) * mv.n64 + qt) * mv.n64 + i] = static_cast<uint8_t>(bits[i]);
-  (void)Bm;
+    flags[(static_cast<int64_t>(plane) * mv.n64 + band) * mv.n64 + i] = static_cast<uint8_t>(tflags[i]);
 }
 
 // Self-test of the failure-detection path: one thread waits on an mbarrier that nothing ever arrives on. The wait
@@ -229,21 +279,27 @@ size_t jvpfa_bwd_workspace_bytes(const jvpfa_bwd_args* a) {
 
 size_t jvpfa_mask_summary_bytes(int32_t Bm, int32_t Hm, int32_t N) {
   const size_t n64 = (static_cast<size_t>(N) + 63) / 64;
-  return static_cast<size_t>(Bm) * Hm * n64 * n64;
+  const size_t planes = static_cast<size_t>(Bm) * Hm;
+  return mask_tile_flag_bytes(planes, n64) + 2 * mask_bit_bytes(planes, n64);
 }
 
 int jvpfa_mask_summary(const jvpfa_mask* mask, int32_t B, int32_t H, int32_t N, uint8_t* summary, void* stream) {
   if (mask == nullptr || summary == nullptr || mask->ptr == nullptr || B <= 0 || H <= 0 || N <= 0) return JVPFA_ERR_BAD_ARG;
   if (mask->kind != JVPFA_MASK_BOOL && mask->kind != JVPFA_MASK_ADDITIVE) return JVPFA_ERR_BAD_ARG;
-  MaskView mv{};
-  mv.ptr = mask->ptr; mv.summary = nullptr;
-  mv.s0 = mask->stride[0]; mv.s1 = mask->stride[1]; mv.s2 = mask->stride[2]; mv.s3 = mask->stride[3];
-  mv.kind = mask->kind; mv.dtype = mask->dtype;
-  mv.n64 = (N + 63) / 64;
-  mv.Hm = mask->stride[1] == 0 ? 1 : H;
+  if ((reinterpret_cast<uintptr_t>(summary) & 15) != 0) return JVPFA_ERR_BAD_ARG;
+  const MaskView mv = make_mask_view(*mask, nullptr, B, H, N);
   const int Bm = mask->stride[0] == 0 ? 1 : B;
-  dim3 grid(mv.n64, Bm * mv.Hm);
-  mask_summary_kernel<<<grid, 256, mv.n64 * sizeof(uint32_t), static_cast<cudaStream_t>(stream)>>>(mv, N, Bm, summary);
+  const size_t planes = static_cast<size_t>(Bm) * mv.Hm;
+  uint8_t* bits = summary + mask_tile_flag_bytes(planes, mv.n64);
+  // 16-byte loads need rows that are contiguous, and every row start on a 16-byte boundary
+  const int es = mask->kind == JVPFA_MASK_BOOL ? 1 : (mask->dtype == JVPFA_F32 ? 4 : 2);
+  auto mult16 = [&](int64_t stride) { return (stride * es) % 16 == 0; };
+  const int vec_ok = mv.s3 == 1 && (reinterpret_cast<uintptr_t>(mask->ptr) & 15) == 0 && mult16(mv.s2) &&
+                     (mv.s0 == 0 || mult16(mv.s0)) && (mv.s1 == 0 || mult16(mv.s1));
+  dim3 grid(mv.n64, static_cast<unsigned>(planes));
+  const size_t smem = 64 * kSummaryRowBytes + mv.n64 * sizeof(uint32_t);
+  mask_summary_kernel<<<grid, 256, smem, static_cast<cudaStream_t>(stream)>>>(
+      mv, N, summary, reinterpret_cast<uint32_t*>(bits), reinterpret_cast<uint64_t*>(bits + mask_bit_bytes(planes, mv.n64)), vec_ok);
   return cudaGetLastError() == cudaSuccess ? JVPFA_OK : JVPFA_ERR_LAUNCH;
 }
 

@@ -1,6 +1,15 @@
-// Mask access shared by the attention kernels: a (B,H,N,N) view given by element strides,
-// the optional 64x64 tile summary, and per-row loaders that turn a run of mask entries into an
-// additive bias in the base-2 logarithm domain (0 / -inf for boolean masks).
+// Mask access shared by the attention kernels: a (B,H,N,N) view given by element strides, the optional output of the
+// summary pre-pass (per 64x64 tile: anything kept / anything excluded or biased; for boolean masks also the mask packed
+// into bits in both orientations), and per-row loaders that turn a run of mask entries into an additive bias in the
+// base-2 logarithm domain (0 / -inf for boolean masks).
+//
+// Layout of the summary buffer for a mask with P = Bm * Hm distinct planes, n64 = ceil(N / 64), n_pad = 64 n64:
+//   tile flags   P * n64 * n64 bytes, rounded up to a multiple of 256
+//   row bits     P * n64 * n_pad words of 64 bits: word [plane][key tile][query] holds the query's 64 entries of that key
+//                tile (bit c = key 64 tile + c takes part); what a thread that owns a query row needs per tile
+//   column bits  the same size: word [plane][query tile][key] holds the key's 64 entries of that query tile; what a
+//                thread that owns a key row needs per tile
+// The bit words exist for boolean masks only; entries outside the sequence are zero bits.
 #pragma once
 #include <cstdint>
 #include <cuda_bf16.h>
@@ -17,7 +26,33 @@ struct MaskView {
   int dtype;               // element type of an additive mask
   int n64;                 // number of 64-wide tiles along N
   int Hm;                  // number of distinct head planes in the summary
+  const uint32_t* rowbits; // packed boolean mask, query-major words (two 32-bit halves each); null if there is none
+  const uint32_t* colbits; // packed boolean mask, key-major words
+  int n_pad;               // 64 * n64
 };
+
+inline size_t mask_tile_flag_bytes(size_t planes, size_t n64) { return (planes * n64 * n64 + 255) / 256 * 256; }
+inline size_t mask_bit_bytes(size_t planes, size_t n64) { return planes * n64 * (64 * n64) * 8; }
+
+// The view the kernels work with, from the mask of a call and the summary buffer (or null) that came with it.
+inline MaskView make_mask_view(const jvpfa_mask& mask, const uint8_t* summary, int B, int H, int N) {
+  MaskView mv{};
+  mv.ptr = mask.ptr;
+  mv.summary = summary;
+  mv.s0 = mask.stride[0]; mv.s1 = mask.stride[1]; mv.s2 = mask.stride[2]; mv.s3 = mask.stride[3];
+  mv.kind = mask.kind;
+  mv.dtype = mask.dtype;
+  mv.n64 = (N + 63) / 64;
+  mv.Hm = mask.stride[1] == 0 ? 1 : H;
+  mv.n_pad = 64 * mv.n64;
+  if (summary != nullptr && mask.kind == JVPFA_MASK_BOOL) {
+    const size_t planes = static_cast<size_t>(mask.stride[0] == 0 ? 1 : B) * mv.Hm;
+    const uint8_t* bits = summary + mask_tile_flag_bytes(planes, mv.n64);
+    mv.rowbits = reinterpret_cast<const uint32_t*>(bits);
+    mv.colbits = reinterpret_cast<const uint32_t*>(bits + mask_bit_bytes(planes, mv.n64));
+  }
+  return mv;
+}
 
 constexpr uint8_t kTileAnyKept = 1;     // some element of the tile takes part in attention
 constexpr uint8_t kTileAnyMasked = 2;   // some element needs the mask: a boolean False, or an additive entry that is not zero
@@ -30,6 +65,17 @@ __device__ __forceinline__ uint8_t mask_tile_bits(const MaskView& mv, int b, int
   const int bm = mv.s0 == 0 ? 0 : b;
   const int hm = mv.s1 == 0 ? 0 : h;
   return mv.summary[((static_cast<int64_t>(bm) * mv.Hm + hm) * mv.n64 + qt) * mv.n64 + kt];
+}
+
+// 32 bits of the packed boolean mask. Row form: query q against keys 64 tile + 32 half + i (bit i); column form: key k
+// against queries 64 tile + 32 half + i.
+__device__ __forceinline__ uint32_t mask_row_bits(const MaskView& mv, int b, int h, int q, int tile, int half) {
+  const int64_t plane = static_cast<int64_t>(mv.s0 == 0 ? 0 : b) * mv.Hm + (mv.s1 == 0 ? 0 : h);
+  return __ldg(mv.rowbits + ((plane * mv.n64 + tile) * mv.n_pad + q) * 2 + half);
+}
+__device__ __forceinline__ uint32_t mask_col_bits(const MaskView& mv, int b, int h, int tile, int k, int half) {
+  const int64_t plane = static_cast<int64_t>(mv.s0 == 0 ? 0 : b) * mv.Hm + (mv.s1 == 0 ? 0 : h);
+  return __ldg(mv.colbits + ((plane * mv.n64 + tile) * mv.n_pad + k) * 2 + half);
 }
 
 __device__ __forceinline__ float mask_elem_as_float(const void* base, int64_t idx, int dtype) {
@@ -66,9 +112,42 @@ __device__ __forceinline__ void mask_bias_run(float (&bias)[CNT], const MaskView
       for (int i = 0; i < CNT; ++i) bias[i] = (first + i < N && mp[i * step]) ? 0.0f : ninf;
     }
   } else {
+    const int es = mv.dtype == JVPFA_F32 ? 4 : 2;
+    const uint8_t* mp = static_cast<const uint8_t*>(mv.ptr) + base * es;
+    if (step == 1 && (reinterpret_cast<uintptr_t>(mp) & 15) == 0 && first + CNT <= N && (CNT % 8) == 0) {
+      // a contiguous, aligned run: 16 bytes per load
+      if (mv.dtype == JVPFA_F32) {
 #pragma unroll
-    for (int i = 0; i < CNT; ++i)
-      bias[i] = (first + i < N) ? mask_elem_as_float(mv.ptr, base + i * step, mv.dtype) * kLog2e : ninf;
+        for (int c = 0; c < CNT / 4; ++c) {
+          const float4 v = *reinterpret_cast<const float4*>(mp + 16 * c);
+          bias[4 * c] = v.x * kLog2e; bias[4 * c + 1] = v.y * kLog2e; bias[4 * c + 2] = v.z * kLog2e; bias[4 * c + 3] = v.w * kLog2e;
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < CNT / 8; ++c) {
+          const uint4 v = *reinterpret_cast<const uint4*>(mp + 16 * c);
+          const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            float lo, hi;
+            if (mv.dtype == JVPFA_BF16) {
+              lo = __uint_as_float(w[i] << 16);
+              hi = __uint_as_float(w[i] & 0xFFFF0000u);
+            } else {
+              const __half2 hh = *reinterpret_cast<const __half2*>(&w[i]);
+              lo = __low2float(hh);
+              hi = __high2float(hh);
+            }
+            bias[8 * c + 2 * i] = lo * kLog2e;
+            bias[8 * c + 2 * i + 1] = hi * kLog2e;
+          }
+        }
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < CNT; ++i)
+        bias[i] = (first + i < N) ? mask_elem_as_float(mv.ptr, base + i * step, mv.dtype) * kLog2e : ninf;
+    }
   }
 }
 #endif
