@@ -165,6 +165,145 @@ mask_summary_kernel(MaskView mv, int N, uint8_t* flags, uint32_t* rowbits, uint6
     flags[(static_cast<int64_t>(plane) * mv.n64 + band) * mv.n64 + i] = static_cast<uint8_t>(tflags[i]);
 }
 
+// The same for a boolean mask whose rows are contiguous and 16-byte aligned, without the detour through shared
+// memory: a warp takes a key tile, its lanes the band's queries (two passes of 32), one half-tile of 32 keys after the
+// other. A lane loads its query's 32 bytes, turns them into 32 bits (that is the query-major half-word), and 32 ballots
+// transpose the warp's 32 x 32 bits into the key-major words. blockIdx.z of gridDim.z takes every gridDim.z-th key tile
+// (more blocks in flight: the kernel lives on memory latency).
+__global__ void __launch_bounds__(256)
+mask_summary_bool_kernel(MaskView mv, int N, uint8_t* flags, uint32_t* rowbits, uint64_t* colbits) {
+  const int band = blockIdx.x;
+  const int plane = blockIdx.y;
+  const int bm = plane / mv.Hm, hm = plane % mv.Hm;
+  const uint8_t* base = static_cast<const uint8_t*>(mv.ptr) + bm * mv.s0 + hm * mv.s1;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int q0 = band * 64;
+  // 4 bytes that are zero / non-zero -> 4 bits
+  auto bits4 = [](uint32_t w) -> uint32_t { return (((__vcmpne4(w, 0u) & 0x01010101u) * 0x01020408u) >> 24) & 0xFu; };
+  for (int kt = blockIdx.z + gridDim.z * warp; kt < mv.n64; kt += gridDim.z * 8) {
+    // all four loads of the tile first (two half-tiles x two passes of queries), so that they are in flight together
+    uint32_t w[2][2][8];
+    uint32_t valid4[2][2];
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int k0 = kt * 64 + half * 32;
+#pragma unroll
+      for (int pass = 0; pass < 2; ++pass) {
+        const int q = q0 + 32 * pass + lane;
+        const uint32_t valid = (q < N && k0 < N) ? (N - k0 >= 32 ? 0xFFFFFFFFu : ((1u << (N - k0)) - 1u)) : 0u;
+        valid4[half][pass] = valid;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) w[half][pass][i] = 0;
+        if (valid) {
+          const uint8_t* src = base + static_cast<int64_t>(q) * mv.s2 + k0;
+          if (valid == 0xFFFFFFFFu) {
+            const uint4 a = *reinterpret_cast<const uint4*>(src), c = *reinterpret_cast<const uint4*>(src + 16);
+            w[half][pass][0] = a.x; w[half][pass][1] = a.y; w[half][pass][2] = a.z; w[half][pass][3] = a.w;
+            w[half][pass][4] = c.x; w[half][pass][5] = c.y; w[half][pass][6] = c.z; w[half][pass][7] = c.w;
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              for (int j = 0; j < 4; ++j)
+                if (k0 + 4 * i + j < N) w[half][pass][i] |= static_cast<uint32_t>(src[4 * i + j]) << (8 * j);
+          }
+        }
+      }
+    }
+    uint32_t kept_any = 0, masked_any = 0;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int k0 = kt * 64 + half * 32;
+      uint32_t col_lo = 0, col_hi = 0;   // lane c: the key-major word of key k0 + c
+#pragma unroll
+      for (int pass = 0; pass < 2; ++pass) {
+        const int q = q0 + 32 * pass + lane;
+        const uint32_t valid = valid4[half][pass];
+        uint32_t bits = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) bits |= bits4(w[half][pass][i]) << (4 * i);
+        bits &= valid;
+        rowbits[((static_cast<int64_t>(plane) * mv.n64 + kt) * mv.n_pad + q) * 2 + half] = bits;
+        kept_any |= bits;
+        masked_any |= ~bits & valid;
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const uint32_t ballot = __ballot_sync(0xFFFFFFFFu, ((bits >> c) & 1u) != 0u);
+          if (c == lane) { if (pass == 0) col_lo = ballot; else col_hi = ballot; }
+        }
+      }
+      colbits[(static_cast<int64_t>(plane) * mv.n64 + band) * mv.n_pad + k0 + lane] = (static_cast<uint64_t>(col_hi) << 32) | col_lo;
+    }
+    const bool any_kept = __any_sync(0xFFFFFFFFu, kept_any != 0u);
+    const bool any_masked = __any_sync(0xFFFFFFFFu, masked_any != 0u);
+    if (lane == 0)
+      flags[(static_cast<int64_t>(plane) * mv.n64 + band) * mv.n64 + kt] =
+          static_cast<uint8_t>((any_kept ? kTileAnyKept : 0) | (any_masked ? kTileAnyMasked : 0));
+  }
+}
+
+// Tile flags of an additive mask whose rows are contiguous and 16-byte aligned: a warp takes a 64x64 tile and reads it
+// in 16-byte pieces (consecutive lanes consecutive pieces of a row), testing bit patterns: "kept" is anything but
+// -inf, "needs the mask" anything but +-0.
+__global__ void __launch_bounds__(256)
+mask_summary_additive_kernel(MaskView mv, int N, uint8_t* flags) {
+  const int band = blockIdx.x;
+  const int plane = blockIdx.y;
+  const int bm = plane / mv.Hm, hm = plane % mv.Hm;
+  const int es = mv.dtype == JVPFA_F32 ? 4 : 2;
+  const int epp = 16 / es;              // elements per piece
+  const int ppr = 64 / epp;             // pieces per tile row
+  const uint8_t* base = static_cast<const uint8_t*>(mv.ptr) + (bm * mv.s0 + hm * mv.s1) * es;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint32_t ninf16 = mv.dtype == JVPFA_BF16 ? 0xFF80u : 0xFC00u;
+  for (int kt = blockIdx.z + gridDim.z * warp; kt < mv.n64; kt += gridDim.z * 8) {
+    bool kept = false, masked = false;
+    for (int p0 = 0; p0 < 64 * ppr; p0 += 32 * 4) {
+      uint4 v[4];
+      int cnt[4];   // elements of the piece that lie inside the sequence
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int p = p0 + 32 * u + lane;
+        const int q = band * 64 + p / ppr, kf = kt * 64 + (p % ppr) * epp;
+        cnt[u] = (q < N && kf < N) ? min(epp, N - kf) : 0;
+        v[u] = make_uint4(0u, 0u, 0u, 0u);
+        const uint8_t* src = base + (static_cast<int64_t>(q) * mv.s2 + kf) * es;
+        if (cnt[u] == epp) {
+          v[u] = *reinterpret_cast<const uint4*>(src);
+        } else if (cnt[u] > 0) {
+          uint8_t tmp[16] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+          for (int j = 0; j < cnt[u] * es; ++j) tmp[j] = src[j];
+          v[u] = *reinterpret_cast<const uint4*>(tmp);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+        if (es == 4) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            if (i < cnt[u]) {
+              kept |= w[i] != 0xFF800000u;
+              masked |= (w[i] & 0x7FFFFFFFu) != 0u;
+            }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            if (i < cnt[u]) {
+              const uint32_t e = (w[i >> 1] >> (16 * (i & 1))) & 0xFFFFu;
+              kept |= e != ninf16;
+              masked |= (e & 0x7FFFu) != 0u;
+            }
+        }
+      }
+    }
+    const bool any_kept = __any_sync(0xFFFFFFFFu, kept);
+    const bool any_masked = __any_sync(0xFFFFFFFFu, masked);
+    if (lane == 0)
+      flags[(static_cast<int64_t>(plane) * mv.n64 + band) * mv.n64 + kt] =
+          static_cast<uint8_t>((any_kept ? kTileAnyKept : 0) | (any_masked ? kTileAnyMasked : 0));
+  }
+}
+
 // Self-test of the failure-detection path: one thread waits on an mbarrier that nothing ever arrives on. The wait
 // runs out of its budget, records WAIT_TIMEOUT_BASE + 77 in the status word and marks the CTA as poisoned; a second
 // wait then gives up after a few polls. The kernel returns normally. out: [0], [1] = results of the two waits
@@ -297,6 +436,17 @@ int jvpfa_mask_summary(const jvpfa_mask* mask, int32_t B, int32_t H, int32_t N, 
   const int vec_ok = mv.s3 == 1 && (reinterpret_cast<uintptr_t>(mask->ptr) & 15) == 0 && mult16(mv.s2) &&
                      (mv.s0 == 0 || mult16(mv.s0)) && (mv.s1 == 0 || mult16(mv.s1));
   dim3 grid(mv.n64, static_cast<unsigned>(planes));
+  if (vec_ok && mask->kind == JVPFA_MASK_BOOL) {
+    grid.z = mv.n64 >= 16 ? 4 : (mv.n64 >= 4 ? 2 : 1);
+    mask_summary_bool_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        mv, N, summary, reinterpret_cast<uint32_t*>(bits), reinterpret_cast<uint64_t*>(bits + mask_bit_bytes(planes, mv.n64)));
+    return cudaGetLastError() == cudaSuccess ? JVPFA_OK : JVPFA_ERR_LAUNCH;
+  }
+  if (vec_ok && mask->kind == JVPFA_MASK_ADDITIVE) {
+    grid.z = mv.n64 >= 16 ? 4 : (mv.n64 >= 4 ? 2 : 1);
+    mask_summary_additive_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(mv, N, summary);
+    return cudaGetLastError() == cudaSuccess ? JVPFA_OK : JVPFA_ERR_LAUNCH;
+  }
   const size_t smem = 64 * kSummaryRowBytes + mv.n64 * sizeof(uint32_t);
   mask_summary_kernel<<<grid, 256, smem, static_cast<cudaStream_t>(stream)>>>(
       mv, N, summary, reinterpret_cast<uint32_t*>(bits), reinterpret_cast<uint64_t*>(bits + mask_bit_bytes(planes, mv.n64)), vec_ok);
