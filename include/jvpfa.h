@@ -129,8 +129,11 @@ size_t jvpfa_bwd_workspace_bytes(const jvpfa_bwd_args* args);
  * lets the kernels skip fully excluded tiles and skip the mask on tiles whose entries are all True / all zero.
  * For a boolean mask the buffer also receives the mask packed into 64-bit words, once by query row and once
  * by key row, so that a kernel thread fetches the 32 entries it needs of a tile with one load whatever the
- * mask's strides are (2 * N^2 / 8 bytes per plane, N rounded up to 64). The summary belongs to the mask's
- * contents: compute it again when they change. No reference counterpart (the reference reads the mask
+ * mask's strides are (2 * N^2 / 8 bytes per plane, N rounded up to 64). For an additive mask with contiguous,
+ * 16-byte aligned rows the words mark the +-0 entries, and a tile whose other entries all carry one value
+ * (0 / -inf, 0 / a large negative constant) is flagged (bit 2) with that value stored per tile: such tiles
+ * are applied from the words too, all others are read element by element. The summary belongs to the
+ * mask's contents: compute it again when they change. No reference counterpart (the reference reads the mask
  * element-wise in every tile, jvp_attention.py:250-262). */
 size_t jvpfa_mask_summary_bytes(int32_t Bm, int32_t Hm, int32_t N);
 int jvpfa_mask_summary(const jvpfa_mask* mask, int32_t B, int32_t H, int32_t N, uint8_t* summary, void* stream);

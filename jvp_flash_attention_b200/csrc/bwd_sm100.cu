@@ -566,23 +566,26 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap rm0, const __grid_constant_
           x2[i] = __ffma2_rn(make_float2(__uint_as_float(a0[2 * i]), __uint_as_float(a0[2 * i + 1])), c1_2, stat2(0, i));
           if constexpr (DUAL) ts2[i] = __fmul2_rn(make_float2(__uint_as_float(a1[2 * i]), __uint_as_float(a1[2 * i + 1])), s_2);
         }
-        if (need_mask && p.mv.rowbits != nullptr) {
-          // boolean mask packed by the summary pre-pass: this thread's 32 entries of the tile in one word (its query row
-          // against the tile's keys in family Q, its key row against the tile's queries in the other families; entries
-          // past the end of the sequence are zero bits; a mask excludes a causal call)
-          const uint32_t mb = (FAM == FAM_Q) ? mask_row_bits(p.mv, b, h, gr_c, j, wg) : mask_col_bits(p.mv, b, h, j, gr_c, wg);
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            if (!((mb >> (2 * i)) & 1u)) x2[i].x = -INFINITY;
-            if (!((mb >> (2 * i + 1)) & 1u)) x2[i].y = -INFINITY;
-          }
-        } else if (need_causal || need_bound || need_mask) {
+        // The mask as this thread sees it: the flags of its own 64x64 tile (query tile, key tile). Packed by the summary
+        // pre-pass (a boolean mask, or a two-valued tile of an additive one), this thread's 32 entries of the tile are
+        // one word: its query row against the tile's keys in family Q, its key row against the tile's queries in the
+        // other families. Anything else is read element by element below.
+        const int my_qt = (FAM == FAM_Q) ? (gr_c >> 6) : j, my_kt = (FAM == FAM_Q) ? j : (gr_c >> 6);
+        int mask_mode = 0;
+        if (need_mask) mask_mode = mask_tile_mode(p.mv, mask_tile_bits(p.mv, b, h, my_qt, my_kt));
+        if (mask_mode == 1) {
+          const float other = p.mv.kind == JVPFA_MASK_BOOL ? -INFINITY : mask_tile_value(p.mv, b, h, my_qt, my_kt) * 1.4426950408889634f;
+          mask_apply_bits(x2, (FAM == FAM_Q) ? mask_row_bits(p.mv, b, h, gr_c, j, wg) : mask_col_bits(p.mv, b, h, j, gr_c, wg), other);
+        }
+        const bool mask_elems = mask_mode == 2;
+        // (keys past the end of the sequence: zero bits of a boolean mask already exclude them)
+        if (need_causal || (need_bound && !(mask_mode == 1 && p.mv.kind == JVPFA_MASK_BOOL)) || mask_elems) {
 #pragma unroll
           for (int hch = 0; hch < 2; ++hch) {
             float bias[16];
 #pragma unroll
             for (int i = 0; i < 16; ++i) bias[i] = 0.f;
-            if (need_mask) {
+            if (mask_elems) {
               if (FAM == FAM_Q) mask_bias_run<16>(bias, p.mv, b, h, gr_c, cw + 16 * hch, N, true);
               else mask_bias_run<16>(bias, p.mv, b, h, cw + 16 * hch, gr_c, N, false);
             }

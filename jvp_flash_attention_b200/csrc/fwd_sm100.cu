@@ -421,22 +421,24 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const bool need_causal = p.causal && j * C::BN + C::BN - 1 > q0;
       const bool need_bound = j * C::BN + C::BN > N;
       const bool need_mask = p.mv.kind != JVPFA_MASK_NONE && (bits & kTileAnyMasked);
-      if (need_mask && p.mv.rowbits != nullptr) {
-        // boolean mask packed by the summary pre-pass: this row's 32 entries of the tile in one word (keys past the end
-        // of the sequence are zero bits; a mask excludes a causal call)
-        const uint32_t mb = mask_row_bits(p.mv, b, h, qi_c, j, wg);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          if (!((mb >> (2 * i)) & 1u)) x2[i].x = -INFINITY;
-          if (!((mb >> (2 * i + 1)) & 1u)) x2[i].y = -INFINITY;
-        }
-      } else if (need_causal || need_bound || need_mask) {
+      // The mask as this thread sees it: the flags of its own 64x64 tile (the two 64-row halves of the query tile may
+      // differ). Packed by the summary pre-pass (a boolean mask, or a two-valued tile of an additive one), this row's 32
+      // entries of the tile are one word; anything else is read element by element below.
+      int mask_mode = 0;
+      if (need_mask) mask_mode = mask_tile_mode(p.mv, mask_tile_bits(p.mv, b, h, qi_c >> 6, j));
+      if (mask_mode == 1) {
+        const float other = p.mv.kind == JVPFA_MASK_BOOL ? -INFINITY : mask_tile_value(p.mv, b, h, qi_c >> 6, j) * 1.4426950408889634f;
+        mask_apply_bits(x2, mask_row_bits(p.mv, b, h, qi_c, j, wg), other);
+      }
+      const bool mask_elems = mask_mode == 2;
+      // (keys past the end of the sequence: zero bits of a boolean mask already exclude them)
+      if (need_causal || (need_bound && !(mask_mode == 1 && p.mv.kind == JVPFA_MASK_BOOL)) || mask_elems) {
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           float bias[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) bias[i] = 0.f;
-          if (need_mask) mask_bias_run<16>(bias, p.mv, b, h, qi_c, k0 + 16 * c, N, true);
+          if (mask_elems) mask_bias_run<16>(bias, p.mv, b, h, qi_c, k0 + 16 * c, N, true);
           if (need_causal) {
 #pragma unroll
             for (int i = 0; i < 16; ++i)

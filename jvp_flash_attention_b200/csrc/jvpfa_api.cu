@@ -241,66 +241,95 @@ mask_summary_bool_kernel(MaskView mv, int N, uint8_t* flags, uint32_t* rowbits, 
   }
 }
 
-// Tile flags of an additive mask whose rows are contiguous and 16-byte aligned: a warp takes a 64x64 tile and reads it
-// in 16-byte pieces (consecutive lanes consecutive pieces of a row), testing bit patterns: "kept" is anything but
-// -inf, "needs the mask" anything but +-0.
+// Additive mask whose rows are contiguous and 16-byte aligned, same scheme as the boolean kernel: a warp takes a key
+// tile, its lanes the band's queries. Bit = the entry is +-0. Per 64x64 tile: "kept" (anything but -inf), "needs the mask"
+// (anything but +-0), and "two-valued": all entries that are not +-0 carry the same bit pattern, which goes into the tile
+// values as a float. ES = bytes per element.
+template <int ES>
 __global__ void __launch_bounds__(256)
-mask_summary_additive_kernel(MaskView mv, int N, uint8_t* flags) {
+mask_summary_additive_kernel(MaskView mv, int N, uint8_t* flags, uint32_t* rowbits, uint64_t* colbits, float* tilevals) {
   const int band = blockIdx.x;
   const int plane = blockIdx.y;
   const int bm = plane / mv.Hm, hm = plane % mv.Hm;
-  const int es = mv.dtype == JVPFA_F32 ? 4 : 2;
-  const int epp = 16 / es;              // elements per piece
-  const int ppr = 64 / epp;             // pieces per tile row
-  const uint8_t* base = static_cast<const uint8_t*>(mv.ptr) + (bm * mv.s0 + hm * mv.s1) * es;
+  const uint8_t* base = static_cast<const uint8_t*>(mv.ptr) + (bm * mv.s0 + hm * mv.s1) * ES;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const uint32_t ninf16 = mv.dtype == JVPFA_BF16 ? 0xFF80u : 0xFC00u;
+  const int q0 = band * 64;
+  constexpr int WORDS = 32 * ES / 4;   // 32-bit words of a query's 32 entries
+  const uint32_t ninf = ES == 4 ? 0xFF800000u : (mv.dtype == JVPFA_BF16 ? 0xFF80u : 0xFC00u);
+  const uint32_t absmask = ES == 4 ? 0x7FFFFFFFu : 0x7FFFu;
   for (int kt = blockIdx.z + gridDim.z * warp; kt < mv.n64; kt += gridDim.z * 8) {
-    bool kept = false, masked = false;
-    for (int p0 = 0; p0 < 64 * ppr; p0 += 32 * 4) {
-      uint4 v[4];
-      int cnt[4];   // elements of the piece that lie inside the sequence
+    bool kept_any = false, masked_any = false, has = false, multi = false;
+    uint32_t val = 0;
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int p = p0 + 32 * u + lane;
-        const int q = band * 64 + p / ppr, kf = kt * 64 + (p % ppr) * epp;
-        cnt[u] = (q < N && kf < N) ? min(epp, N - kf) : 0;
-        v[u] = make_uint4(0u, 0u, 0u, 0u);
-        const uint8_t* src = base + (static_cast<int64_t>(q) * mv.s2 + kf) * es;
-        if (cnt[u] == epp) {
-          v[u] = *reinterpret_cast<const uint4*>(src);
-        } else if (cnt[u] > 0) {
-          uint8_t tmp[16] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
-          for (int j = 0; j < cnt[u] * es; ++j) tmp[j] = src[j];
-          v[u] = *reinterpret_cast<const uint4*>(tmp);
+    for (int half = 0; half < 2; ++half) {
+      const int k0 = kt * 64 + half * 32;
+      uint32_t w[2][WORDS];
+      int cnt[2];   // entries of this lane's run that lie inside the sequence
+#pragma unroll
+      for (int pass = 0; pass < 2; ++pass) {
+        const int q = q0 + 32 * pass + lane;
+        cnt[pass] = (q < N && k0 < N) ? min(32, N - k0) : 0;
+#pragma unroll
+        for (int i = 0; i < WORDS; ++i) w[pass][i] = 0;
+        const uint8_t* src = base + (static_cast<int64_t>(q) * mv.s2 + k0) * ES;
+        if (cnt[pass] == 32) {
+#pragma unroll
+          for (int i = 0; i < WORDS / 4; ++i) {
+            const uint4 v = *reinterpret_cast<const uint4*>(src + 16 * i);
+            w[pass][4 * i] = v.x; w[pass][4 * i + 1] = v.y; w[pass][4 * i + 2] = v.z; w[pass][4 * i + 3] = v.w;
+          }
+        } else if (cnt[pass] > 0) {
+#pragma unroll
+          for (int i = 0; i < WORDS; ++i)
+            for (int j = 0; j < 4; ++j)
+              if (4 * i + j < cnt[pass] * ES) w[pass][i] |= static_cast<uint32_t>(src[4 * i + j]) << (8 * j);
         }
       }
+      uint32_t col_lo = 0, col_hi = 0;
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
-        if (es == 4) {
+      for (int pass = 0; pass < 2; ++pass) {
+        const int q = q0 + 32 * pass + lane;
+        uint32_t bits = 0;
 #pragma unroll
-          for (int i = 0; i < 4; ++i)
-            if (i < cnt[u]) {
-              kept |= w[i] != 0xFF800000u;
-              masked |= (w[i] & 0x7FFFFFFFu) != 0u;
-            }
-        } else {
+        for (int i = 0; i < 32; ++i) {
+          const uint32_t e = ES == 4 ? w[pass][i] : ((w[pass][i >> 1] >> (16 * (i & 1))) & 0xFFFFu);
+          const bool in = i < cnt[pass];
+          const bool zero = (e & absmask) == 0u;
+          bits |= (in && zero ? 1u : 0u) << i;
+          kept_any |= in && e != ninf;
+          const bool nz = in && !zero;
+          masked_any |= nz;
+          multi |= nz && has && e != val;
+          val = (nz && !has) ? e : val;
+          has |= nz;
+        }
+        rowbits[((static_cast<int64_t>(plane) * mv.n64 + kt) * mv.n_pad + q) * 2 + half] = bits;
 #pragma unroll
-          for (int i = 0; i < 8; ++i)
-            if (i < cnt[u]) {
-              const uint32_t e = (w[i >> 1] >> (16 * (i & 1))) & 0xFFFFu;
-              kept |= e != ninf16;
-              masked |= (e & 0x7FFFu) != 0u;
-            }
+        for (int c = 0; c < 32; ++c) {
+          const uint32_t ballot = __ballot_sync(0xFFFFFFFFu, ((bits >> c) & 1u) != 0u);
+          if (c == lane) { if (pass == 0) col_lo = ballot; else col_hi = ballot; }
         }
       }
+      colbits[(static_cast<int64_t>(plane) * mv.n64 + band) * mv.n_pad + k0 + lane] = (static_cast<uint64_t>(col_hi) << 32) | col_lo;
     }
-    const bool any_kept = __any_sync(0xFFFFFFFFu, kept);
-    const bool any_masked = __any_sync(0xFFFFFFFFu, masked);
-    if (lane == 0)
-      flags[(static_cast<int64_t>(plane) * mv.n64 + band) * mv.n64 + kt] =
-          static_cast<uint8_t>((any_kept ? kTileAnyKept : 0) | (any_masked ? kTileAnyMasked : 0));
+    const bool any_kept = __any_sync(0xFFFFFFFFu, kept_any);
+    const bool any_masked = __any_sync(0xFFFFFFFFu, masked_any);
+    const bool any_multi = __any_sync(0xFFFFFFFFu, multi);
+    const uint32_t has_b = __ballot_sync(0xFFFFFFFFu, has);
+    const uint32_t v0 = __shfl_sync(0xFFFFFFFFu, val, has_b ? __ffs(has_b) - 1 : 0);
+    const bool same = __all_sync(0xFFFFFFFFu, !has || val == v0);
+    if (lane == 0) {
+      const bool two = !any_multi && same;
+      const int64_t t = (static_cast<int64_t>(plane) * mv.n64 + band) * mv.n64 + kt;
+      flags[t] = static_cast<uint8_t>((any_kept ? kTileAnyKept : 0) | (any_masked ? kTileAnyMasked : 0) | (two ? kTileTwoValued : 0));
+      float c = 0.f;
+      if (has_b) {
+        if (ES == 4) c = __uint_as_float(v0);
+        else if (mv.dtype == JVPFA_BF16) c = __uint_as_float(v0 << 16);
+        else c = __half2float(__ushort_as_half(static_cast<unsigned short>(v0)));
+      }
+      tilevals[t] = c;
+    }
   }
 }
 
@@ -419,7 +448,7 @@ size_t jvpfa_bwd_workspace_bytes(const jvpfa_bwd_args* a) {
 size_t jvpfa_mask_summary_bytes(int32_t Bm, int32_t Hm, int32_t N) {
   const size_t n64 = (static_cast<size_t>(N) + 63) / 64;
   const size_t planes = static_cast<size_t>(Bm) * Hm;
-  return mask_tile_flag_bytes(planes, n64) + 2 * mask_bit_bytes(planes, n64);
+  return mask_tile_flag_bytes(planes, n64) + 2 * mask_bit_bytes(planes, n64) + mask_tile_value_bytes(planes, n64);
 }
 
 int jvpfa_mask_summary(const jvpfa_mask* mask, int32_t B, int32_t H, int32_t N, uint8_t* summary, void* stream) {
@@ -444,7 +473,11 @@ int jvpfa_mask_summary(const jvpfa_mask* mask, int32_t B, int32_t H, int32_t N, 
   }
   if (vec_ok && mask->kind == JVPFA_MASK_ADDITIVE) {
     grid.z = mv.n64 >= 16 ? 4 : (mv.n64 >= 4 ? 2 : 1);
-    mask_summary_additive_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(mv, N, summary);
+    uint32_t* rb = reinterpret_cast<uint32_t*>(bits);
+    uint64_t* cb = reinterpret_cast<uint64_t*>(bits + mask_bit_bytes(planes, mv.n64));
+    float* tv = reinterpret_cast<float*>(bits + 2 * mask_bit_bytes(planes, mv.n64));
+    if (es == 4) mask_summary_additive_kernel<4><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(mv, N, summary, rb, cb, tv);
+    else mask_summary_additive_kernel<2><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(mv, N, summary, rb, cb, tv);
     return cudaGetLastError() == cudaSuccess ? JVPFA_OK : JVPFA_ERR_LAUNCH;
   }
   const size_t smem = 64 * kSummaryRowBytes + mv.n64 * sizeof(uint32_t);

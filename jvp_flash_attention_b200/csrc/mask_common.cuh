@@ -9,7 +9,11 @@
 //                tile (bit c = key 64 tile + c takes part); what a thread that owns a query row needs per tile
 //   column bits  the same size: word [plane][query tile][key] holds the key's 64 entries of that query tile; what a
 //                thread that owns a key row needs per tile
-// The bit words exist for boolean masks only; entries outside the sequence are zero bits.
+//   tile values  P * n64 * n64 floats (additive masks)
+// Boolean masks: bit = the entry takes part; entries outside the sequence are zero bits. Additive masks (contiguous
+// rows only): bit = the entry is +-0, and a tile all of whose other entries inside the sequence carry one and the same
+// value c is flagged "two-valued" with c in the tile values -- the common additive masks (0 / -inf, 0 / a large negative
+// constant) then cost one load per thread and tile like a boolean mask; every other tile is read element by element.
 #pragma once
 #include <cstdint>
 #include <cuda_bf16.h>
@@ -28,11 +32,13 @@ struct MaskView {
   int Hm;                  // number of distinct head planes in the summary
   const uint32_t* rowbits; // packed boolean mask, query-major words (two 32-bit halves each); null if there is none
   const uint32_t* colbits; // packed boolean mask, key-major words
+  const float* tilevals;   // additive masks: the other value of a two-valued tile; null if there is none
   int n_pad;               // 64 * n64
 };
 
 inline size_t mask_tile_flag_bytes(size_t planes, size_t n64) { return (planes * n64 * n64 + 255) / 256 * 256; }
 inline size_t mask_bit_bytes(size_t planes, size_t n64) { return planes * n64 * (64 * n64) * 8; }
+inline size_t mask_tile_value_bytes(size_t planes, size_t n64) { return planes * n64 * n64 * sizeof(float); }
 
 // The view the kernels work with, from the mask of a call and the summary buffer (or null) that came with it.
 inline MaskView make_mask_view(const jvpfa_mask& mask, const uint8_t* summary, int B, int H, int N) {
@@ -45,17 +51,19 @@ inline MaskView make_mask_view(const jvpfa_mask& mask, const uint8_t* summary, i
   mv.n64 = (N + 63) / 64;
   mv.Hm = mask.stride[1] == 0 ? 1 : H;
   mv.n_pad = 64 * mv.n64;
-  if (summary != nullptr && mask.kind == JVPFA_MASK_BOOL) {
+  if (summary != nullptr && mask.kind != JVPFA_MASK_NONE) {
     const size_t planes = static_cast<size_t>(mask.stride[0] == 0 ? 1 : B) * mv.Hm;
     const uint8_t* bits = summary + mask_tile_flag_bytes(planes, mv.n64);
     mv.rowbits = reinterpret_cast<const uint32_t*>(bits);
     mv.colbits = reinterpret_cast<const uint32_t*>(bits + mask_bit_bytes(planes, mv.n64));
+    if (mask.kind == JVPFA_MASK_ADDITIVE) mv.tilevals = reinterpret_cast<const float*>(bits + 2 * mask_bit_bytes(planes, mv.n64));
   }
   return mv;
 }
 
 constexpr uint8_t kTileAnyKept = 1;     // some element of the tile takes part in attention
 constexpr uint8_t kTileAnyMasked = 2;   // some element needs the mask: a boolean False, or an additive entry that is not zero
+constexpr uint8_t kTileTwoValued = 4;   // additive mask: every entry is +-0 or the tile's one other value (bit words + tile values)
 
 #if defined(__CUDACC__)
 // Summary bits of the 64x64 tile (qt, kt) for batch b, head h; "mixed" when there is no summary.
@@ -67,7 +75,13 @@ __device__ __forceinline__ uint8_t mask_tile_bits(const MaskView& mv, int b, int
   return mv.summary[((static_cast<int64_t>(bm) * mv.Hm + hm) * mv.n64 + qt) * mv.n64 + kt];
 }
 
-// 32 bits of the packed boolean mask. Row form: query q against keys 64 tile + 32 half + i (bit i); column form: key k
+// The other value of the two-valued 64x64 tile (qt, kt) of an additive mask.
+__device__ __forceinline__ float mask_tile_value(const MaskView& mv, int b, int h, int qt, int kt) {
+  const int64_t plane = static_cast<int64_t>(mv.s0 == 0 ? 0 : b) * mv.Hm + (mv.s1 == 0 ? 0 : h);
+  return __ldg(mv.tilevals + (plane * mv.n64 + qt) * mv.n64 + kt);
+}
+
+// 32 bits of the packed mask. Row form: query q against keys 64 tile + 32 half + i (bit i); column form: key k
 // against queries 64 tile + 32 half + i.
 __device__ __forceinline__ uint32_t mask_row_bits(const MaskView& mv, int b, int h, int q, int tile, int half) {
   const int64_t plane = static_cast<int64_t>(mv.s0 == 0 ? 0 : b) * mv.Hm + (mv.s1 == 0 ? 0 : h);
@@ -76,6 +90,26 @@ __device__ __forceinline__ uint32_t mask_row_bits(const MaskView& mv, int b, int
 __device__ __forceinline__ uint32_t mask_col_bits(const MaskView& mv, int b, int h, int tile, int k, int half) {
   const int64_t plane = static_cast<int64_t>(mv.s0 == 0 ? 0 : b) * mv.Hm + (mv.s1 == 0 ? 0 : h);
   return __ldg(mv.colbits + ((plane * mv.n64 + tile) * mv.n_pad + k) * 2 + half);
+}
+
+// Applies the mask to a thread's 32 scores x2[16] (log2 domain) through the packed words, if the thread's own 64x64
+// tile (qt, kt) allows it. `mb`: the thread's 32 bits (mask_row_bits / mask_col_bits), loaded by the caller only when
+// this returns true for its tile. Returns false if the tile has to be read element by element.
+//   0 = nothing to do for this thread (its 64x64 tile needs no mask), 1 = apply bits, 2 = element-wise
+__device__ __forceinline__ int mask_tile_mode(const MaskView& mv, uint8_t my_flags) {
+  if (!(my_flags & kTileAnyMasked)) return 0;
+  if (mv.rowbits == nullptr) return 2;
+  if (mv.kind == JVPFA_MASK_BOOL || (my_flags & kTileTwoValued)) return 1;
+  return 2;
+}
+// x2[i] = scores (2 i, 2 i + 1); `other` = what a zero bit adds (-inf for a boolean mask, c log2(e) for a two-valued
+// additive tile)
+__device__ __forceinline__ void mask_apply_bits(float2 (&x2)[16], uint32_t mb, float other) {
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    if (!((mb >> (2 * i)) & 1u)) x2[i].x += other;
+    if (!((mb >> (2 * i + 1)) & 1u)) x2[i].y += other;
+  }
 }
 
 __device__ __forceinline__ float mask_elem_as_float(const void* base, int64_t idx, int dtype) {

@@ -64,7 +64,7 @@ def test_boolean_mask_summary_matches_torch(dev, B, H, N, layout):
     n_pad = 64 * n64
     fb = (planes * n64 * n64 + 255) // 256 * 256
     bb = planes * n64 * n_pad * 8
-    assert out.numel() == fb + 2 * bb
+    assert out.numel() == fb + 2 * bb + planes * n64 * n64 * 4
     flags = out[: planes * n64 * n64].view(planes, n64, n64)
     rows = out[fb: fb + bb].view(torch.int64).view(planes, n64, n_pad)
     cols = out[fb + bb: fb + 2 * bb].view(torch.int64).view(planes, n64, n_pad)
@@ -94,4 +94,39 @@ def test_additive_mask_summary_flags(dev, dtype, N):
     flags = out[: planes * n64 * n64].view(planes, n64, n64)
     mm = m.reshape(planes, N, N).float()
     want_flags, _, _ = _expected(mm != float("-inf"), mm != 0, N)
-    assert torch.equal(flags, want_flags)
+    assert torch.equal(flags & 3, want_flags)      # (bit 2 marks two-valued tiles of contiguous masks)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+def test_additive_two_valued_tiles(dev, dtype):
+    """Contiguous additive masks: the bit words mark the +-0 entries, and a tile whose other entries all carry one value is
+    flagged two-valued (bit 2) with that value in the tile values; a tile with two different biases is not."""
+    from jvp_flash_attention_b200 import _lib
+    B, H, N = 1, 2, 256
+    g = torch.Generator(device=dev).manual_seed(8)
+    r = torch.rand(B, H, N, N, device=dev, generator=g)
+    m = torch.where(r > 0.7, 0.0, -100.0)
+    m[..., :64, 64:128] = torch.where(r[..., :64, 64:128] > 0.5, 0.0, float("-inf"))   # 0 / -inf
+    m[..., 64:128, 64:128] = torch.where(r[..., 64:128, 64:128] > 0.5, -1.0, -2.0)       # two biases, no zeros
+    m[..., 128:192, :64] = torch.where(r[..., 128:192, :64] > 0.5, 0.0, -3.5)
+    m[..., 128, 5] = -7.0                                                                # a third value
+    m = m.to(dtype)
+    mc = _lib.make_mask(m, B, H, N)
+    out = _lib.mask_summary(mc, m, B, H, N)
+    torch.cuda.synchronize()
+    planes, n64 = B * H, N // 64
+    fb = (planes * n64 * n64 + 255) // 256 * 256
+    bb = planes * n64 * N * 8
+    flags = out[: planes * n64 * n64].view(planes, n64, n64)
+    rows = out[fb: fb + bb].view(torch.int64).view(planes, n64, N)
+    cols = out[fb + bb: fb + 2 * bb].view(torch.int64).view(planes, n64, N)
+    vals = out[fb + 2 * bb: fb + 2 * bb + planes * n64 * n64 * 4].view(torch.float32).view(planes, n64, n64)
+    mm = m.reshape(planes, N, N).float()
+    _, want_rows, want_cols = _expected(mm == 0, mm != 0, N)
+    assert torch.equal(rows, want_rows) and torch.equal(cols, want_cols)
+    two = (flags & 4) != 0
+    assert two[:, 0, 0].all() and vals[:, 0, 0].eq(-100.0).all()
+    assert two[:, 0, 1].all() and torch.isinf(vals[:, 0, 1]).all() and (flags[:, 0, 1] & 3).eq(3).all()
+    assert not two[:, 1, 1].any()
+    assert not two[:, 2, 0].any()
+    assert two[:, 3, 3].all() and vals[:, 3, 3].eq(-100.0).all()
