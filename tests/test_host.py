@@ -72,9 +72,9 @@ def test_workspace_and_summary_sizes(built_library):
     b = _lib.BwdArgs()
     b.B, b.H, b.N, b.D, b.dtype = 2, 3, 100, 64, _lib.BF16
     assert built_library.jvpfa_bwd_workspace_bytes(C.byref(b)) == 256 + 2 * 3 * 100 * 16
-    # 2 planes, 3 tiles of 64 along the sequence: tile flags (18 bytes, rounded up to 256) + the boolean mask packed into
-    # 64-bit words in both orientations (planes x tiles x 192 padded rows each)
-    assert built_library.jvpfa_mask_summary_bytes(2, 1, 130) == 256 + 2 * (2 * 3 * 192 * 8)
+    # 2 planes, 3 tiles of 64 along the sequence: tile flags (18 bytes, rounded up to 256) + the mask packed into 64-bit
+    # words in both orientations (planes x tiles x 192 padded rows each) + one float per tile
+    assert built_library.jvpfa_mask_summary_bytes(2, 1, 130) == 256 + 2 * (2 * 3 * 192 * 8) + 2 * 3 * 3 * 4
 
 
 def test_python_api_error_behaviour():
