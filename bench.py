@@ -169,12 +169,15 @@ def run_reference(args, rank):
 # take the benchmark down). Reads the copy of the reference package under baseline/_ref.
 # ------------------------------------------------------------------------------------------------
 INCUMBENT_SHAPES = (
-    # name, dtype (None = the benchmark's), B, H, N, D, causal   (the reference's published tables: B=2 H=12 N=2048 D=64)
-    ("readme_shape_bf16", "bf16", 2, 12, 2048, 64, False),
-    ("readme_shape_fp16", "fp16", 2, 12, 2048, 64, False),
-    ("readme_shape_fp32", "fp32", 2, 12, 2048, 64, False),
-    ("readme_shape_bf16_causal", "bf16", 2, 12, 2048, 64, True),
-    ("headline_shape", None, 8, 16, 4096, 128, True),
+    # name, dtype (None = the benchmark's), B, H, N, D, causal, mask   (the reference's published tables: B=2 H=12 N=2048
+    # D=64, masks of shape (B,H,N,N) with 10 % of the entries kept, tests/test_jvp_attention.py:309-394)
+    ("readme_shape_bf16", "bf16", 2, 12, 2048, 64, False, None),
+    ("readme_shape_fp16", "fp16", 2, 12, 2048, 64, False, None),
+    ("readme_shape_fp32", "fp32", 2, 12, 2048, 64, False, None),
+    ("readme_shape_bf16_causal", "bf16", 2, 12, 2048, 64, True, None),
+    ("readme_shape_bf16_boolean_mask", "bf16", 2, 12, 2048, 64, False, "boolean"),
+    ("readme_shape_bf16_additive_mask", "bf16", 2, 12, 2048, 64, False, "additive"),
+    ("headline_shape", None, 8, 16, 4096, 128, True, None),
 )
 
 
@@ -210,26 +213,31 @@ def run_incumbent_child(args):
     dev = torch.device("cuda", 0)
     dtypes = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}
     only = set(args.incumbent_shapes.split(",")) if args.incumbent_shapes else None
-    for name, dt_name, B, H, N, D, causal in INCUMBENT_SHAPES:
+    for name, dt_name, B, H, N, D, causal, mask_kind in INCUMBENT_SHAPES:
         if only is not None and name not in only:
             continue
         dt_name = dt_name or args.dtype
         dtype = dtypes[dt_name]
-        rec = {"B": B, "H": H, "N": N, "D": D, "causal": causal, "dtype": dt_name}
+        rec = {"B": B, "H": H, "N": N, "D": D, "causal": causal, "dtype": dt_name, "mask": mask_kind}
         g = torch.Generator(device=dev).manual_seed(7)
         q, k, v, tq, tk, tv, go = [torch.randn(B, H, N, D, device=dev, dtype=dtype, generator=g) for _ in range(7)]
+        mask = None
+        if mask_kind is not None:   # the reference benchmark's masks: every entry kept with probability 0.1
+            keep = torch.rand(B, H, N, N, device=dev, generator=g) > 0.9
+            mask = keep if mask_kind == "boolean" else torch.where(keep, 0.0, -100.0).to(dtype)
         fwd_f, bwd_f = algorithmic_flops(B, H, N, D, causal)
         iters = 5 if N >= 4096 else 20
         try:
             def ref_fwd():
                 with fwAD.dual_level():
-                    o = RefAttn.fwd_dual(fwAD.make_dual(q, tq), fwAD.make_dual(k, tk), fwAD.make_dual(v, tv), causal=causal)
+                    o = RefAttn.fwd_dual(fwAD.make_dual(q, tq), fwAD.make_dual(k, tk), fwAD.make_dual(v, tv), attn_mask=mask,
+                                         causal=causal)
                     return fwAD.unpack_dual(o)
             o_ref, to_ref = ref_fwd()
             torch.cuda.synchronize()
             rec["ref_dual_fwd_ms"] = _time_ms(ref_fwd, iters)
             ql, kl, vl = (t.clone().requires_grad_(True) for t in (q, k, v))
-            o2 = RefAttn.fwd(ql, kl, vl, causal=causal)
+            o2 = RefAttn.fwd(ql, kl, vl, attn_mask=mask, causal=causal)
 
             def ref_bwd():
                 return torch.autograd.grad(o2, (ql, kl, vl), go, retain_graph=True)
@@ -241,15 +249,22 @@ def run_incumbent_child(args):
             out["shapes"][name] = rec
             continue
         s = D ** -0.5
-        mask_c = _lib.make_mask(None, B, H, N)
-        o, to, lse2, mu = _lib.fwd(q, k, v, tq, tk, tv, mask_c, None, causal, s)
-        rec["ours_dual_fwd_ms"] = _time_ms(lambda: _lib.fwd(q, k, v, tq, tk, tv, mask_c, None, causal, s), iters)
-        o1, _, lse1, mu1 = _lib.fwd(q, k, v, None, None, None, mask_c, None, causal, s)
-        gours = _lib.bwd(q, k, v, None, None, None, o1, None, lse1, mu1, go, None, mask_c, None, causal, s)
+        mask_c = _lib.make_mask(mask, B, H, N)
+        summ = _lib.mask_summary(mask_c, mask, B, H, N) if mask is not None else None
+
+        def ours_fwd():   # what a forward call through the public API launches: the mask pre-pass, then the kernel
+            sm = _lib.mask_summary(mask_c, mask, B, H, N) if mask is not None else None
+            return _lib.fwd(q, k, v, tq, tk, tv, mask_c, sm, causal, s)
+        o, to, lse2, mu = ours_fwd()
+        rec["ours_dual_fwd_ms"] = _time_ms(ours_fwd, iters)
+        if mask is not None:
+            rec["ours_mask_prepass_ms"] = _time_ms(lambda: _lib.mask_summary(mask_c, mask, B, H, N), iters)
+        o1, _, lse1, mu1 = _lib.fwd(q, k, v, None, None, None, mask_c, summ, causal, s)
+        gours = _lib.bwd(q, k, v, None, None, None, o1, None, lse1, mu1, go, None, mask_c, summ, causal, s)
         rec["ours_primal_bwd_ms"] = _time_ms(
-            lambda: _lib.bwd(q, k, v, None, None, None, o1, None, lse1, mu1, go, None, mask_c, None, causal, s), iters)
+            lambda: _lib.bwd(q, k, v, None, None, None, o1, None, lse1, mu1, go, None, mask_c, summ, causal, s), iters)
         rec["ours_dual_bwd_ms"] = _time_ms(
-            lambda: _lib.bwd(q, k, v, tq, tk, tv, o, to, lse2, mu, go, go, mask_c, None, causal, s), iters)
+            lambda: _lib.bwd(q, k, v, tq, tk, tv, o, to, lse2, mu, go, go, mask_c, summ, causal, s), iters)
         rec["ref_dual_fwd_tflops"] = fwd_f / rec["ref_dual_fwd_ms"] / 1e9
         rec["ours_dual_fwd_tflops"] = fwd_f / rec["ours_dual_fwd_ms"] / 1e9
         rec["fwd_speedup"] = rec["ref_dual_fwd_ms"] / rec["ours_dual_fwd_ms"]
