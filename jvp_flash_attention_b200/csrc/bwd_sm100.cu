@@ -6,7 +6,7 @@
 // gradient through the tangent output and the tangent-input gradients, which the reference does
 // not compute (jvp_attention.py:3081, 3226).
 //
-// One kernel template, three output families. A CTA owns a "row" tile of 128 sequence positions
+// One kernel template, one instantiation per output family. A CTA owns a "row" tile of 128 sequence positions
 // whose operands stay in shared memory, and streams 64-wide "column" tiles of the other side:
 //   family Q : rows = queries.  scores S, tS, X, A (q on TMEM lanes)    -> dQ, dtQ
 //   family K : rows = keys.     transposed scores (k on TMEM lanes)      -> dK, dtK
