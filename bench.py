@@ -194,6 +194,19 @@ def _time_ms(fn, iters, warmup=3):
     return e0.elapsed_time(e1) / iters
 
 
+def _peak_mb(fn):
+    """Device memory one call allocates beyond what is held before it (outputs included), as the reference's benchmark
+    reports it (tests/test_jvp_attention.py:116-143), in MB."""
+    torch.cuda.synchronize()
+    torch.cuda.reset_peak_memory_stats()
+    before = torch.cuda.memory_allocated()
+    out = fn()
+    torch.cuda.synchronize()
+    peak = torch.cuda.max_memory_allocated()
+    del out
+    return (peak - before) / 1e6
+
+
 def run_incumbent_child(args):
     """Child process: times the reference's dual forward (JVPAttn.fwd_dual under fwAD.dual_level) and its primal-only
     backward through its stock code path, and this library's kernels on the same shapes; prints one JSON object."""
@@ -236,6 +249,7 @@ def run_incumbent_child(args):
             o_ref, to_ref = ref_fwd()
             torch.cuda.synchronize()
             rec["ref_dual_fwd_ms"] = _time_ms(ref_fwd, iters)
+            rec["ref_dual_fwd_peak_mb"] = _peak_mb(ref_fwd)
             ql, kl, vl = (t.clone().requires_grad_(True) for t in (q, k, v))
             o2 = RefAttn.fwd(ql, kl, vl, attn_mask=mask, causal=causal)
 
@@ -257,6 +271,7 @@ def run_incumbent_child(args):
             return _lib.fwd(q, k, v, tq, tk, tv, mask_c, sm, causal, s)
         o, to, lse2, mu = ours_fwd()
         rec["ours_dual_fwd_ms"] = _time_ms(ours_fwd, iters)
+        rec["ours_dual_fwd_peak_mb"] = _peak_mb(ours_fwd)
         if mask is not None:
             rec["ours_mask_prepass_ms"] = _time_ms(lambda: _lib.mask_summary(mask_c, mask, B, H, N), iters)
         o1, _, lse1, mu1 = _lib.fwd(q, k, v, None, None, None, mask_c, summ, causal, s)
