@@ -456,9 +456,9 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       float m_tile = fmaxf(x2[0].x, x2[0].y);
 #pragma unroll
       for (int i = 1; i < 16; ++i) m_tile = fmaxf(m_tile, fmaxf(x2[i].x, x2[i].y));
-      // row maximum over both warpgroups
+      // row maximum over both warpgroups: the two warps that share these 32 rows meet on a barrier of their own
       xch[it & 1][wg][r] = m_tile;
-      named_bar_sync(1, 256);
+      named_bar_sync(3 + (warp & 3), 64);
       m_tile = fmaxf(m_tile, xch[it & 1][wg ^ 1][r]);
       const float m_new = fmaxf(m_used, m_tile);
       const bool need = m_new > m_used + p.thresh;
@@ -535,10 +535,10 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     // o_done flips once per key tile and a parity wait is only meaningful within one phase of the
     // barrier, so the end of the last accumulation has a barrier of its own.
     float l = l2.x + l2.y, mu = mu2.x + mu2.y;
-    named_bar_sync(1, 256);
+    named_bar_sync(3 + (warp & 3), 64);
     xch[0][wg][r] = l;
     xch[1][wg][r] = mu;
-    named_bar_sync(1, 256);
+    named_bar_sync(3 + (warp & 3), 64);
     l += xch[0][wg ^ 1][r];
     mu += xch[1][wg ^ 1][r];
     if (it > 0) {
