@@ -51,17 +51,39 @@ def _(q, k, v, q_t, k_t, v_t, o, o_t, lse2, mu, go, go_t, mask, sm_scale, causal
     return tuple(torch.empty_like(q) for _ in range(6))
 
 
+@torch.library.custom_op("jvp_flash_attention_b200::attn_bwd_primal", mutates_args=())
+def attn_bwd_primal(q: Tensor, k: Tensor, v: Tensor, o: Tensor, lse2: Tensor, mu: Tensor, go: Tensor, mask: Optional[Tensor],
+                    sm_scale: float, causal: bool, dropout_p: float = 0.0,
+                    dropout_seed: int = 0) -> Tuple[Tensor, Tensor, Tensor]:
+    """Backward through the primal output only (nothing flows back through the tangent output): dq, dk, dv."""
+    B, H, N, D = q.shape
+    mask_c = _lib.make_mask(mask, B, H, N)
+    summary = _lib.mask_summary(mask_c, mask, B, H, N) if mask is not None else None
+    return _lib.bwd(q, k, v, None, None, None, o.contiguous(), None, lse2, mu, go, None, mask_c, summary, causal, sm_scale,
+                    dropout_p=dropout_p, dropout_seed=dropout_seed)
+
+
+@attn_bwd_primal.register_fake
+def _(q, k, v, o, lse2, mu, go, mask, sm_scale, causal, dropout_p=0.0, dropout_seed=0):
+    return tuple(torch.empty_like(q) for _ in range(3))
+
+
 def _setup_context(ctx, inputs, output):
     q, k, v, q_t, k_t, v_t, mask, sm_scale, causal, dropout_p, dropout_seed = inputs
     o, o_t, lse2, mu = output
     ctx.save_for_backward(q, k, v, q_t, k_t, v_t, o, o_t, lse2, mu)
     ctx.mask, ctx.sm_scale, ctx.causal, ctx.dropout = mask, sm_scale, causal, (dropout_p, dropout_seed)
+    ctx.set_materialize_grads(False)
 
 
 def _backward(ctx, go, go_t, _g_lse, _g_mu):
     q, k, v, q_t, k_t, v_t, o, o_t, lse2, mu = ctx.saved_tensors
+    if go is None and go_t is None:
+        return (None,) * 11
+    if go_t is None:   # nothing flows back through the tangent output: the primal-only backward, no tangent-input gradients
+        dq, dk, dv = attn_bwd_primal(q, k, v, o, lse2, mu, go, ctx.mask, ctx.sm_scale, ctx.causal, ctx.dropout[0], ctx.dropout[1])
+        return (dq, dk, dv, None, None, None, None, None, None, None, None)
     go = torch.zeros_like(o) if go is None else go
-    go_t = torch.zeros_like(o) if go_t is None else go_t
     grads = attn_bwd_dual(q, k, v, q_t, k_t, v_t, o, o_t, lse2, mu, go, go_t, ctx.mask, ctx.sm_scale, ctx.causal,
                           ctx.dropout[0], ctx.dropout[1])
     return (*grads, None, None, None, None, None)

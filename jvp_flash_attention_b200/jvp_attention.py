@@ -117,14 +117,26 @@ class _DualAttention(Function):
         ctx.causal = causal
         ctx.sm_scale = sm_scale
         ctx.dropout = (dropout_p, dropout_seed)
+        ctx.set_materialize_grads(False)    # an output the loss does not use arrives as None, not as a tensor of zeros
 
     @staticmethod
     @once_differentiable      # the gradients come from kernels: differentiating them again raises instead of returning zeros
     def backward(ctx, go, gto, _g_lse, _g_mu, _g_summary):
         q, k, v, tq, tk, tv, o, to, lse2, mu, summary = ctx.saved_tensors
         B, H, N, D = q.shape
+        if go is None and gto is None:
+            return (None,) * 11
         mask_c = _lib.make_mask(ctx.attn_mask, B, H, N)
         summ = summary if summary.numel() > 0 else None
+        if gto is None:
+            # Nothing flows back through the tangent output (a tangent that is only used as a detached target, or not at
+            # all): the primal-only backward -- what the reference's backward always is (jvp_attention.py:3081, 3226) --
+            # gives dq, dk, dv with half the tile products, and the tangent inputs get no gradient.
+            dq, dk, dv = _lib.bwd(q, k, v, None, None, None, o, None, lse2, mu, go, None, mask_c, summ, ctx.causal,
+                                  ctx.sm_scale, dropout_p=ctx.dropout[0], dropout_seed=ctx.dropout[1])
+            return dq, dk, dv, None, None, None, None, None, None, None, None
+        if go is None:
+            go = torch.zeros_like(o)
         dq, dk, dv, dtq, dtk, dtv = _lib.bwd(q, k, v, tq, tk, tv, o, to, lse2, mu, go, gto, mask_c, summ,
                                               ctx.causal, ctx.sm_scale, dropout_p=ctx.dropout[0], dropout_seed=ctx.dropout[1])
         return dq, dk, dv, dtq, dtk, dtv, None, None, None, None, None

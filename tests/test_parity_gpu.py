@@ -253,6 +253,34 @@ def test_partial_tangents_and_no_tangents(dev):
     assert float((plain.double().cpu() - torch.from_numpy(ref["O"])).abs().max()) <= 2e-2
 
 
+@pytest.mark.parametrize("compiled", [False, True])
+def test_loss_through_one_output_only(dev, compiled):
+    """A loss that uses only O (the tangent is a detached target, or unused) takes the primal-only backward -- the reference's
+    backward is always that (jvp_attention.py:3081, 3226) -- and gives the tangent inputs no gradient; a loss that uses only
+    tO runs the dual backward with a zero gradient for O. Both against the oracle with the other upstream gradient zero."""
+    JVPAttn, _ = _api()
+    ts = make_inputs(2, 2, 200, 64, dtype=torch.float16, seed=12)
+    q, k, v, tq, tk, tv, gO, gtO = [t.to(dev) for t in ts]
+    z = torch.zeros_like(ts[6])
+
+    def call(*leaves):
+        return JVPAttn.dual(*leaves, causal=True)
+    fn = torch.compile(call, fullgraph=True) if compiled else call
+
+    leaves = [t.clone().requires_grad_(True) for t in (q, k, v, tq, tk, tv)]
+    O, tO = fn(*leaves)
+    grads = torch.autograd.grad((O * gO).sum(), leaves, allow_unused=True)
+    assert all(g is None or float(g.abs().max()) == 0.0 for g in grads[3:])
+    ref = closed_form_oracle(*ts[:6], ts[6], z, causal=True)
+    _compare({n: g.double().cpu() for n, g in zip(("dq", "dk", "dv"), grads[:3])}, ref, TOL[torch.float16], names=("dq", "dk", "dv"))
+
+    leaves = [t.clone().requires_grad_(True) for t in (q, k, v, tq, tk, tv)]
+    O, tO = fn(*leaves)
+    grads = torch.autograd.grad((tO * gtO).sum(), leaves)
+    ref = closed_form_oracle(*ts[:6], z, ts[7], causal=True)
+    _compare({n: g.double().cpu() for n, g in zip(GRAD_NAMES, grads)}, ref, TOL[torch.float16], names=GRAD_NAMES)
+
+
 def test_error_behaviour_on_gpu(dev):
     JVPAttn, attention = _api()
     q = torch.randn(1, 2, 64, 64, device=dev, dtype=torch.bfloat16)
