@@ -30,8 +30,8 @@ struct MaskView {
   int dtype;               // element type of an additive mask
   int n64;                 // number of 64-wide tiles along N
   int Hm;                  // number of distinct head planes in the summary
-  const uint32_t* rowbits; // packed boolean mask, query-major words (two 32-bit halves each); null if there is none
-  const uint32_t* colbits; // packed boolean mask, key-major words
+  const uint32_t* rowbits; // packed mask, query-major words (two 32-bit halves each); null if there is no summary
+  const uint32_t* colbits; // packed mask, key-major words
   const float* tilevals;   // additive masks: the other value of a two-valued tile; null if there is none
   int n_pad;               // 64 * n64
 };
@@ -92,18 +92,17 @@ __device__ __forceinline__ uint32_t mask_col_bits(const MaskView& mv, int b, int
   return __ldg(mv.colbits + ((plane * mv.n64 + tile) * mv.n_pad + k) * 2 + half);
 }
 
-// Applies the mask to a thread's 32 scores x2[16] (log2 domain) through the packed words, if the thread's own 64x64
-// tile (qt, kt) allows it. `mb`: the thread's 32 bits (mask_row_bits / mask_col_bits), loaded by the caller only when
-// this returns true for its tile. Returns false if the tile has to be read element by element.
-//   0 = nothing to do for this thread (its 64x64 tile needs no mask), 1 = apply bits, 2 = element-wise
+// How a thread applies the mask to its 32 scores of a tile, from the flags of its own 64x64 tile:
+//   0 = nothing to do (the tile needs no mask), 1 = from the packed words (mask_apply_bits), 2 = element by element
 __device__ __forceinline__ int mask_tile_mode(const MaskView& mv, uint8_t my_flags) {
   if (!(my_flags & kTileAnyMasked)) return 0;
   if (mv.rowbits == nullptr) return 2;
   if (mv.kind == JVPFA_MASK_BOOL || (my_flags & kTileTwoValued)) return 1;
   return 2;
 }
-// x2[i] = scores (2 i, 2 i + 1); `other` = what a zero bit adds (-inf for a boolean mask, c log2(e) for a two-valued
-// additive tile)
+// x2[i] = scores (2 i, 2 i + 1) in the log2 domain, mb = the thread's 32 bits (mask_row_bits / mask_col_bits), `other` =
+// what a zero bit adds: -inf for a boolean mask, c log2(e) for a two-valued additive tile (whose zero bits outside the
+// sequence are excluded by the caller's bound check, not here)
 __device__ __forceinline__ void mask_apply_bits(float2 (&x2)[16], uint32_t mb, float other) {
 #pragma unroll
   for (int i = 0; i < 16; ++i) {
