@@ -65,6 +65,11 @@ def test_bad_arguments_rejected_before_launch(built_library):
     assert L.jvpfa_fwd(C.byref(a), None) == _lib.ERR_BAD_ARG           # null tensors
     assert L.jvpfa_read_status(None, None, None) == _lib.ERR_BAD_ARG
     assert L.jvpfa_mask_summary(None, 1, 1, 64, None, None) == _lib.ERR_BAD_ARG
+    m = _lib.Mask()
+    m.ptr, m.kind, m.dtype = 4096, _lib.MASK_BOOL, 0
+    m.stride[0], m.stride[1], m.stride[2], m.stride[3] = 64 * 64, 0, 64, 1
+    # the summary buffer holds 64-bit words: it has to be 16-byte aligned (refused before anything is launched)
+    assert L.jvpfa_mask_summary(C.byref(m), 1, 1, 64, C.c_void_p(4096 + 8), None) == _lib.ERR_BAD_ARG
 
 
 def test_workspace_and_summary_sizes(built_library):
