@@ -323,7 +323,7 @@ def dit_record(timeout_s=300):
     import subprocess
     rec = {}
     for impl in ("jvpfa", "sdpa"):
-        cmd = [sys.executable, os.path.join(ROOT, "bench_dit.py"), "--steps", "4", "--warmup", "2", "--attention", impl]
+        cmd = [sys.executable, os.path.join(ROOT, "bench_dit.py"), "--steps", "6", "--warmup", "3", "--attention", impl]
         try:
             r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout_s, cwd=ROOT)
             line = [ln for ln in r.stdout.strip().splitlines() if ln.startswith("{")]
